@@ -1,0 +1,113 @@
+/*
+ * leapquant_b200 -- C ABI of the B200 (sm_100a) kernels for LeapQuant's quantized recurrent-state decode path.
+ *
+ * Every entry point takes raw DEVICE pointers, plain sizes and the CUDA stream to launch on (a cudaStream_t passed as
+ * void*; NULL = the legacy default stream).  Nothing here allocates, frees, synchronises or reads device data on the
+ * host, so every call is legal while the stream is being captured into a CUDA graph.  All memory belongs to the caller.
+ *
+ * The LeapQuant reference has no native interface: its kernels are TileLang programs compiled at run time and called
+ * with torch tensors.  Each function below replaces one of those compiled kernels; the comment above it names the
+ * reference kernel factory (file:line in the reference tree) whose launch it stands in for, and the argument order
+ * follows that kernel's tensor order with the aliasing views of the state tensor collapsed into `ssm` + `SS`.
+ *
+ * Packed state layout (reference leapquant/state.py:1-6,29-40).  `ssm` points at element [0,0,0,0] of the fp32 state
+ * tensor [NS, HV, V, K]; `SS` is its slot stride in floats (inner dims packed).  Inside each (slot, head) region of
+ * 4*V*K bytes:   int8 codes [V][K]  |  f32 Sk[K]  |  f32 Sv[V]  |  f16 [R][K+V] = U^T | Q^T   (rest unused).
+ * Window buffers (reference leapquant/state.py:61-70): Kbuf bf16 [NS,HV,L,K], Ubuf bf16 [NS,HV,L,V], Wbuf f32 [NS,HV,L],
+ * Pbuf f32 [NS,HV,1] (GDN, running decay) or [NS,HV,K] (KDA, cumulative log gate), Gbuf f16 [NS,HV,L,K] (KDA only),
+ * hcnt i32 [NS,HV].  Slot indices `idx` are int32; idx <= 0 marks a padding row.
+ *
+ * Supported shapes: K = V = 128; R in {4, 8}; L a multiple of 4 with 4 <= L <= 64; HV a multiple of H;
+ * ssm 16-byte aligned and SS a multiple of 4.  Anything else returns LQ_ERR_UNSUPPORTED / LQ_ERR_ALIGN and launches nothing.
+ *
+ * Return value: LQ_OK (0) or a negative LQ_ERR_* code.  Errors are argument or launch errors found on the host; the
+ * kernels themselves never trap.  lq_strerror() gives a static description.
+ */
+#ifndef LEAPQUANT_B200_H
+#define LEAPQUANT_B200_H
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define LQ_OK 0
+#define LQ_ERR_NULL (-1)         /* a required pointer is NULL */
+#define LQ_ERR_UNSUPPORTED (-2)  /* shape outside the supported set */
+#define LQ_ERR_ALIGN (-3)        /* pointer or stride alignment */
+#define LQ_ERR_RANGE (-4)        /* a size is negative or inconsistent (e.g. HV % H != 0, N < 0) */
+#define LQ_ERR_LAUNCH (-5)       /* the CUDA runtime refused the launch; see lq_last_cuda_error() */
+
+/* Shape of one layer's state, shared by all entry points. */
+typedef struct lq_dims {
+    int32_t NS;   /* slots in the state tensor (slot 0 is the null slot) */
+    int32_t HV;   /* value heads */
+    int32_t H;    /* key heads (HV % H == 0) */
+    int32_t K;    /* key dim   (128) */
+    int32_t V;    /* value dim (128) */
+    int32_t L;    /* window length */
+    int32_t R;    /* Compensator Tokens per head */
+    int64_t SS;   /* slot stride of the state tensor in floats */
+} lq_dims;
+
+int lq_version(void);
+const char* lq_strerror(int code);
+/* cudaError_t value of the most recent LQ_ERR_LAUNCH on this thread (0 if none). */
+int lq_last_cuda_error(void);
+/* Copies the device-side status word (0 = no kernel gave up a bounded wait) to *status and clears it.  Synchronises
+ * the device: debugging / tests only.  No reference counterpart. */
+int lq_device_status(int* status);
+
+/* GDN decode step.  Replaces the kernel built by make_gdn_step (reference leapquant/kernels.py:27-692, launch
+ * signature :80-89).  One token per row n < N: reads the INT8 checkpoint and the h live window entries of
+ * (idx[n], hv), writes o[n,hv,:] (bf16) and appends (k_hat, u, w = 1) to the window; hcnt += 1.
+ * mixed bf16 [N, 2*H*K + HV*V] = q | k | v;  a bf16 [N,HV];  b bf16 [N,HV];  A_log f32 [HV];  dt_bias f32 [HV];
+ * o bf16 [N,HV,V].  scale <= 0 selects K^-1/2.  A head whose window is already full (hcnt == L) is skipped: o = 0. */
+int lq_gdn_step(const lq_dims* d, void* ssm, void* Kbuf, void* Ubuf, float* Wbuf, float* Pbuf, int32_t* hcnt,
+                const void* mixed, const void* a, const void* b, const float* A_log, const float* dt_bias,
+                const int32_t* idx, void* o, int32_t N, float scale, void* stream);
+
+/* KDA decode step.  Replaces the kernel built by make_kda_step (reference leapquant/kernels.py:694-1075, launch
+ * signature :732-741).  As lq_gdn_step with a gate per key channel: a bf16 [N,HV,K], dt_bias f32 [HV,K],
+ * Pbuf f32 [NS,HV,K], Gbuf f16 [NS,HV,L,K].  gate_lower_bound != 0 selects the bounded gate
+ * g = glb * sigmoid(exp(A_log) (a + dt_bias)); 0 selects g = -exp(A_log) softplus(a + dt_bias). */
+int lq_kda_step(const lq_dims* d, void* ssm, void* Kbuf, void* Ubuf, float* Wbuf, float* Pbuf, void* Gbuf,
+                int32_t* hcnt, const void* mixed, const void* a, const void* b, const float* A_log,
+                const float* dt_bias, const int32_t* idx, void* o, int32_t N, float scale, float gate_lower_bound,
+                void* stream);
+
+/* Window flush.  Replaces the kernel built by make_flush (reference leapquant/kernels.py:1077-2033, launch
+ * signature :1139-1148).  For every (idx[n] > 0, hv) with hcnt == L: rebuilds the state from checkpoint + window,
+ * extracts R new Compensator Tokens by `iters` rounds of subspace iteration from Q0 (f32 [V,R]) with CholeskyQR2,
+ * recomputes Sk / Sv, requantises the residual to INT8 and resets the window.  Due heads are found on the device;
+ * the launch shape does not depend on how many are due.  kda != 0 selects the per-channel-gate variant (Gbuf used). */
+int lq_flush(const lq_dims* d, void* ssm, void* Kbuf, void* Ubuf, float* Wbuf, float* Pbuf, void* Gbuf,
+             int32_t* hcnt, const float* Q0, const int32_t* idx, int32_t N, int32_t kda, int32_t iters, void* stream);
+
+/* Standalone quantize.  Replaces the kernel built by make_quantize (reference leapquant/kernels.py:2126-2242);
+ * with kda != 0 it also stands in for LeapQuantState._kda_checkpoint (reference leapquant/state.py:130-142, which
+ * calls lowrank_factor with 3 iterations).  For every idx[n] > 0 and every head: reads the fp32 state [V][K] that
+ * fills the slot and writes the 8-bit checkpoint over it; resets the window (Wbuf = 0, hcnt = 0, Pbuf = 1 for GDN;
+ * Pbuf = 0 and Gbuf = 1 for KDA).  Orthogonalisation is modified Gram-Schmidt, as in the reference kernel. */
+int lq_quantize(const lq_dims* d, void* ssm, float* Wbuf, float* Pbuf, void* Gbuf, int32_t* hcnt, const float* Q0,
+                const int32_t* idx, int32_t N, int32_t kda, int32_t iters, void* stream);
+
+/* Dequantize in place.  Replaces the kernel built by make_dequant (reference leapquant/kernels.py:2041-2123, GDN
+ * branch); with kda != 0 it stands in for LeapQuantState._kda_rebuild (reference leapquant/state.py:118-128).
+ * For every idx[n] > 0 and every head: fp32 state = decay * (deq + Q U^T) + live window entries, written over the
+ * slot.  GDN then resets the window (Wbuf = 0, Pbuf = 1, hcnt = 0); KDA leaves the window buffers untouched, as the
+ * reference does (its quantize after the prefill resets them). */
+int lq_dequant(const lq_dims* d, void* ssm, const void* Kbuf, const void* Ubuf, float* Wbuf, float* Pbuf,
+               const void* Gbuf, int32_t* hcnt, const int32_t* idx, int32_t N, int32_t kda, void* stream);
+
+/* Rank-r factors of x f32 [n, K, V] (contiguous): `iters` rounds of P = x Q -> MGS, Q = x^T P -> MGS from Q0
+ * f32 [V, r]; U = x Q f32 [n, K, r], Q f32 [n, V, r].  Replaces the kernel built by make_lowrank (reference
+ * leapquant/kernels.py:2246-2314) as called by lowrank_factor (:2321-2331). */
+int lq_lowrank(const float* x, const float* Q0, float* U, float* Q, int32_t n, int32_t K, int32_t V, int32_t r,
+               int32_t iters, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* LEAPQUANT_B200_H */

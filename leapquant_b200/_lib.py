@@ -1,0 +1,105 @@
+"""ctypes binding of libleapquant_b200.so (the C ABI declared in include/leapquant_b200.h).
+
+There is no fallback of any kind: if the library is missing, does not load, or a tensor is not on a CUDA device,
+the call raises.  The library is built in-tree by `python -m leapquant_b200.csrc.build`.
+"""
+import ctypes
+import os
+
+import torch
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(_HERE, "libleapquant_b200.so")
+
+EXPORTS = ("lq_version", "lq_strerror", "lq_last_cuda_error", "lq_device_status", "lq_gdn_step", "lq_kda_step",
+           "lq_flush", "lq_quantize", "lq_dequant", "lq_lowrank")
+
+_P = ctypes.c_void_p
+_I = ctypes.c_int32
+_F = ctypes.c_float
+
+
+class LqDims(ctypes.Structure):
+    """struct lq_dims of include/leapquant_b200.h."""
+    _fields_ = [("NS", _I), ("HV", _I), ("H", _I), ("K", _I), ("V", _I), ("L", _I), ("R", _I), ("SS", ctypes.c_int64)]
+
+
+class LeapQuantError(RuntimeError):
+    pass
+
+
+_lib = None
+
+
+def lib():
+    """The loaded library (loads on first use; raises if it is absent)."""
+    global _lib
+    if _lib is None:
+        if not os.path.exists(LIB_PATH):
+            raise LeapQuantError(f"{LIB_PATH} is missing: build it with `python -m leapquant_b200.csrc.build` "
+                                 "(leapquant_b200 has no CPU or PyTorch fallback)")
+        L = ctypes.CDLL(LIB_PATH)
+        D = ctypes.POINTER(LqDims)
+        L.lq_version.restype = _I
+        L.lq_strerror.restype = ctypes.c_char_p
+        L.lq_strerror.argtypes = [_I]
+        L.lq_last_cuda_error.restype = _I
+        L.lq_device_status.argtypes = [ctypes.POINTER(_I)]
+        L.lq_gdn_step.argtypes = [D, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _I, _F, _P]
+        L.lq_kda_step.argtypes = [D, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _I, _F, _F, _P]
+        L.lq_flush.argtypes = [D, _P, _P, _P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _P]
+        L.lq_quantize.argtypes = [D, _P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _P]
+        L.lq_dequant.argtypes = [D, _P, _P, _P, _P, _P, _P, _P, _P, _I, _I, _P]
+        L.lq_lowrank.argtypes = [_P, _P, _P, _P, _I, _I, _I, _I, _I, _P]
+        for name in ("lq_device_status", "lq_gdn_step", "lq_kda_step", "lq_flush", "lq_quantize", "lq_dequant", "lq_lowrank"):
+            getattr(L, name).restype = _I
+        _lib = L
+    return _lib
+
+
+def check(rc, what):
+    if rc != 0:
+        L = lib()
+        msg = L.lq_strerror(rc).decode()
+        extra = f" (cudaError {L.lq_last_cuda_error()})" if rc == -5 else ""
+        raise LeapQuantError(f"{what}: {msg}{extra}")
+
+
+def dims(NS, HV, H, K, V, L, R, SS):
+    return LqDims(int(NS), int(HV), int(H), int(K), int(V), int(L), int(R), int(SS))
+
+
+def ptr(t):
+    """Device address of a CUDA tensor's first element; refuses host tensors (no CPU path exists)."""
+    if not t.is_cuda:
+        raise LeapQuantError("leapquant_b200 kernels take CUDA tensors only (there is no CPU fallback)")
+    return t.data_ptr()
+
+
+def stream_of(t):
+    return torch.cuda.current_stream(t.device).cuda_stream
+
+
+class on_device:
+    """Makes the tensor's device current for the duration of a launch when it is not already."""
+
+    def __init__(self, t):
+        self.idx = t.device.index
+        self.prev = None
+
+    def __enter__(self):
+        cur = torch.cuda.current_device()
+        if cur != self.idx:
+            self.prev = cur
+            torch.cuda.set_device(self.idx)
+
+    def __exit__(self, *exc):
+        if self.prev is not None:
+            torch.cuda.set_device(self.prev)
+
+
+def device_status():
+    """Device-side status word (0 = clean); synchronises.  Debug / tests."""
+    v = _I(0)
+    check(lib().lq_device_status(ctypes.byref(v)), "lq_device_status")
+    return v.value

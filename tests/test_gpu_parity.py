@@ -1,0 +1,381 @@
+"""GPU parity tests: every kernel, called through the C ABI (leapquant_b200.kernels / .state), against the CPU oracle
+on the same seeded inputs.
+
+Tolerances (fp32 after upcast): outputs, appended window rows and dequantised states rtol 1e-3 / atol 1e-4 scaled to the
+tensor's magnitude where the tensor is not O(1); INT8 codes bit-exact given the stored scales and factors, except +-1
+where the pre-rounding value lies within 1e-3 code units of a rounding boundary (fp32 summation order of the rebuild).
+"""
+import pytest
+import torch
+
+from lq_testlib import CpuSide, GpuSide, assert_close, random_states
+from oracle import lq_oracle as O
+
+pytestmark = pytest.mark.gpu
+K = V = 128
+
+
+def make_pair(NS, HV, H, L, R, kda=False, glb=0.0, seed=0, scale=0.1, slot_pad=0, quant_idx=None):
+    cpu = CpuSide(NS, HV, H, K, V, L, R, kda=kda, glb=glb, slot_pad=slot_pad)
+    cpu.ssm.copy_(random_states(NS, HV, V, K, seed, scale))
+    idx = torch.arange(NS, dtype=torch.int32) if quant_idx is None else quant_idx
+    cpu.quantize(idx)
+    return cpu, GpuSide(cpu)
+
+
+def step_inputs(N, H, HV, steps, seed, kda):
+    return O.synth_inputs(N, H, HV, K, V, steps, seed, kda=kda)
+
+
+def compare_window(cpu, gpu, slots, what):
+    s4, v, b = gpu.views_cpu()
+    cb = cpu.bufs
+    sl = torch.as_tensor(slots).long()
+    assert torch.equal(b["hcnt"][sl], cb.hcnt[sl]), what + ": hcnt"
+    assert_close(b["Wbuf"][sl], cb.Wbuf[sl], 1e-5, 1e-7, what + ": Wbuf")
+    assert_close(b["Pbuf"][sl], cb.Pbuf[sl], 1e-4 if cpu.kda else 1e-5, 1e-5 if cpu.kda else 1e-7, what + ": Pbuf")
+    assert_close(b["Kbuf"][sl], cb.Kbuf[sl], 8e-3, 1e-6, what + ": Kbuf")          # one bf16 ulp
+    assert_close(b["Ubuf"][sl], cb.Ubuf[sl], 8e-3, 2e-4, what + ": Ubuf")
+    if cpu.kda:
+        assert_close(b["Gbuf"][sl], cb.Gbuf[sl], 1e-3, 1e-6, what + ": Gbuf")
+    return s4, v, b
+
+
+# ---------------------------------------------------------------------------------------------------------------------
+# quantize / dequantize / lowrank
+# ---------------------------------------------------------------------------------------------------------------------
+def near_boundary_only(code_gpu, x_scaled, tol=1e-3):
+    """Codes equal RNE(x_scaled) except +-1 where x_scaled is within tol of a half-integer."""
+    want = torch.round(x_scaled.double())
+    diff = code_gpu.double() - want
+    bad = diff != 0
+    if not bool(bad.any()):
+        return 0
+    assert int(diff.abs().max()) <= 1, "a code differs by more than one LSB"
+    frac = (x_scaled.double()[bad] - torch.floor(x_scaled.double()[bad]) - 0.5).abs()
+    assert float(frac.max()) < tol, f"code differs away from a rounding boundary (distance {float(frac.max()):.2e})"
+    return int(bad.sum())
+
+
+@pytest.mark.parametrize("R", [4, 8])
+def test_quantize_gdn(R):
+    NS, HV = 5, 3
+    cpu = CpuSide(NS, HV, HV, K, V, 16, R, slot_pad=4096)
+    src = O.outlier_states(NS, HV, V, K, seed=7)
+    cpu.ssm.copy_(src)
+    cpu.bufs.Wbuf.fill_(0.5); cpu.bufs.Pbuf.fill_(0.25); cpu.bufs.hcnt.fill_(3)
+    gpu = GpuSide(cpu)
+    idx = torch.tensor([1, 0, 4, 2], dtype=torch.int32)
+    cpu.quantize(idx)
+    gpu.st.quantize(gpu.ssm, idx.cuda())
+    s4, v, b = gpu.views_cpu()
+    sl = torch.tensor([1, 4, 2])
+    # window reset, untouched slot 3 and null slot 0
+    for t, want in ((b["Wbuf"], 0.0), (b["Pbuf"], 1.0)):
+        assert float((t[sl] - want).abs().max()) == 0.0
+    assert int(b["hcnt"][sl].abs().max()) == 0 and int(b["hcnt"][3].min()) == 3
+    assert torch.equal(s4[3], src[3]) and torch.equal(s4[0], src[0])
+    # factors and dequantised state against the oracle
+    cq = cpu.v
+    S_g = gpu.full_state(sl)
+    S_c = cpu.full_state(sl)
+    mag = float(src[sl].abs().max())
+    assert_close(S_g, S_c, 1e-3, 2e-3 * mag, "dequantised state")
+    uq_g, uq_c = v["uq"][sl].float(), cq["uq"][sl].float()
+    QU_g = torch.einsum("nhrv,nhrc->nhvc", uq_g[..., K:], uq_g[..., :K])
+    QU_c = torch.einsum("nhrv,nhrc->nhvc", uq_c[..., K:], uq_c[..., :K])
+    assert_close(QU_g, QU_c, 1e-3, 2e-3 * mag, "Q U^T")
+    # stage-wise: codes are exactly the oracle's function of the residual defined by the GPU's own stored factors
+    E = src[sl] - QU_g
+    sk_g, sv_g = v["Sk"][sl], v["Sv"][sl]
+    sk_c = torch.clamp(torch.sqrt(E.abs().sum(-2) / V), min=1e-12)
+    assert_close(sk_g, sk_c, 1e-4, 0.0, "Sk given the stored factors")
+    sv_c = torch.clamp((E / sk_g[..., None, :]).abs().amax(-1), min=1e-12)
+    assert_close(sv_g, sv_c, 1e-4, 0.0, "Sv given the stored factors")
+    x = E / (sk_g[..., None, :] * sv_g[..., :, None]) * 127.0
+    nb = near_boundary_only(v["Sq"][sl], x, tol=2e-2)
+    assert nb < 0.002 * x.numel()
+    assert int(v["Sq"][sl].abs().max()) == 127
+
+
+@pytest.mark.parametrize("R,L", [(4, 16), (8, 64)])
+def test_dequantize_gdn(R, L):
+    NS, HV, H = 4, 4, 2
+    cpu, gpu = make_pair(NS, HV, H, L, R, seed=3)
+    idx = torch.tensor([1, 2, 3], dtype=torch.int32)
+    mixed, a, b_, A_log, dtb = step_inputs(3, H, HV, 5, 21, False)
+    o = torch.zeros(3, HV, V, dtype=torch.bfloat16)
+    for t in range(5):                                   # put a few live entries in the window
+        cpu.step(mixed[t], a[t], b_[t], A_log, dtb, idx, o)
+    gpu.sync_from(cpu)
+    want = cpu.full_state([1, 2, 3])
+    didx = torch.tensor([3, 0, 1], dtype=torch.int32)
+    cpu.dequantize(didx)
+    gpu.st.dequantize(gpu.ssm, didx.cuda())
+    got = gpu.ssm.cpu()
+    assert_close(got[[3, 1]], cpu.ssm[[3, 1]], 1e-3, 1e-5, "dequantised fp32 slots")
+    assert_close(got[[1]], want[[0]], 1e-3, 1e-5, "dequantised vs full_state")
+    s4, v, b = gpu.views_cpu()
+    assert int(b["hcnt"][[3, 1]].abs().max()) == 0 and int(b["hcnt"][2].min()) == 5
+    assert float(b["Wbuf"][[3, 1]].abs().max()) == 0.0 and float((b["Pbuf"][[3, 1]] - 1).abs().max()) == 0.0
+    assert torch.equal(s4[2].view(torch.int32), cpu.ssm[2].view(torch.int32))          # slot 2 still packed, bit-identical
+
+
+@pytest.mark.parametrize("r,iters", [(4, 3), (8, 1)])
+def test_lowrank_factor(r, iters):
+    from leapquant_b200.kernels import lowrank_factor
+    g = torch.Generator().manual_seed(5)
+    base = torch.randn(6, K, r, generator=g) @ torch.randn(6, r, V, generator=g)
+    x = base + 0.05 * torch.randn(6, K, V, generator=g)
+    U, Q = lowrank_factor(x.cuda().view(2, 3, K, V), r, iters)
+    Uc, Qc = O.lowrank_factor(x.view(2, 3, K, V), r, iters)
+    assert U.shape == (2, 3, K, r) and Q.shape == (2, 3, V, r)
+    rec_g = U.cpu() @ Q.cpu().transpose(-1, -2)
+    rec_c = Uc @ Qc.transpose(-1, -2)
+    assert_close(rec_g, rec_c, 1e-3, 1e-3 * float(x.abs().max()), "U Q^T")
+    G = torch.einsum("...vr,...vs->...rs", Q.cpu(), Q.cpu())
+    assert torch.allclose(G, torch.eye(r).expand_as(G), atol=1e-4)
+
+
+def test_kda_round_trip():
+    NS, HV, L, R = 4, 2, 32, 8
+    cpu = CpuSide(NS, HV, HV, K, V, L, R, kda=True)
+    src = O.outlier_states(NS, HV, V, K, seed=9)
+    cpu.ssm.copy_(src)
+    gpu = GpuSide(cpu)
+    idx = torch.tensor([2, 1], dtype=torch.int32)
+    cpu.quantize(idx)
+    gpu.st.quantize(gpu.ssm, idx.cuda())
+    s4, v, b = gpu.views_cpu()
+    assert float(b["Pbuf"][[1, 2]].abs().max()) == 0.0 and float((b["Gbuf"][[1, 2]].float() - 1).abs().max()) == 0.0
+    mag = float(src.abs().max())
+    assert_close(gpu.full_state([1, 2]), cpu.full_state([1, 2]), 1e-3, 2e-3 * mag, "KDA checkpoint")
+    assert_close(gpu.full_state([1, 2]), src[[1, 2]], 0.0, 2e-2 * mag, "KDA checkpoint vs source")
+    # live window, then dequantize on the GPU against the reference formula
+    mixed, a, b_, A_log, dtb = step_inputs(2, HV, HV, 7, 4, True)
+    o = torch.zeros(2, HV, V, dtype=torch.bfloat16)
+    for t in range(7):
+        cpu.step(mixed[t], a[t], b_[t], A_log, dtb, idx, o)
+    gpu.sync_from(cpu)
+    want = cpu.full_state([1, 2])
+    gpu.st.dequantize(gpu.ssm, idx.cuda())
+    assert_close(gpu.ssm.cpu()[[1, 2]], want, 1e-3, 1e-4 * mag, "KDA dequantize")
+    assert int(gpu.st.hcnt.cpu()[[1, 2]].min()) == 7                                  # KDA dequantize leaves the window
+
+
+# ---------------------------------------------------------------------------------------------------------------------
+# decode step
+# ---------------------------------------------------------------------------------------------------------------------
+@pytest.mark.parametrize("kda,glb,L,R,H,HV", [(False, 0.0, 16, 4, 2, 4), (False, 0.0, 64, 4, 1, 2), (False, 0.0, 32, 8, 2, 2),
+                                              (True, 0.0, 16, 4, 2, 2), (True, -5.0, 32, 8, 2, 2)])
+def test_step_every_fill_level(kda, glb, L, R, H, HV):
+    """From identical state, one step at every window fill h = 0 .. L-1; the device state is re-synchronised from the
+    oracle after each step so that every step is compared from bit-identical inputs."""
+    NS, N = 6, 4
+    cpu, gpu = make_pair(NS, HV, H, L, R, kda=kda, glb=glb, seed=1)
+    idx = torch.tensor([3, 0, 5, 1], dtype=torch.int32)
+    mixed, a, b_, A_log, dtb = step_inputs(N, H, HV, L, 13, kda)
+    A_log = A_log + 0.1 * torch.arange(HV)
+    dtb = dtb + 0.05
+    o_c = torch.zeros(N, HV, V, dtype=torch.bfloat16)
+    o_g = torch.full((N, HV, V), 7.0, dtype=torch.bfloat16, device="cuda")
+    dev = lambda t: t.cuda()
+    for h in range(L):
+        cpu.step(mixed[h], a[h], b_[h], A_log, dtb, idx, o_c)
+        st = gpu.st
+        vv = st.views(gpu.ssm)
+        args = (mixed[h].cuda(), a[h].reshape(N, HV, -1).contiguous().cuda(), b_[h].cuda(), A_log.cuda(),
+                dtb.reshape(HV, -1).contiguous().cuda(), vv["uq"], idx.cuda(), o_g)
+        if kda:
+            st.kstep(vv["q32"], vv["Sk"], vv["Sv"], vv["skv"], st.Kbuf, st.Ubuf, st.Wbuf, st.Pbuf, st.Gbuf, st.hcnt, *args)
+        else:
+            st.kstep(vv["q32"], vv["Sk"], vv["Sv"], vv["skv"], st.Kbuf, st.Ubuf, st.Wbuf, st.Pbuf, st.hcnt, *args)
+        og = o_g.cpu()
+        assert float(og[1].float().abs().max()) == 0.0, "null row must write zeros"
+        mag = float(o_c.float().abs().max())
+        assert_close(og, o_c, 8e-3, 1e-4 + 1e-3 * mag, f"output at h={h}")
+        compare_window(cpu, gpu, [1, 3, 5], f"h={h}")
+        s4, v, b = gpu.views_cpu()
+        assert torch.equal(b["hcnt"][[0, 2, 4]], cpu.bufs.hcnt[[0, 2, 4]])
+        gpu.sync_from(cpu)
+    assert int(cpu.bufs.hcnt[3].min()) == L
+
+
+def test_step_full_window_is_skipped():
+    cpu, gpu = make_pair(3, 2, 2, 16, 4)
+    gpu.st.hcnt.fill_(16)
+    mixed, a, b_, A_log, dtb = step_inputs(2, 2, 2, 1, 1, False)
+    o = torch.ones(2, 2, V, dtype=torch.bfloat16, device="cuda")
+    vv = gpu.st.views(gpu.ssm)
+    st = gpu.st
+    st.kstep(vv["q32"], vv["Sk"], vv["Sv"], vv["skv"], st.Kbuf, st.Ubuf, st.Wbuf, st.Pbuf, st.hcnt, mixed[0].cuda(),
+             a[0].cuda(), b_[0].cuda(), A_log.cuda(), dtb.cuda(), vv["uq"], torch.tensor([1, 2], dtype=torch.int32).cuda(), o)
+    assert float(o.float().abs().max()) == 0.0 and int(st.hcnt.max()) == 16
+
+
+# ---------------------------------------------------------------------------------------------------------------------
+# flush
+# ---------------------------------------------------------------------------------------------------------------------
+def run_window(cpu, idx, H, HV, L, seed, kda):
+    N = idx.numel()
+    mixed, a, b_, A_log, dtb = step_inputs(N, H, HV, L, seed, kda)
+    o = torch.zeros(N, HV, V, dtype=torch.bfloat16)
+    for t in range(L):
+        cpu.step(mixed[t], a[t], b_[t], A_log, dtb, idx, o)
+
+
+def check_flush(cpu, gpu, idx, slots, what, code_tol=5e-3, code_frac=0.002):
+    """Flush both sides from identical inputs and compare stage by stage."""
+    R, kda = cpu.R, cpu.kda
+    b, v = cpu.bufs, cpu.v
+    sl = torch.as_tensor(slots).long()
+    due = b.hcnt[sl].long() == cpu.L                        # [n, HV]
+    nn, hh = torch.nonzero(due, as_tuple=True)
+    ss = sl[nn]
+    B, Ut_o, Qt_o, p = O.flush_rebuild(v["Sq"][ss, hh], v["Sk"][ss, hh], v["Sv"][ss, hh], b.Kbuf[ss, hh], b.Ubuf[ss, hh],
+                                       b.Wbuf[ss, hh], b.Pbuf[ss, hh], b.Gbuf[ss, hh] if kda else None, v["uq"][ss, hh], kda)
+    T = B + p[:, None, None] * torch.einsum("drv,drc->dvc", Qt_o, Ut_o)
+    before_c = cpu.full_state(slots)
+    nfl = cpu.flush(idx)
+    assert nfl == int(due.sum())
+    vv = gpu.st.views(gpu.ssm)
+    st = gpu.st
+    st.kflush(vv["q32"], vv["Sk"], vv["Sv"], vv["skv"], st.Kbuf, st.Ubuf, st.Wbuf, st.Pbuf, st.Gbuf if kda else st.Gd, st.hcnt,
+              vv["sq16"], vv["uq"], st.Q0, idx.cuda())
+    s4, gv, gb = compare_window(cpu, gpu, slots, what)
+    mag = float(T.abs().max())
+    # factor parity: the rank-R products, never the factors column by column
+    uq_g = gv["uq"][ss, hh].float()
+    uq_c = v["uq"][ss, hh].float()
+    QU_g = torch.einsum("drv,drc->dvc", uq_g[..., K:], uq_g[..., :K])
+    QU_c = torch.einsum("drv,drc->dvc", uq_c[..., K:], uq_c[..., :K])
+    assert_close(QU_g, QU_c, 1e-3, 3e-3 * mag, what + ": Q U^T")
+    # stage-wise: scales and codes are the oracle's function of the residual defined by the GPU's stored factors
+    E = T - QU_g
+    sk_g, sv_g = gv["Sk"][ss, hh], gv["Sv"][ss, hh]
+    sk_c, _ = O.column_scales(E)
+    assert_close(sk_g, sk_c, 1e-4, 1e-12, what + ": Sk given the stored factors")
+    x = E * (1.0 / sk_g)[:, None, :]
+    sv_c = torch.clamp(x.abs().amax(-1), min=1e-12)
+    assert_close(sv_g, sv_c, 1e-4, 1e-12, what + ": Sv given the stored factors")
+    xs = x.double() * (127.0 * (1.0 / sv_g)).double()[:, :, None]
+    nb = near_boundary_only(gv["Sq"][ss, hh], xs, tol=code_tol)
+    assert nb <= code_frac * xs.numel(), f"{what}: {nb} codes off by one"
+    # the flushed state equals the state before the flush up to the INT8 step, on both sides alike
+    after_g = gpu.full_state(slots)
+    after_c = cpu.full_state(slots)
+    err_c = float((after_c - before_c).abs().max())
+    err_g = float((after_g - before_c).abs().max())
+    assert err_g <= 1.5 * err_c + 1e-6 * mag, f"{what}: flush error {err_g:.3e} vs oracle {err_c:.3e}"
+    assert_close(after_g, after_c, 1e-3, 3e-3 * mag + 2 * err_c, what + ": state after flush")
+
+
+@pytest.mark.parametrize("kda,L,R", [(False, 16, 4), (False, 64, 4), (False, 32, 8), (True, 16, 4), (True, 32, 8)])
+def test_flush_against_oracle(kda, L, R):
+    NS, HV, H = 5, 4, 2
+    cpu, gpu = make_pair(NS, HV, H, L, R, kda=kda, seed=2)
+    idx = torch.tensor([4, 2, 0, 1], dtype=torch.int32)
+    run_window(cpu, idx, H, HV, L, 31, kda)
+    cpu.bufs.hcnt[2, 1] = L - 3                              # one head of a due row is not due
+    cpu.bufs.hcnt[3] = L                                     # a full slot that is not in the call
+    gpu.sync_from(cpu)
+    check_flush(cpu, gpu, idx, [4, 2, 1], f"flush kda={kda} L={L} R={R}")
+    assert int(gpu.st.hcnt[3].min()) == L and int(gpu.st.hcnt[2, 1]) == L - 3
+
+
+def test_flush_nothing_due_is_a_noop():
+    cpu, gpu = make_pair(4, 2, 2, 16, 4)
+    before = gpu.store.clone()
+    idx = torch.tensor([1, 2, 3], dtype=torch.int32).cuda()
+    vv = gpu.st.views(gpu.ssm)
+    st = gpu.st
+    st.kflush(vv["q32"], vv["Sk"], vv["Sv"], vv["skv"], st.Kbuf, st.Ubuf, st.Wbuf, st.Pbuf, st.Gd, st.hcnt, vv["sq16"],
+              vv["uq"], st.Q0, idx)
+    assert torch.equal(before, gpu.store)
+
+
+def test_flush_degenerate_heads():
+    """Fully decayed head (P below the 1e-20 floor), an exactly rank-2 state and an all-zero state stay finite."""
+    NS, HV, H, L, R = 4, 2, 2, 16, 4
+    cpu = CpuSide(NS, HV, H, K, V, L, R)
+    g = torch.Generator().manual_seed(3)
+    cpu.ssm.copy_(random_states(NS, HV, V, K, 4))
+    cpu.ssm[2] = torch.randn(HV, V, 2, generator=g) @ torch.randn(HV, 2, K, generator=g)
+    cpu.ssm[3] = 0.0
+    idx = torch.tensor([1, 2, 3], dtype=torch.int32)
+    cpu.quantize(idx)
+    run_window(cpu, idx, H, HV, L, 8, False)
+    cpu.bufs.Pbuf[1] = 1e-30
+    cpu.bufs.Ubuf[3] = 0
+    gpu = GpuSide(cpu)
+    check_flush(cpu, gpu, idx, [1, 2, 3], "degenerate flush", code_tol=5e-2, code_frac=0.01)
+    s4, v, b = gpu.views_cpu()
+    for k in ("Sk", "Sv", "uq"):
+        assert torch.isfinite(v[k][[1, 2, 3]].float()).all(), k
+
+
+# ---------------------------------------------------------------------------------------------------------------------
+# whole path
+# ---------------------------------------------------------------------------------------------------------------------
+@pytest.mark.parametrize("kda,L,R,steps", [(False, 64, 4, 140), (True, 32, 8, 70)])
+def test_decode_free_running(kda, L, R, steps):
+    """decode() (step + flush) for several windows without re-synchronising: outputs track the oracle and the
+    unquantised fp32 recurrence (the reference's accuracy claim)."""
+    NS, HV, H, N = 4, 4, 2, 3
+    cpu, gpu = make_pair(NS, HV, H, L, R, kda=kda, seed=6)
+    src = random_states(NS, HV, V, K, 6)
+    idx = torch.tensor([2, 3, 1], dtype=torch.int32)
+    S = src[idx.long()].clone()
+    mixed, a, b_, A_log, dtb = step_inputs(N, H, HV, steps, 17, kda)
+    o_c = torch.zeros(N, HV, V, dtype=torch.bfloat16)
+    o_g = torch.zeros(N, HV, V, dtype=torch.bfloat16, device="cuda")
+    A_g, d_g, i_g = A_log.cuda(), dtb.cuda(), idx.cuda()
+    worst_oracle, worst_fp32 = 0.0, 0.0
+    for t in range(steps):
+        cpu.decode(mixed[t], a[t], b_[t], A_log, dtb, idx, o_c)
+        gpu.st.decode(gpu.ssm, mixed[t].cuda(), a[t].cuda(), b_[t].cuda(), A_g, d_g, i_g, o_g)
+        m = mixed[t].float()
+        q = m[:, :H * K].view(N, H, K).repeat_interleave(HV // H, 1)
+        k = m[:, H * K:2 * H * K].view(N, H, K).repeat_interleave(HV // H, 1)
+        vv = m[:, 2 * H * K:].view(N, HV, V)
+        beta = torch.sigmoid(b_[t].float()).bfloat16().float()
+        alpha = torch.exp(-torch.nn.functional.softplus(a[t].float()))
+        ref = (O.fp32_kda_recurrence if kda else O.fp32_gdn_recurrence)(S, q, k, vv, alpha, beta)
+        scale = float(ref.abs().max())
+        worst_oracle = max(worst_oracle, float((o_g.cpu().float() - o_c.float()).abs().max()) / scale)
+        worst_fp32 = max(worst_fp32, float((o_g.cpu().float() - ref).abs().max()) / scale)
+    assert torch.equal(gpu.st.hcnt.cpu(), cpu.bufs.hcnt)
+    assert worst_oracle < 2e-2, worst_oracle
+    assert worst_fp32 < 3e-2, worst_fp32
+    full = gpu.full_state(idx)
+    assert float((full - S).abs().max() / S.abs().max()) < 3e-2
+
+
+def test_sharded_equals_unsharded():
+    """Sequences split over two state objects (as over two GPUs) give bit-identical results to one object."""
+    NS, HV, H, L, R, N = 9, 4, 2, 16, 4, 8
+    cpu, gpu_all = make_pair(NS, HV, H, L, R, seed=5)
+    gpu_a, gpu_b = GpuSide(cpu), GpuSide(cpu)
+    idx = torch.arange(1, N + 1, dtype=torch.int32)
+    mixed, a, b_, A_log, dtb = step_inputs(N, H, HV, 20, 3, False)
+    o_all = torch.zeros(N, HV, V, dtype=torch.bfloat16, device="cuda")
+    o_a = torch.zeros(N // 2, HV, V, dtype=torch.bfloat16, device="cuda")
+    o_b = torch.zeros(N // 2, HV, V, dtype=torch.bfloat16, device="cuda")
+    for t in range(20):
+        gpu_all.st.decode(gpu_all.ssm, mixed[t].cuda(), a[t].cuda(), b_[t].cuda(), A_log.cuda(), dtb.cuda(), idx.cuda(), o_all)
+        gpu_a.st.decode(gpu_a.ssm, mixed[t][:4].cuda(), a[t][:4].cuda(), b_[t][:4].cuda(), A_log.cuda(), dtb.cuda(), idx[:4].cuda(), o_a)
+        gpu_b.st.decode(gpu_b.ssm, mixed[t][4:].cuda(), a[t][4:].cuda(), b_[t][4:].cuda(), A_log.cuda(), dtb.cuda(), idx[4:].cuda(), o_b)
+        assert torch.equal(o_all[:4], o_a) and torch.equal(o_all[4:], o_b)
+    assert torch.equal(gpu_all.ssm[1:5], gpu_a.ssm[1:5]) and torch.equal(gpu_all.ssm[5:9], gpu_b.ssm[5:9])
+
+
+def test_cpu_tensor_is_refused():
+    from leapquant_b200.state import LeapQuantState
+    with pytest.raises(RuntimeError):
+        LeapQuantState(torch.zeros(2, 2, V, K), 2)
+
+
+def test_device_status_clean():
+    from leapquant_b200 import _lib
+    torch.cuda.synchronize()
+    assert _lib.device_status() == 0

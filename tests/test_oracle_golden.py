@@ -1,0 +1,226 @@
+"""CPU tests: the oracle against the fixtures generated from the reference's own Python code, and against itself."""
+import json
+import os
+
+import numpy as np
+import pytest
+import torch
+
+from oracle import lq_oracle as O
+
+GOLD = os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden")
+
+
+def _bf16(a):
+    return torch.from_numpy(a).view(torch.bfloat16)
+
+
+def _f16(a):
+    return torch.from_numpy(a).view(torch.float16)
+
+
+def _mk(NS, HV, V, K, off, pad):
+    SS = HV * V * K + pad
+    store = torch.zeros(off + NS * SS)
+    return store[off:off + NS * SS].view(NS, SS)[:, :HV * V * K].view(NS, HV, V, K)
+
+
+@pytest.mark.parametrize("which", ["oracle", "product"])
+def test_layout_matches_reference(which):
+    """state_views: dtype, shape, stride and storage offset of all seven views (reference leapquant/state.py:29-40)."""
+    if which == "oracle":
+        fn = O.state_views
+    else:
+        from leapquant_b200.state import state_views as fn
+    cases = json.load(open(os.path.join(GOLD, "layout.json")))
+    assert len(cases) >= 5
+    for c in cases:
+        ssm = _mk(c["NS"], c["HV"], c["V"], c["K"], c["off"], c["pad"])
+        views = fn(ssm, c["R"])
+        assert set(views) == set(c["views"])
+        for k, g in c["views"].items():
+            t = views[k]
+            assert str(t.dtype) == g["dtype"] and list(t.shape) == g["shape"], k
+            assert list(t.stride()) == g["stride"] and t.storage_offset() == g["offset"], k
+            assert t.untyped_storage().data_ptr() == ssm.untyped_storage().data_ptr()
+
+
+def test_checkpoint_bytes():
+    assert O.checkpoint_bytes(128, 128, 4) == 19456 and O.checkpoint_bytes(128, 128, 8) == 21504
+
+
+def test_kda_rebuild_matches_reference():
+    """oracle.kda_rebuild == LeapQuantState._kda_rebuild of the reference on the same seeded tensors."""
+    z = np.load(os.path.join(GOLD, "kda_rebuild.npz"))
+    NS, HV, V, K, L, R = (int(x) for x in z["dims"])
+    ssm = torch.from_numpy(z["ssm"]).clone()
+    v = O.state_views(ssm, R)
+    S = O.kda_rebuild(v["Sq"], v["Sk"], v["Sv"], v["uq"], _bf16(z["Kbuf"]), _bf16(z["Ubuf"]), torch.from_numpy(z["Wbuf"]),
+                      torch.from_numpy(z["Pbuf"]), _f16(z["Gbuf"]), torch.from_numpy(z["hcnt"]), torch.from_numpy(z["sl"]))
+    ref = torch.from_numpy(z["S"])
+    assert torch.allclose(S, ref, rtol=1e-5, atol=1e-6), float((S - ref).abs().max())
+    # the step/flush form of the per-entry decay agrees with the cumprod form of the reference
+    sl = torch.from_numpy(z["sl"])
+    E = _f16(z["Gbuf"])[sl].float()
+    h = torch.from_numpy(z["hcnt"])[sl].long()
+    D = O.kda_decay(E, h)
+    live = torch.arange(L)[None, None, :, None] < h[..., None, None]
+    E1 = torch.where(live, E, torch.ones_like(E))
+    Dref = torch.flip(torch.cumprod(torch.flip(E1, [2]), 2), [2]) / E1
+    assert torch.allclose(D[live.expand_as(D)], Dref[live.expand_as(D)], rtol=1e-5)
+
+
+def test_kda_checkpoint_matches_reference():
+    """oracle.kda_checkpoint == LeapQuantState._kda_checkpoint of the reference (given the same rank-R factors)."""
+    z = np.load(os.path.join(GOLD, "kda_checkpoint.npz"))
+    NS, HV, V, K, L, R = (int(x) for x in z["dims"])
+    ssm = torch.from_numpy(z["src"]).clone()
+    v = O.state_views(ssm, R)
+    W, P = torch.ones(NS, HV, L), torch.ones(NS, HV, K)
+    G, hc = torch.zeros(NS, HV, L, K).half(), torch.full((NS, HV), 3, dtype=torch.int32)
+    O.kda_checkpoint(ssm, v["Sq"], v["Sk"], v["Sv"], v["uq"], W, P, G, hc, torch.from_numpy(z["sl"]), R)
+    ref = torch.from_numpy(z["out"])
+    vr = O.state_views(ref, R)
+    sl = torch.from_numpy(z["sl"])
+    assert torch.equal(v["Sq"][sl], vr["Sq"][sl])
+    assert torch.equal(v["Sk"][sl], vr["Sk"][sl]) and torch.equal(v["Sv"][sl], vr["Sv"][sl])
+    assert torch.equal(v["uq"][sl].view(torch.int16), vr["uq"][sl].view(torch.int16))
+    assert torch.equal(W, torch.from_numpy(z["Wbuf"])) and torch.equal(P, torch.from_numpy(z["Pbuf"]))
+    assert torch.equal(G.view(torch.int16), _f16(z["Gbuf"]).view(torch.int16)) and torch.equal(hc, torch.from_numpy(z["hcnt"]))
+
+
+# ---------------------------------------------------------------------------------------------------------------------
+# oracle self-consistency
+# ---------------------------------------------------------------------------------------------------------------------
+def _setup(kda, L, R, NS=4, HV=4, H=2, seed=0, scale=0.1):
+    K = V = 128
+    g = torch.Generator().manual_seed(seed)
+    ssm = torch.randn(NS, HV, V, K, generator=g) * scale
+    src = ssm.clone()
+    v = O.state_views(ssm, R)
+    b = O.Buffers(NS, HV, K, V, L, R, kda)
+    return ssm, src, v, b
+
+
+@pytest.mark.parametrize("R", [4, 8])
+def test_quantize_dequantize_round_trip(R):
+    ssm, src, v, b = _setup(False, 16, R)
+    idx = torch.tensor([1, 0, 3], dtype=torch.int32)
+    O.quantize(ssm, v["Sq"], v["Sk"], v["Sv"], v["uq"], b.Wbuf, b.Pbuf, b.hcnt, b.Q0, idx)
+    assert int(v["Sq"][[1, 3]].abs().max()) == 127              # every row reaches full scale
+    O.dequantize(ssm, v["Sq"], v["Sk"], v["Sv"], b.Kbuf, b.Ubuf, b.Wbuf, b.Pbuf, b.hcnt, v["uq"], idx)
+    err = (ssm[[1, 3]] - src[[1, 3]]).abs().max() / src.abs().max()
+    assert err < 8e-3, float(err)
+    assert torch.equal(ssm[2], src[2]) and torch.equal(ssm[0], src[0])   # untouched slots
+
+
+@pytest.mark.parametrize("kda,L,R", [(False, 8, 4), (False, 16, 8), (True, 8, 4), (True, 4, 8)])
+def test_decode_tracks_fp32_recurrence(kda, L, R):
+    """Quantized decode (step + flush) stays close to the unquantised recurrence over several windows."""
+    NS, HV, H, K, V, steps = 3, 4, 2, 128, 128, 3 * L + 2
+    ssm, src, v, b = _setup(kda, L, R, NS=NS, HV=HV, H=H, seed=3)
+    idx = torch.tensor([2, 1], dtype=torch.int32)
+    if kda:
+        O.kda_checkpoint(ssm, v["Sq"], v["Sk"], v["Sv"], v["uq"], b.Wbuf, b.Pbuf, b.Gbuf, b.hcnt, idx.long(), R)
+    else:
+        O.quantize(ssm, v["Sq"], v["Sk"], v["Sv"], v["uq"], b.Wbuf, b.Pbuf, b.hcnt, b.Q0, idx)
+    mixed, a, bb, A_log, dtb = O.synth_inputs(2, H, HV, K, V, steps, 11, kda=kda)
+    S = src[idx.long()].clone()
+    o = torch.zeros(2, HV, V, dtype=torch.bfloat16)
+    nflush = 0
+    worst = 0.0
+    for t in range(steps):
+        if kda:
+            O.kda_step(v["Sq"], v["Sk"], v["Sv"], b.Kbuf, b.Ubuf, b.Wbuf, b.Pbuf, b.Gbuf, b.hcnt, mixed[t], a[t], bb[t],
+                       A_log, dtb, v["uq"], idx, o, H)
+        else:
+            O.gdn_step(v["Sq"], v["Sk"], v["Sv"], b.Kbuf, b.Ubuf, b.Wbuf, b.Pbuf, b.hcnt, mixed[t], a[t], bb[t], A_log, dtb,
+                       v["uq"], idx, o, H)
+        nflush += O.flush(v["Sq"], v["Sk"], v["Sv"], b.Kbuf, b.Ubuf, b.Wbuf, b.Pbuf, b.Gbuf if kda else None, b.hcnt,
+                          v["uq"], b.Q0, idx, kda=kda)
+        m = mixed[t].float()
+        q = m[:, :H * K].view(2, H, K).repeat_interleave(HV // H, 1)
+        k = m[:, H * K:2 * H * K].view(2, H, K).repeat_interleave(HV // H, 1)
+        vv = m[:, 2 * H * K:].view(2, HV, V)
+        beta = torch.sigmoid(bb[t].float()).bfloat16().float()
+        if kda:
+            alpha = torch.exp(-torch.nn.functional.softplus(a[t].float()))
+            ref = O.fp32_kda_recurrence(S, q, k, vv, alpha, beta)
+        else:
+            alpha = torch.exp(-torch.nn.functional.softplus(a[t].float()))
+            ref = O.fp32_gdn_recurrence(S, q, k, vv, alpha, beta)
+        worst = max(worst, float((o.float() - ref).abs().max() / ref.abs().max()))
+    assert nflush == 3 * 2 * HV
+    assert worst < 3e-2, worst
+    full = O.full_state(v["Sq"], v["Sk"], v["Sv"], v["uq"], b.Kbuf, b.Ubuf, b.Wbuf, b.Pbuf, b.Gbuf, b.hcnt, idx, kda)
+    assert float((full - S).abs().max() / S.abs().max()) < 3e-2
+
+
+def test_null_rows_touch_nothing():
+    ssm, src, v, b = _setup(False, 8, 4)
+    idx = torch.tensor([0, -1], dtype=torch.int32)
+    before = (ssm.clone(), b.clone())
+    mixed, a, bb, A_log, dtb = O.synth_inputs(2, 2, 4, 128, 128, 1, 5)
+    o = torch.ones(2, 4, 128, dtype=torch.bfloat16)
+    O.gdn_step(v["Sq"], v["Sk"], v["Sv"], b.Kbuf, b.Ubuf, b.Wbuf, b.Pbuf, b.hcnt, mixed[0], a[0], bb[0], A_log, dtb,
+               v["uq"], idx, o, 2)
+    assert float(o.float().abs().max()) == 0.0
+    assert torch.equal(ssm, before[0]) and torch.equal(b.hcnt, before[1].hcnt) and torch.equal(b.Kbuf, before[1].Kbuf)
+
+
+def test_cholesky_qr_orthonormal_and_floors():
+    g = torch.Generator().manual_seed(0)
+    X = torch.randn(3, 128, 4, generator=g)
+    Q = O.cholesky_qr(O.cholesky_qr(X, False), False)
+    G = torch.einsum("dvr,dvs->drs", Q, Q)
+    assert torch.allclose(G, torch.eye(4).expand(3, 4, 4), atol=1e-5)
+    X[:, :, 3] = X[:, :, 0] * 2.0                                   # dependent column: floored (R <= 4), dropped (R = 8)
+    Qf = O.cholesky_qr(X, False)
+    assert torch.isfinite(Qf).all()
+    X8 = torch.randn(2, 128, 8, generator=g)
+    X8[:, :, 5] = X8[:, :, 1]
+    Qd = O.cholesky_qr(X8, True)
+    assert float(Qd[:, :, 5].abs().max()) == 0.0 and torch.isfinite(Qd).all()
+
+
+def test_quant_stage_codes_are_rne():
+    g = torch.Generator().manual_seed(1)
+    E = torch.randn(2, 128, 128, generator=g)
+    sk, rsk = O.column_scales(E)
+    assert torch.equal(rsk, 1.0 / sk)
+    sv, code = O.quant_stage(E, rsk)
+    x = E * rsk[:, None, :]
+    want = torch.round(x.double() * (127.0 / sv.double())[:, :, None])
+    assert int((code.double() - want).abs().max()) <= 1
+    assert float(((code.double() - want) != 0).double().mean()) < 1e-4
+    assert int(code.abs().max()) == 127
+
+
+def test_fp32_recurrences_match_fla():
+    """Second opinion for the unquantised recurrences: flash-linear-attention's naive torch implementations."""
+    fla = pytest.importorskip("fla")
+    try:
+        from fla.ops.gated_delta_rule.naive import naive_recurrent_gated_delta_rule
+    except Exception:
+        pytest.skip("fla naive gated delta rule not importable")
+    g = torch.Generator().manual_seed(2)
+    B, T, H, K, V = 1, 6, 2, 16, 16
+    q = torch.randn(B, T, H, K, generator=g)
+    k = torch.randn(B, T, H, K, generator=g)
+    v = torch.randn(B, T, H, V, generator=g)
+    beta = torch.sigmoid(torch.randn(B, T, H, generator=g))
+    gl = -torch.nn.functional.softplus(torch.randn(B, T, H, generator=g))
+    qn = q / (q * q).sum(-1, keepdim=True).add(1e-6).sqrt()
+    kn = k / (k * k).sum(-1, keepdim=True).add(1e-6).sqrt()
+    try:
+        ref, _ = naive_recurrent_gated_delta_rule(qn, kn, v, beta, gl, scale=K ** -0.5, output_final_state=True)
+    except Exception as e:                                        # signature drift between fla versions
+        pytest.skip(f"fla naive signature differs: {e}")
+    S = torch.zeros(B, H, V, K)
+    outs = []
+    for t in range(T):
+        outs.append(O.fp32_gdn_recurrence(S, q[:, t], k[:, t], v[:, t], torch.exp(gl[:, t]), beta[:, t]))
+    mine = torch.stack(outs, 1)
+    if ref.shape != mine.shape:
+        pytest.skip("fla naive layout differs")
+    assert torch.allclose(mine, ref.float(), rtol=1e-4, atol=1e-5), float((mine - ref).abs().max())
