@@ -65,7 +65,7 @@ class ClockSampler(threading.Thread):
 
     def __init__(self, index):
         super().__init__(daemon=True)
-        self.index, self.samples, self.reasons, self.max_mhz, self._stop = index, [], set(), None, threading.Event()
+        self.index, self.samples, self.reasons, self.max_mhz, self._halt = index, [], set(), None, threading.Event()
         try:
             import pynvml
             pynvml.nvmlInit()
@@ -84,7 +84,7 @@ class ClockSampler(threading.Thread):
                  "sw_thermal_slowdown": getattr(nv, "nvmlClocksEventReasonSwThermalSlowdown", 0x20),
                  "sw_power_cap": getattr(nv, "nvmlClocksEventReasonSwPowerCap", 0x4)}
         get = getattr(nv, "nvmlDeviceGetCurrentClocksEventReasons", None) or nv.nvmlDeviceGetCurrentClocksThrottleReasons
-        while not self._stop.is_set():
+        while not self._halt.is_set():
             try:
                 self.samples.append(nv.nvmlDeviceGetClockInfo(self.h, nv.NVML_CLOCK_SM))
                 mask = get(self.h)
@@ -93,10 +93,10 @@ class ClockSampler(threading.Thread):
                         self.reasons.add(k)
             except Exception:
                 pass
-            self._stop.wait(0.1)
+            self._halt.wait(0.1)
 
     def finish(self):
-        self._stop.set()
+        self._halt.set()
         self.join(timeout=2)
         return {"sm_mhz": statistics.median(self.samples) if self.samples else None, "sm_max_mhz": self.max_mhz,
                 "reasons": sorted(self.reasons)}
@@ -380,7 +380,7 @@ def run_b200(args, wl):
                 "e2e": {"value": e2e_value, "unit": "head-steps/s", "h2d_bytes_per_step": layer.h2d_bytes(),
                         "d2h_bytes_per_step": layer.d2h_bytes(), "steps": e2e_steps},
                 "gpu_launches": 2 * done,
-                "roofline": {"bound": "hbm", "kernel": "step_direct_kernel", "achieved": achieved, "peak": peak,
+                "roofline": {"bound": "hbm", "kernel": "step_pipelined_kernel", "achieved": achieved, "peak": peak,
                              "unit": "GB/s", "frac": achieved / peak, "frac_of_8tbs": achieved / 8000.0,
                              "traffic": (traffic * B * HV) if traffic else None, "alg_bytes_per_launch": alg_launch,
                              "ms_per_launch": step_ms, "peak_source": "MEASURED_PEAKS.json" if peaks else "fallback"},

@@ -59,6 +59,10 @@ int lq_last_cuda_error(void);
  * the device: debugging / tests only.  No reference counterpart. */
 int lq_device_status(int* status);
 
+/* Tuning / debugging switch, process-wide; no reference counterpart.  "step_impl": 0 = persistent CTAs fed by bulk
+ * asynchronous copies (default), 1 = one CTA per (row, head) with plain loads.  Both run the same arithmetic. */
+int lq_set_option(const char* name, int32_t value);
+
 /* GDN decode step.  Replaces the kernel built by make_gdn_step (reference leapquant/kernels.py:27-692, launch
  * signature :80-89).  One token per row n < N: reads the INT8 checkpoint and the h live window entries of
  * (idx[n], hv), writes o[n,hv,:] (bf16) and appends (k_hat, u, w = 1) to the window; hcnt += 1.

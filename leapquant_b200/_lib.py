@@ -11,7 +11,7 @@ import torch
 _HERE = os.path.dirname(os.path.abspath(__file__))
 LIB_PATH = os.path.join(_HERE, "libleapquant_b200.so")
 
-EXPORTS = ("lq_version", "lq_strerror", "lq_last_cuda_error", "lq_device_status", "lq_gdn_step", "lq_kda_step",
+EXPORTS = ("lq_version", "lq_strerror", "lq_last_cuda_error", "lq_device_status", "lq_set_option", "lq_gdn_step", "lq_kda_step",
            "lq_flush", "lq_quantize", "lq_dequant", "lq_lowrank")
 
 _P = ctypes.c_void_p
@@ -45,6 +45,8 @@ def lib():
         L.lq_strerror.argtypes = [_I]
         L.lq_last_cuda_error.restype = _I
         L.lq_device_status.argtypes = [ctypes.POINTER(_I)]
+        L.lq_set_option.argtypes = [ctypes.c_char_p, _I]
+        L.lq_set_option.restype = _I
         L.lq_gdn_step.argtypes = [D, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _I, _F, _P]
         L.lq_kda_step.argtypes = [D, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _I, _F, _F, _P]
         L.lq_flush.argtypes = [D, _P, _P, _P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _P]
@@ -96,6 +98,11 @@ class on_device:
     def __exit__(self, *exc):
         if self.prev is not None:
             torch.cuda.set_device(self.prev)
+
+
+def set_option(name, value):
+    """Process-wide tuning / debugging switch of the library (see lq_set_option in the header)."""
+    check(lib().lq_set_option(name.encode(), int(value)), f"lq_set_option({name})")
 
 
 def device_status():

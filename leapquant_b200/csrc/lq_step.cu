@@ -10,6 +10,8 @@
 // Thread mapping of the matvec: eight lanes share a row of the 128 x 128 INT8 tile; lane l8 = lane & 7 owns the
 // 16 columns 16 l8 .. 16 l8 + 15, so a warp-wide 16-byte load covers four whole 128-byte rows and the operand
 // vectors k_hat * Sk / 127 and q_hat * Sk / 127 for those columns stay in registers for the whole tile.
+#include <string.h>
+
 #include "lq_common.cuh"
 
 namespace lq {
@@ -18,7 +20,7 @@ constexpr int GT = 128;                   // threads of one consumer group
 
 // ---- stage layout (bytes); the checkpoint part mirrors the packed slot so that it is ONE contiguous copy ----
 struct StageLayout {
-    int kb, ub, w, q, k, v, gb, pb, a, dtb, bytes;
+    int kb, ub, w, q, k, v, gb, pb, a, dtb, sc, bytes;
 };
 __host__ __device__ inline StageLayout stage_layout(int L, int R, bool kda) {
     StageLayout s;
@@ -36,6 +38,7 @@ __host__ __device__ inline StageLayout stage_layout(int L, int R, bool kda) {
         s.a = o; o += 256;
         s.dtb = o; o += 512;
     }
+    s.sc = o; o += 32;                      // ProgScalars written by the producer warp (pipelined driver)
     s.bytes = (o + 127) & ~127;
     return s;
 }
@@ -412,13 +415,229 @@ __global__ void __launch_bounds__(GT, 4) step_direct_kernel(StepParams P) {
     step_body<R, KDA>(P, sc, st, lay, gs, t, 1);
 }
 
+// ------------------------------------------------------------------------------------------------------------------
+// driver 2: persistent CTAs, producer warp + bulk asynchronous copies into a ring of stages
+// ------------------------------------------------------------------------------------------------------------------
+constexpr uint32_t WAIT_LIMIT = 1u << 22;      // bounded spin: ~seconds at worst, then the kernel records a status and leaves
+constexpr int ST_PRODUCER_TIMEOUT = 1, ST_CONSUMER_TIMEOUT = 2;
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return uint32_t(__cvta_generic_to_shared(p)); }
+__device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive_expect_tx(uint64_t* bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n"
+        ".reg .pred p;\n"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n"
+        "selp.u32 %0, 1, 0, p;\n"
+        "}\n"
+        : "=r"(ok)
+        : "r"(smem_u32(bar)), "r"(parity), "r"(2000u)
+        : "memory");
+    return ok != 0;
+}
+// waits for the phase with the given parity; gives up after WAIT_LIMIT polls
+__device__ __forceinline__ bool mbar_wait_bounded(uint64_t* bar, uint32_t parity) {
+    for (uint32_t it = 0; it < WAIT_LIMIT; ++it)
+        if (mbar_try_wait(bar, parity)) return true;
+    return false;
+}
+// bulk asynchronous copy global -> this CTA's shared memory, completion counted in bytes on `bar`
+__device__ __forceinline__ void bulk_g2s(void* dst, const void* src, uint32_t bytes, uint64_t* bar) {
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(smem_u32(dst)),
+                 "l"(src), "r"(bytes), "r"(smem_u32(bar))
+                 : "memory");
+}
+__device__ __forceinline__ void fence_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
+// group-wide AND of a predicate over a named barrier (also a barrier)
+__device__ __forceinline__ bool group_all(int bar, int nthreads, bool pred) {
+    uint32_t r;
+    asm volatile(
+        "{\n"
+        ".reg .pred p, q;\n"
+        "setp.ne.u32 q, %3, 0;\n"
+        "barrier.cta.red.and.pred p, %1, %2, q;\n"
+        "selp.u32 %0, 1, 0, p;\n"
+        "}\n"
+        : "=r"(r)
+        : "r"(bar), "r"(nthreads), "r"(uint32_t(pred))
+        : "memory");
+    return r != 0;
+}
+
+template <int R, bool KDA, int NG>
+__global__ void __launch_bounds__(32 + NG * GT, 1) step_pipelined_kernel(StepParams P, int nstages) {
+    extern __shared__ __align__(128) char stage_smem[];
+    const StageLayout lay = stage_layout(P.d.L, R, KDA);
+    char* scratch0 = stage_smem + size_t(nstages) * lay.bytes;
+    uint64_t* full = reinterpret_cast<uint64_t*>(scratch0 + NG * SCRATCH_BYTES);
+    uint64_t* empty = full + nstages;
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int HV = P.d.HV, H = P.d.H, L = P.d.L;
+    const int nprog = P.N * HV;
+    const int grid = gridDim.x, bid = blockIdx.x;
+    const int nit = (nprog - bid + grid - 1) / grid;
+
+    if (tid == 0) {
+        for (int s = 0; s < nstages; ++s) {
+            mbar_init(full + s, 1);
+            mbar_init(empty + s, GT);
+        }
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        fence_async_smem();
+    }
+    __syncthreads();
+
+    if (warp == 0) {
+        // ================= producer: scalars of 32 programs per batch, then one stage fill per program =================
+        const int MIX = 2 * H * KD + HV * VD;
+        const int gqa = HV / H;
+        ProgScalars cur, nxt;
+        auto fetch = [&](int i) {
+            ProgScalars r;
+            r.slot = 0; r.h = 0; r.n = 0; r.hv = 0; r.alpha = 1.f; r.beta = 0.f; r.pold = 1.f; r.ea = 1.f;
+            if (i < nit) {
+                const int p = bid + i * grid;
+                const int n = p / HV;
+                r = load_scalars(P, n, p - n * HV, KDA);
+            }
+            return r;
+        };
+        nxt = fetch(lane);
+        bool ok = true;
+        for (int base = 0; base < nit && ok; base += 32) {
+            cur = nxt;
+            nxt = fetch(base + 32 + lane);
+            const int cnt = min(32, nit - base);
+            for (int j = 0; j < cnt; ++j) {
+                const int i = base + j;
+                const int s = i % nstages;
+                const uint32_t u = uint32_t(i / nstages);
+                ProgScalars sc;
+                sc.slot = __shfl_sync(0xffffffffu, cur.slot, j);
+                sc.h = __shfl_sync(0xffffffffu, cur.h, j);
+                sc.n = __shfl_sync(0xffffffffu, cur.n, j);
+                sc.hv = __shfl_sync(0xffffffffu, cur.hv, j);
+                sc.alpha = __shfl_sync(0xffffffffu, cur.alpha, j);
+                sc.beta = __shfl_sync(0xffffffffu, cur.beta, j);
+                sc.pold = __shfl_sync(0xffffffffu, cur.pold, j);
+                sc.ea = __shfl_sync(0xffffffffu, cur.ea, j);
+                int good = 1;
+                if (lane == 0) good = mbar_wait_bounded(empty + s, (u & 1u) ^ 1u) ? 1 : 0;
+                good = __shfl_sync(0xffffffffu, good, 0);
+                if (!good) {
+                    if (lane == 0) atomicOr(&g_status, ST_PRODUCER_TIMEOUT);
+                    ok = false;
+                    break;
+                }
+                char* st = stage_smem + size_t(s) * lay.bytes;
+                const bool live = sc.slot > 0 && sc.h >= 0 && sc.h < L;
+                if (lane == 0) {
+                    *reinterpret_cast<ProgScalars*>(st + lay.sc) = sc;
+                    if (live) {
+                        uint32_t bytes = ck_bytes(R) + 2u * uint32_t(sc.h) * 256u + uint32_t(L) * 4u + 3u * 256u;
+                        if (KDA) bytes += uint32_t(sc.h) * 256u + 512u + 256u + 512u;
+                        mbar_arrive_expect_tx(full + s, bytes);
+                    } else {
+                        mbar_arrive(full + s);
+                    }
+                }
+                __syncwarp();
+                if (live) {
+                    const int64_t sh = int64_t(sc.slot) * HV + sc.hv;
+                    const char* mrow = reinterpret_cast<const char*>(P.mixed + int64_t(sc.n) * MIX);
+                    const int hk = sc.hv / gqa;
+                    const uint32_t hb = uint32_t(sc.h) * 256u;
+                    switch (lane) {
+                        case 0: bulk_g2s(st, head_base(P.ssm, P.d.SS, sc.slot, sc.hv), ck_bytes(R), full + s); break;
+                        case 1: if (hb) bulk_g2s(st + lay.kb, P.Kbuf + sh * L * KD, hb, full + s); break;
+                        case 2: if (hb) bulk_g2s(st + lay.ub, P.Ubuf + sh * L * VD, hb, full + s); break;
+                        case 3: bulk_g2s(st + lay.w, P.Wbuf + sh * L, uint32_t(L) * 4u, full + s); break;
+                        case 4: bulk_g2s(st + lay.q, mrow + hk * 256, 256u, full + s); break;
+                        case 5: bulk_g2s(st + lay.k, mrow + (H + hk) * 256, 256u, full + s); break;
+                        case 6: bulk_g2s(st + lay.v, mrow + (2 * H + sc.hv) * 256, 256u, full + s); break;
+                        case 7: if (KDA && hb) bulk_g2s(st + lay.gb, P.Gbuf + sh * L * KD, hb, full + s); break;
+                        case 8: if (KDA) bulk_g2s(st + lay.pb, P.Pbuf + sh * KD, 512u, full + s); break;
+                        case 9: if (KDA) bulk_g2s(st + lay.a, P.a + (int64_t(sc.n) * HV + sc.hv) * KD, 256u, full + s); break;
+                        case 10: if (KDA) bulk_g2s(st + lay.dtb, P.dt_bias + int64_t(sc.hv) * KD, 512u, full + s); break;
+                        default: break;
+                    }
+                }
+            }
+        }
+        // Leave only after every stage this warp armed has been consumed (bounded): no copy of this CTA is then in flight.
+        if (lane == 0) {
+            const int last = ok ? nit : 0;
+            for (int s = 0; s < nstages && s < last; ++s) {
+                const int uses = (last - 1 - s) / nstages + 1;            // fills of stage s
+                if (!mbar_wait_bounded(empty + s, uint32_t(uses - 1) & 1u)) {
+                    atomicOr(&g_status, ST_PRODUCER_TIMEOUT);
+                    break;
+                }
+            }
+        }
+        return;
+    }
+
+    // ================= consumers: group g takes programs g, g + NG, ... =================
+    const int g = (warp - 1) >> 2;
+    const int t = tid - 32 - g * GT;
+    const int bar = 1 + g;
+    const GroupScratch gs = carve_scratch(scratch0 + g * SCRATCH_BYTES);
+    for (int i = g; i < nit; i += NG) {
+        const int s = i % nstages;
+        const uint32_t u = uint32_t(i / nstages);
+        const bool got = mbar_wait_bounded(full + s, u & 1u);
+        if (!group_all(bar, GT, got)) {                 // uniform decision: nobody enters the body unless all saw the data
+            if (t == 0) atomicOr(&g_status, ST_CONSUMER_TIMEOUT);
+            return;
+        }
+        char* st = stage_smem + size_t(s) * lay.bytes;
+        const ProgScalars sc = *reinterpret_cast<const ProgScalars*>(st + lay.sc);
+        if (sc.slot > 0 && sc.h >= 0 && sc.h < L) {
+            step_body<R, KDA>(P, sc, st, lay, gs, t, bar);
+        } else {
+            const int p = bid + i * grid;
+            if (t < 64) reinterpret_cast<uint32_t*>(P.o)[int64_t(p) * 64 + t] = 0u;
+        }
+        fence_async_smem();                              // generic-proxy accesses to the stage before the next bulk copy lands
+        mbar_arrive(empty + s);
+    }
+}
+
+// 0 = pipelined (default), 1 = direct
+static int g_step_impl = 0;
+
 template <int R, bool KDA>
 static int launch_step(const StepParams& P, cudaStream_t st) {
     const StageLayout lay = stage_layout(P.d.L, R, KDA);
-    const size_t smem = size_t(lay.bytes) + SCRATCH_BYTES;
-    int rc = ensure_smem((const void*)step_direct_kernel<R, KDA>, smem);
+    if (g_step_impl == 1) {
+        const size_t smem = size_t(lay.bytes) + SCRATCH_BYTES;
+        int rc = ensure_smem((const void*)step_direct_kernel<R, KDA>, smem);
+        if (rc) return rc;
+        step_direct_kernel<R, KDA><<<unsigned(P.N) * P.d.HV, GT, smem, st>>>(P);
+        return finish_launch();
+    }
+    constexpr int NG = 2;
+    const size_t budget = 227 * 1024;
+    const size_t fixed = size_t(NG) * SCRATCH_BYTES + 2 * 16 * sizeof(uint64_t);
+    int nstages = int((budget - fixed) / size_t(lay.bytes));
+    if (nstages > 16) nstages = 16;
+    if (nstages < 2) return LQ_ERR_UNSUPPORTED;
+    const size_t smem = size_t(nstages) * lay.bytes + size_t(NG) * SCRATCH_BYTES + 2 * size_t(nstages) * sizeof(uint64_t);
+    int rc = ensure_smem((const void*)step_pipelined_kernel<R, KDA, NG>, smem);
     if (rc) return rc;
-    step_direct_kernel<R, KDA><<<unsigned(P.N) * P.d.HV, GT, smem, st>>>(P);
+    const int nprog = P.N * P.d.HV;
+    const int grid = nprog < device_sm_count() ? nprog : device_sm_count();
+    step_pipelined_kernel<R, KDA, NG><<<grid, 32 + NG * GT, smem, st>>>(P, nstages);
     return finish_launch();
 }
 
@@ -449,6 +668,16 @@ static int step_common(const lq_dims* d, void* ssm, void* Kbuf, void* Ubuf, floa
 }
 
 }  // namespace lq
+
+extern "C" int lq_set_option(const char* name, int32_t value) {
+    if (!name) return LQ_ERR_NULL;
+    if (strcmp(name, "step_impl") == 0) {
+        if (value != 0 && value != 1) return LQ_ERR_RANGE;
+        lq::g_step_impl = value;
+        return LQ_OK;
+    }
+    return LQ_ERR_UNSUPPORTED;
+}
 
 extern "C" int lq_gdn_step(const lq_dims* d, void* ssm, void* Kbuf, void* Ubuf, float* Wbuf, float* Pbuf, int32_t* hcnt,
                            const void* mixed, const void* a, const void* b, const float* A_log, const float* dt_bias,

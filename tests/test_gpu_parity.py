@@ -23,8 +23,24 @@ def make_pair(NS, HV, H, L, R, kda=False, glb=0.0, seed=0, scale=0.1, slot_pad=0
     return cpu, GpuSide(cpu)
 
 
-def step_inputs(N, H, HV, steps, seed, kda):
-    return O.synth_inputs(N, H, HV, K, V, steps, seed, kda=kda)
+def step_inputs(N, H, HV, steps, seed, kda, gate_shift=0.0):
+    """BASELINE's seeded distributions; gate_shift > 0 moves the raw gate down so that the per-step decay is mild
+    (alpha close to 1) and the state keeps a well-conditioned spectrum over a whole window."""
+    mixed, a, b, A_log, dtb = O.synth_inputs(N, H, HV, K, V, steps, seed, kda=kda)
+    if gate_shift:
+        a = (a.float() - gate_shift).to(a.dtype)
+    return mixed, a, b, A_log, dtb
+
+
+@pytest.fixture(params=[0, 1], ids=["pipelined", "direct"])
+def step_impl(request):
+    """Runs a test once per driver of the step kernel (persistent bulk-copy pipeline / one CTA per program)."""
+    from leapquant_b200 import _lib
+    _lib.set_option("step_impl", request.param)
+    yield request.param
+    torch.cuda.synchronize()
+    assert _lib.device_status() == 0, "a kernel gave up a bounded wait"
+    _lib.set_option("step_impl", 0)
 
 
 def compare_window(cpu, gpu, slots, what):
@@ -45,7 +61,8 @@ def compare_window(cpu, gpu, slots, what):
 # quantize / dequantize / lowrank
 # ---------------------------------------------------------------------------------------------------------------------
 def near_boundary_only(code_gpu, x_scaled, tol=1e-3):
-    """Codes equal RNE(x_scaled) except +-1 where x_scaled is within tol of a half-integer."""
+    """Codes equal RNE(x_scaled) except +-1 where x_scaled is within tol (a number or a per-element tensor, in code
+    units) of a half-integer."""
     want = torch.round(x_scaled.double())
     diff = code_gpu.double() - want
     bad = diff != 0
@@ -53,8 +70,19 @@ def near_boundary_only(code_gpu, x_scaled, tol=1e-3):
         return 0
     assert int(diff.abs().max()) <= 1, "a code differs by more than one LSB"
     frac = (x_scaled.double()[bad] - torch.floor(x_scaled.double()[bad]) - 0.5).abs()
-    assert float(frac.max()) < tol, f"code differs away from a rounding boundary (distance {float(frac.max()):.2e})"
+    lim = tol[bad].double() if torch.is_tensor(tol) else torch.full_like(frac, tol)
+    over = frac > lim
+    assert not bool(over.any()), (f"{int(over.sum())} codes differ away from a rounding boundary "
+                                  f"(worst distance {float((frac - lim).max() + lim[(frac - lim).argmax()]):.2e})")
     return int(bad.sum())
+
+
+def residual_noise(S_abs, uq, sk):
+    """Bound, per element and in units of E / Sk, of the fp32 evaluation noise of E = S - sum_r Q_r U_r^T: a few ulps of
+    the magnitudes that cancel."""
+    Qa, Ua = uq[..., K:].abs(), uq[..., :K].abs()
+    mags = S_abs + torch.einsum("...rv,...rc->...vc", Qa, Ua)
+    return 6e-7 * mags / sk[..., None, :]
 
 
 @pytest.mark.parametrize("R", [4, 8])
@@ -91,9 +119,10 @@ def test_quantize_gdn(R):
     sk_c = torch.clamp(torch.sqrt(E.abs().sum(-2) / V), min=1e-12)
     assert_close(sk_g, sk_c, 1e-4, 0.0, "Sk given the stored factors")
     sv_c = torch.clamp((E / sk_g[..., None, :]).abs().amax(-1), min=1e-12)
-    assert_close(sv_g, sv_c, 1e-4, 0.0, "Sv given the stored factors")
+    noise = residual_noise(src[sl].abs(), uq_g, sk_g)                      # in units of E / Sk
+    assert bool(((sv_g - sv_c).abs() <= 1e-5 * sv_c + noise.amax(-1)).all()), "Sv given the stored factors"
     x = E / (sk_g[..., None, :] * sv_g[..., :, None]) * 127.0
-    nb = near_boundary_only(v["Sq"][sl], x, tol=2e-2)
+    nb = near_boundary_only(v["Sq"][sl], x, tol=1e-3 + noise / sv_g[..., :, None] * 127.0)
     assert nb < 0.002 * x.numel()
     assert int(v["Sq"][sl].abs().max()) == 127
 
@@ -168,7 +197,7 @@ def test_kda_round_trip():
 # ---------------------------------------------------------------------------------------------------------------------
 @pytest.mark.parametrize("kda,glb,L,R,H,HV", [(False, 0.0, 16, 4, 2, 4), (False, 0.0, 64, 4, 1, 2), (False, 0.0, 32, 8, 2, 2),
                                               (True, 0.0, 16, 4, 2, 2), (True, -5.0, 32, 8, 2, 2)])
-def test_step_every_fill_level(kda, glb, L, R, H, HV):
+def test_step_every_fill_level(kda, glb, L, R, H, HV, step_impl):
     """From identical state, one step at every window fill h = 0 .. L-1; the device state is re-synchronised from the
     oracle after each step so that every step is compared from bit-identical inputs."""
     NS, N = 6, 4
@@ -201,6 +230,35 @@ def test_step_every_fill_level(kda, glb, L, R, H, HV):
     assert int(cpu.bufs.hcnt[3].min()) == L
 
 
+def test_step_many_programs_per_cta(step_impl):
+    """More programs than 32 per persistent CTA (the producer's scalar batches and the stage ring wrap several times),
+    ragged fill levels, null rows in between."""
+    NS, HV, H, L, R, N = 171, 32, 16, 16, 4, 170
+    cpu, gpu = make_pair(NS, HV, H, L, R, seed=8)
+    g = torch.Generator().manual_seed(0)
+    # ragged windows: give every (slot, head) its own number of live entries with plausible contents
+    h = torch.randint(0, L, (NS, HV), generator=g)
+    live = torch.arange(L)[None, None, :] < h[..., None]
+    cpu.bufs.hcnt.copy_(h.int())
+    cpu.bufs.Kbuf.copy_((torch.randn(NS, HV, L, K, generator=g) * 0.09).bfloat16())
+    cpu.bufs.Ubuf.copy_(torch.randn(NS, HV, L, V, generator=g).bfloat16())
+    cpu.bufs.Wbuf.copy_(torch.where(live, torch.rand(NS, HV, L, generator=g), torch.zeros(NS, HV, L)))
+    cpu.bufs.Pbuf.copy_(torch.rand(NS, HV, 1, generator=g))
+    gpu.sync_from(cpu)
+    idx = torch.arange(1, N + 1, dtype=torch.int32)
+    idx[torch.randperm(N, generator=g)[:9]] = 0
+    mixed, a, b_, A_log, dtb = step_inputs(N, H, HV, 1, 3, False)
+    o_c = torch.zeros(N, HV, V, dtype=torch.bfloat16)
+    o_g = torch.full((N, HV, V), 3.0, dtype=torch.bfloat16, device="cuda")
+    cpu.step(mixed[0], a[0], b_[0], A_log, dtb, idx, o_c)
+    st, vv = gpu.st, gpu.st.views(gpu.ssm)
+    st.kstep(vv["q32"], vv["Sk"], vv["Sv"], vv["skv"], st.Kbuf, st.Ubuf, st.Wbuf, st.Pbuf, st.hcnt, mixed[0].cuda(), a[0].cuda(),
+             b_[0].cuda(), A_log.cuda(), dtb.cuda(), vv["uq"], idx.cuda(), o_g)
+    mag = float(o_c.float().abs().max())
+    assert_close(o_g.cpu(), o_c, 8e-3, 1e-4 + 1e-3 * mag, "outputs")
+    compare_window(cpu, gpu, list(range(NS)), "ragged batch")
+
+
 def test_step_full_window_is_skipped():
     cpu, gpu = make_pair(3, 2, 2, 16, 4)
     gpu.st.hcnt.fill_(16)
@@ -216,15 +274,15 @@ def test_step_full_window_is_skipped():
 # ---------------------------------------------------------------------------------------------------------------------
 # flush
 # ---------------------------------------------------------------------------------------------------------------------
-def run_window(cpu, idx, H, HV, L, seed, kda):
+def run_window(cpu, idx, H, HV, L, seed, kda, gate_shift=0.0):
     N = idx.numel()
-    mixed, a, b_, A_log, dtb = step_inputs(N, H, HV, L, seed, kda)
+    mixed, a, b_, A_log, dtb = step_inputs(N, H, HV, L, seed, kda, gate_shift)
     o = torch.zeros(N, HV, V, dtype=torch.bfloat16)
     for t in range(L):
         cpu.step(mixed[t], a[t], b_[t], A_log, dtb, idx, o)
 
 
-def check_flush(cpu, gpu, idx, slots, what, code_tol=5e-3, code_frac=0.002):
+def check_flush(cpu, gpu, idx, slots, what, code_tol=5e-3, code_frac=0.002, strict_factors=True):
     """Flush both sides from identical inputs and compare stage by stage."""
     R, kda = cpu.R, cpu.kda
     b, v = cpu.bufs, cpu.v
@@ -249,7 +307,19 @@ def check_flush(cpu, gpu, idx, slots, what, code_tol=5e-3, code_frac=0.002):
     uq_c = v["uq"][ss, hh].float()
     QU_g = torch.einsum("drv,drc->dvc", uq_g[..., K:], uq_g[..., :K])
     QU_c = torch.einsum("drv,drc->dvc", uq_c[..., K:], uq_c[..., :K])
-    assert_close(QU_g, QU_c, 1e-3, 3e-3 * mag, what + ": Q U^T")
+    # (the trailing directions of a one-round subspace iteration are ill-conditioned, so the products agree to ~1 %
+    #  while the quality of the rank-R fit, which is what matters, agrees much more tightly)
+    fit_g = float((T - QU_g).norm()); fit_c = float((T - QU_c).norm())
+    if strict_factors:
+        assert_close(QU_g, QU_c, 1e-3, 3e-2 * mag, what + ": Q U^T")
+        assert abs(fit_g - fit_c) <= 5e-3 * fit_c, f"{what}: rank-R fit {fit_g:.6e} vs oracle {fit_c:.6e}"
+    else:       # numerically rank-deficient heads: which dependent column is floored / dropped depends on rounding
+        assert fit_g <= 1.5 * fit_c + 1e-6 * mag, f"{what}: rank-R fit {fit_g:.6e} vs oracle {fit_c:.6e}"
+    Qg = uq_g[..., K:]
+    gram = torch.einsum("drv,dsv->drs", Qg, Qg)
+    live = gram.diagonal(dim1=-2, dim2=-1) > 0.5                            # dropped (zeroed) columns excepted
+    eye = torch.diag_embed(live.float())
+    assert float((gram - eye).abs().max()) < 5e-3, f"{what}: stored Q is not orthonormal"
     # stage-wise: scales and codes are the oracle's function of the residual defined by the GPU's stored factors
     E = T - QU_g
     sk_g, sv_g = gv["Sk"][ss, hh], gv["Sv"][ss, hh]
@@ -271,15 +341,21 @@ def check_flush(cpu, gpu, idx, slots, what, code_tol=5e-3, code_frac=0.002):
 
 
 @pytest.mark.parametrize("kda,L,R", [(False, 16, 4), (False, 64, 4), (False, 32, 8), (True, 16, 4), (True, 32, 8)])
-def test_flush_against_oracle(kda, L, R):
+@pytest.mark.parametrize("gate_shift", [4.0, 0.0], ids=["mild_decay", "baseline_decay"])
+def test_flush_against_oracle(kda, L, R, gate_shift):
+    """gate_shift = 4: alpha ~ 0.98 per step, the state stays full rank and the factors are well defined -> strict factor
+    parity.  gate_shift = 0 is BASELINE's distribution (alpha ~ 0.5 per step): after a window the state is the last few
+    tokens only, numerically rank deficient, and only the fit quality, the stage-wise codes and the state are compared."""
     NS, HV, H = 5, 4, 2
     cpu, gpu = make_pair(NS, HV, H, L, R, kda=kda, seed=2)
     idx = torch.tensor([4, 2, 0, 1], dtype=torch.int32)
-    run_window(cpu, idx, H, HV, L, 31, kda)
+    run_window(cpu, idx, H, HV, L, 31, kda, gate_shift)
     cpu.bufs.hcnt[2, 1] = L - 3                              # one head of a due row is not due
     cpu.bufs.hcnt[3] = L                                     # a full slot that is not in the call
     gpu.sync_from(cpu)
-    check_flush(cpu, gpu, idx, [4, 2, 1], f"flush kda={kda} L={L} R={R}")
+    strict = gate_shift > 0
+    check_flush(cpu, gpu, idx, [4, 2, 1], f"flush kda={kda} L={L} R={R}", strict_factors=strict,
+                code_tol=5e-3 if strict else 5e-2, code_frac=0.002 if strict else 0.01)
     assert int(gpu.st.hcnt[3].min()) == L and int(gpu.st.hcnt[2, 1]) == L - 3
 
 
@@ -291,7 +367,7 @@ def test_flush_nothing_due_is_a_noop():
     st = gpu.st
     st.kflush(vv["q32"], vv["Sk"], vv["Sv"], vv["skv"], st.Kbuf, st.Ubuf, st.Wbuf, st.Pbuf, st.Gd, st.hcnt, vv["sq16"],
               vv["uq"], st.Q0, idx)
-    assert torch.equal(before, gpu.store)
+    assert torch.equal(before.view(torch.int32), gpu.store.view(torch.int32))
 
 
 def test_flush_degenerate_heads():
@@ -308,7 +384,7 @@ def test_flush_degenerate_heads():
     cpu.bufs.Pbuf[1] = 1e-30
     cpu.bufs.Ubuf[3] = 0
     gpu = GpuSide(cpu)
-    check_flush(cpu, gpu, idx, [1, 2, 3], "degenerate flush", code_tol=5e-2, code_frac=0.01)
+    check_flush(cpu, gpu, idx, [1, 2, 3], "degenerate flush", code_tol=5e-2, code_frac=0.01, strict_factors=False)
     s4, v, b = gpu.views_cpu()
     for k in ("Sk", "Sv", "uq"):
         assert torch.isfinite(v[k][[1, 2, 3]].float()).all(), k
@@ -318,7 +394,7 @@ def test_flush_degenerate_heads():
 # whole path
 # ---------------------------------------------------------------------------------------------------------------------
 @pytest.mark.parametrize("kda,L,R,steps", [(False, 64, 4, 140), (True, 32, 8, 70)])
-def test_decode_free_running(kda, L, R, steps):
+def test_decode_free_running(kda, L, R, steps, step_impl):
     """decode() (step + flush) for several windows without re-synchronising: outputs track the oracle and the
     unquantised fp32 recurrence (the reference's accuracy claim)."""
     NS, HV, H, N = 4, 4, 2, 3
@@ -366,7 +442,8 @@ def test_sharded_equals_unsharded():
         gpu_a.st.decode(gpu_a.ssm, mixed[t][:4].cuda(), a[t][:4].cuda(), b_[t][:4].cuda(), A_log.cuda(), dtb.cuda(), idx[:4].cuda(), o_a)
         gpu_b.st.decode(gpu_b.ssm, mixed[t][4:].cuda(), a[t][4:].cuda(), b_[t][4:].cuda(), A_log.cuda(), dtb.cuda(), idx[4:].cuda(), o_b)
         assert torch.equal(o_all[:4], o_a) and torch.equal(o_all[4:], o_b)
-    assert torch.equal(gpu_all.ssm[1:5], gpu_a.ssm[1:5]) and torch.equal(gpu_all.ssm[5:9], gpu_b.ssm[5:9])
+    bits = lambda t: t.view(torch.int32)
+    assert torch.equal(bits(gpu_all.ssm[1:5]), bits(gpu_a.ssm[1:5])) and torch.equal(bits(gpu_all.ssm[5:9]), bits(gpu_b.ssm[5:9]))
 
 
 def test_cpu_tensor_is_refused():
