@@ -1,11 +1,12 @@
 // GDN / KDA decode-step kernels (sm_100a).
 //
 // One "program" is one (row n, value head hv): it streams the head's INT8 checkpoint (codes, scales, factors) and the
-// h live entries of its window buffer, and appends the new token.  A program is executed by a group of 128 threads
-// working out of a shared-memory stage; the same body serves the two drivers in this file:
+// h live entries of its window buffer, and appends the new token.  A program is executed out of a shared-memory stage
+// in two parts: a one-warp prologue (l2 norms, operand vectors, gates, window-weight decay, key append) and a body run
+// by a group of GT threads (window dots, checkpoint matvec, contribution, output).  Two drivers share them:
 //   * step_direct_kernel    : one CTA per program, cooperative 16-byte global loads into the stage;
-//   * step_pipelined_kernel : persistent CTAs, a producer warp filling a ring of stages with bulk asynchronous
-//                             copies (cp.async.bulk + mbarrier) while the consumer groups compute.
+//   * step_pipelined_kernel : persistent CTAs; a producer warp fills a ring of stages with bulk asynchronous copies
+//                             (cp.async.bulk + mbarrier), a prologue warp prepares each stage, consumer groups compute.
 //
 // Thread mapping of the matvec: eight lanes share a row of the 128 x 128 INT8 tile; lane l8 = lane & 7 owns the
 // 16 columns 16 l8 .. 16 l8 + 15, so a warp-wide 16-byte load covers four whole 128-byte rows and the operand
@@ -16,11 +17,14 @@
 
 namespace lq {
 
-constexpr int GT = 128;                   // threads of one consumer group
+constexpr int GW = 8;                     // warps of one consumer group (a group executes one program at a time)
+constexpr int GT = 32 * GW;               // its threads
+constexpr int NPASS = 32 / GW;            // tile passes per warp (four 128-byte rows per pass)
+static_assert(GW == 4 || GW == 8, "the reductions below are written for 4 or 8 warps per group");
 
 // ---- stage layout (bytes); the checkpoint part mirrors the packed slot so that it is ONE contiguous copy ----
 struct StageLayout {
-    int kb, ub, w, q, k, v, gb, pb, a, dtb, sc, bytes;
+    int kb, ub, w, q, k, v, gb, pb, a, dtb, nrm, sc, bytes;
 };
 __host__ __device__ inline StageLayout stage_layout(int L, int R, bool kda) {
     StageLayout s;
@@ -38,7 +42,8 @@ __host__ __device__ inline StageLayout stage_layout(int L, int R, bool kda) {
         s.a = o; o += 256;
         s.dtb = o; o += 512;
     }
-    s.sc = o; o += 32;                      // ProgScalars written by the producer warp (pipelined driver)
+    s.nrm = o; o += 4 * 512;                // prologue output: k_hat, q_hat, then GDN: kf, qf | KDA: pc, en  (f32[128] each)
+    s.sc = o; o += 64;                      // ProgScalars (producer) + k_hat . q_hat (prologue)
     s.bytes = (o + 127) & ~127;
     return s;
 }
@@ -74,19 +79,13 @@ struct ProgScalars {
 struct GroupScratch {
     float2* wd;      // [64 + 8]  (w_j dk_j, w_j dq_j) for j < L, then (dU_r . k, dU_r . q) at 64 + r
     float2* mqy;     // [128]     (mq, yq) per row
-    float4* part;    // [64][2]   partial contribution sums of the odd-j half
-    float* pcs;      // [128]     KDA: pc per column
-    float* ens;      // [128]     KDA: en per column
 };
-constexpr int SCRATCH_BYTES = (72 * 8) + 128 * 8 + 64 * 32 + 128 * 4 + 128 * 4;   // 4672
+constexpr int SCRATCH_BYTES = 72 * 8 + 128 * 8;
 
 __device__ __forceinline__ GroupScratch carve_scratch(char* p) {
     GroupScratch g;
-    g.wd = reinterpret_cast<float2*>(p); p += 72 * 8;
-    g.mqy = reinterpret_cast<float2*>(p); p += 128 * 8;
-    g.part = reinterpret_cast<float4*>(p); p += 64 * 32;
-    g.pcs = reinterpret_cast<float*>(p); p += 128 * 4;
-    g.ens = reinterpret_cast<float*>(p);
+    g.wd = reinterpret_cast<float2*>(p);
+    g.mqy = reinterpret_cast<float2*>(p + 72 * 8);
     return g;
 }
 
@@ -110,134 +109,251 @@ __device__ __forceinline__ ProgScalars load_scalars(const StepParams& P, int n, 
     }
     return s;
 }
+__device__ __forceinline__ bool prog_live(const ProgScalars& s, int L) { return s.slot > 0 && s.h >= 0 && s.h < L; }
 
-// Transposed reduction: every lane holds eight partial sums x[0..7] (one per tile pass); the eight lanes of a row group
-// add them up so that lane l8 ends with the total of pass l8.  7 shuffles instead of 24.
-__device__ __forceinline__ float oct_transpose_sum(const float (&x)[8], int l8) {
-    float y[4];
-    const bool b2 = l8 & 4;
+// Transposed reductions over the eight lanes of a row group.  Every lane holds one partial sum per tile pass; the lanes
+// add them up so that lane l8 ends with the total of pass l8 (mod the number of passes).
+template <int N>
+__device__ __forceinline__ float pass_transpose_sum(const float (&x)[N], int l8) {
+    if constexpr (N == 8) {                       // 7 shuffles instead of 24
+        float y[4];
+        const bool b2 = l8 & 4;
 #pragma unroll
-    for (int k = 0; k < 4; ++k) {
-        const float keep = b2 ? x[4 + k] : x[k];
-        const float send = b2 ? x[k] : x[4 + k];
-        y[k] = keep + __shfl_xor_sync(0xffffffffu, send, 4);
-    }
-    float z[2];
-    const bool b1 = l8 & 2;
+        for (int k = 0; k < 4; ++k) {
+            const float keep = b2 ? x[4 + k] : x[k];
+            const float send = b2 ? x[k] : x[4 + k];
+            y[k] = keep + __shfl_xor_sync(0xffffffffu, send, 4);
+        }
+        float z[2];
+        const bool b1 = l8 & 2;
 #pragma unroll
-    for (int k = 0; k < 2; ++k) {
-        const float keep = b1 ? y[2 + k] : y[k];
-        const float send = b1 ? y[k] : y[2 + k];
-        z[k] = keep + __shfl_xor_sync(0xffffffffu, send, 2);
+        for (int k = 0; k < 2; ++k) {
+            const float keep = b1 ? y[2 + k] : y[k];
+            const float send = b1 ? y[k] : y[2 + k];
+            z[k] = keep + __shfl_xor_sync(0xffffffffu, send, 2);
+        }
+        const bool b0 = l8 & 1;
+        const float keep = b0 ? z[1] : z[0];
+        const float send = b0 ? z[0] : z[1];
+        return keep + __shfl_xor_sync(0xffffffffu, send, 1);
+    } else {                                      // four passes: transposed over lane bits 1 and 0, summed over bit 2
+        static_assert(N == 4, "4 or 8 passes");
+        float y[2];
+        const bool b1 = l8 & 2;
+#pragma unroll
+        for (int k = 0; k < 2; ++k) {
+            const float keep = b1 ? x[2 + k] : x[k];
+            const float send = b1 ? x[k] : x[2 + k];
+            y[k] = keep + __shfl_xor_sync(0xffffffffu, send, 2);
+        }
+        const bool b0 = l8 & 1;
+        const float keep = b0 ? y[1] : y[0];
+        const float send = b0 ? y[0] : y[1];
+        const float z = keep + __shfl_xor_sync(0xffffffffu, send, 1);
+        return z + __shfl_xor_sync(0xffffffffu, z, 4);
     }
-    const bool b0 = l8 & 1;
-    const float keep = b0 ? z[1] : z[0];
-    const float send = b0 ? z[0] : z[1];
-    return keep + __shfl_xor_sync(0xffffffffu, send, 1);
 }
 
+#ifdef LQ_TRACE
+static __device__ long long g_qtrace[160 * 256 * 8];
+#define LQ_QSTAMP(k) do { if (i < 256 && blockIdx.x < 160 && lane == 0) g_qtrace[(blockIdx.x * 256 + i) * 8 + (k)] = clock64(); } while (0)
+static __device__ long long g_ntrace[160 * 256 * 8];
+#define LQ_NSTAMP(k) do { if (pi >= 0 && pi < 256 && blockIdx.x < 160 && lane == 0) g_ntrace[(blockIdx.x * 256 + pi) * 8 + (k)] = clock64(); } while (0)
+#define LQ_NSTAMPD(k, dep) do { if (pi >= 0 && pi < 256 && blockIdx.x < 160 && lane == 0) g_ntrace[(blockIdx.x * 256 + pi) * 8 + (k)] = clock64() + (long long)(__float_as_uint(dep) & 0u); } while (0)
+#else
+#define LQ_NSTAMP(k) do { } while (0)
+#define LQ_QSTAMP(k) do { } while (0)
+#define LQ_NSTAMPD(k, dep) do { } while (0)
+#endif
+
+// The four f32[128] vectors the prologue leaves in the stage are read back by eight lanes at a time, lane l8 taking the
+// 64 bytes of its 16 channels as four 16-byte chunks.  Chunk c (0..31) is stored at c with its two low bits XORed by
+// bits 3..4 of c, which spreads the eight lanes of a quarter-warp over all eight 16-byte bank groups.
+__device__ __forceinline__ int nrm_chunk(int c) { return (c & ~3) | ((c & 3) ^ ((c >> 3) & 3)); }
+
 // ------------------------------------------------------------------------------------------------------------------
-// the program body: 128 threads, operands in the shared-memory stage `st`
+// prologue: ONE warp, lane owns key channels 4 lane .. 4 lane + 3
 // ------------------------------------------------------------------------------------------------------------------
-template <int R, bool KDA>
+// `signal()` is called after the last shared-memory write and BEFORE the global stores (see step_body's `release`).
+template <bool KDA, typename Signal>
+__device__ __forceinline__ void step_prologue(const StepParams& P, const ProgScalars& sc, char* st, const StageLayout& lay,
+                                              int lane, Signal signal, int pi = -1) {
+    const int L = P.d.L, h = sc.h;
+    LQ_NSTAMP(0);
+    const int64_t sh = int64_t(sc.slot) * P.d.HV + sc.hv;
+    const uint2 qw = reinterpret_cast<const uint2*>(st + lay.q)[lane];
+    const uint2 kw = reinterpret_cast<const uint2*>(st + lay.k)[lane];
+    float q[4], k[4];
+    q[0] = bf16lo(qw.x); q[1] = bf16hi(qw.x); q[2] = bf16lo(qw.y); q[3] = bf16hi(qw.y);
+    k[0] = bf16lo(kw.x); k[1] = bf16hi(kw.x); k[2] = bf16lo(kw.y); k[3] = bf16hi(kw.y);
+    float sq = 0.f, sk = 0.f, skq = 0.f;
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        sq = fmaf(q[i], q[i], sq);
+        sk = fmaf(k[i], k[i], sk);
+        skq = fmaf(k[i], q[i], skq);
+    }
+    LQ_NSTAMPD(1, sq + sk + skq);
+    sq = warp_sum(sq);
+    LQ_NSTAMPD(7, sq);
+    sk = warp_sum(sk); skq = warp_sum(skq);
+    LQ_NSTAMPD(2, sq + sk + skq);
+    const float inq = rsqrtf(sq + 1e-6f) * P.scale, ink = rsqrtf(sk + 1e-6f);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        q[i] *= inq;
+        k[i] *= ink;
+    }
+    float4* nrm = reinterpret_cast<float4*>(st + lay.nrm);
+    const int sl = nrm_chunk(lane);                       // swizzled 16-byte chunk of this lane's four channels
+    nrm[sl] = make_float4(k[0], k[1], k[2], k[3]);
+    nrm[32 + sl] = make_float4(q[0], q[1], q[2], q[3]);
+    if (lane == 0) *reinterpret_cast<float*>(st + lay.sc + 32) = skq * inq * ink;
+    LQ_NSTAMP(3);
+    const uint2 kapp = make_uint2(f2_to_bf16x2(k[0], k[1]), f2_to_bf16x2(k[2], k[3]));      // k_hat (bf16) for the window
+    if (KDA) {
+        // per-channel gate: log-decay g, cumulative log gate gn, pc = exp(gn), step factor en = exp(g)
+        const uint2 aw = reinterpret_cast<const uint2*>(st + lay.a)[lane];
+        const float4 db = reinterpret_cast<const float4*>(st + lay.dtb)[lane];
+        const float4 pb = reinterpret_cast<const float4*>(st + lay.pb)[lane];
+        const float xa[4] = {bf16lo(aw.x) + db.x, bf16hi(aw.x) + db.y, bf16lo(aw.y) + db.z, bf16hi(aw.y) + db.w};
+        const float pbv[4] = {pb.x, pb.y, pb.z, pb.w};
+        float gn[4], en[4], pc[4];
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            float gl;
+            if (P.glb != 0.f) gl = P.glb * (1.0f / (1.0f + __expf(-sc.ea * xa[i])));
+            else gl = -sc.ea * (xa[i] <= SOFTPLUS_THRESHOLD ? __logf(1.0f + __expf(xa[i])) : xa[i]);
+            gn[i] = pbv[i] + gl;
+            en[i] = __expf(gl);
+            pc[i] = __expf(gn[i]);
+        }
+        nrm[64 + sl] = make_float4(pc[0], pc[1], pc[2], pc[3]);
+        nrm[96 + sl] = make_float4(en[0], en[1], en[2], en[3]);
+        signal();
+        reinterpret_cast<uint2*>(P.Kbuf + (sh * L + h) * KD)[lane] = kapp;
+        reinterpret_cast<float4*>(P.Pbuf + sh * KD)[lane] = make_float4(gn[0], gn[1], gn[2], gn[3]);
+        __half2 e01 = __floats2half2_rn(en[0], en[1]), e23 = __floats2half2_rn(en[2], en[3]);
+        reinterpret_cast<uint2*>(P.Gbuf + (sh * L + h) * KD)[lane] =
+            make_uint2(*reinterpret_cast<uint32_t*>(&e01), *reinterpret_cast<uint32_t*>(&e23));
+    } else {
+        // matvec operands k_hat Sk / 127 and q_hat Sk / 127
+        const float4 s4 = reinterpret_cast<const float4*>(st + CK_SK)[lane];
+        const float s[4] = {s4.x * (1.0f / QMAX), s4.y * (1.0f / QMAX), s4.z * (1.0f / QMAX), s4.w * (1.0f / QMAX)};
+        nrm[64 + sl] = make_float4(k[0] * s[0], k[1] * s[1], k[2] * s[2], k[3] * s[3]);
+        nrm[96 + sl] = make_float4(q[0] * s[0], q[1] * s[1], q[2] * s[2], q[3] * s[3]);
+        // window weights decay: w_j <- w_j alpha for the live entries, in the stage and (after the signal) in global memory
+        float* ws = reinterpret_cast<float*>(st + lay.w);
+        float wj[2] = {0.f, 0.f};
+#pragma unroll
+        for (int i = 0; i < 2; ++i) {
+            const int j = lane + 32 * i;
+            if (j < h) {
+                wj[i] = ws[j] * sc.alpha;
+                ws[j] = wj[i];
+            }
+        }
+        LQ_NSTAMP(4);
+        signal();
+        LQ_NSTAMP(5);
+        reinterpret_cast<uint2*>(P.Kbuf + (sh * L + h) * KD)[lane] = kapp;
+#pragma unroll
+        for (int i = 0; i < 2; ++i) {
+            const int j = lane + 32 * i;
+            if (j < h) P.Wbuf[sh * L + j] = wj[i];
+        }
+        LQ_NSTAMP(6);
+    }
+}
+
+#ifdef LQ_TRACE
+static __device__ long long g_ptrace[160 * 256 * 8];
+#define LQ_PSTAMP(k) do { if (pi >= 0 && pi < 256 && blockIdx.x < 160 && t == 0) g_ptrace[(blockIdx.x * 256 + pi) * 8 + (k)] = clock64(); } while (0)
+#else
+#define LQ_PSTAMP(k) do { } while (0)
+#endif
+
+// ------------------------------------------------------------------------------------------------------------------
+// body: GT threads, operands in the shared-memory stage `st` (prologue done)
+// ------------------------------------------------------------------------------------------------------------------
+// `release()` is called by every thread after its last read of the stage and BEFORE the program's global stores: the
+// stage hand-back is an mbarrier arrive with release semantics, which would otherwise wait for those stores to drain.
+template <int R, bool KDA, typename Release>
 __device__ __forceinline__ void step_body(const StepParams& P, const ProgScalars& sc, char* st, const StageLayout& lay,
-                                          const GroupScratch& gs, int t, int bar) {
+                                          const GroupScratch& gs, int t, int bar, Release release, int pi = -1) {
     const int w = t >> 5, lane = t & 31, l8 = lane & 7, g = lane >> 3;
     const int L = P.d.L, h = sc.h;
     const int64_t sh = int64_t(sc.slot) * P.d.HV + sc.hv;
-    const float alpha = sc.alpha;
+    LQ_PSTAMP(0);
+    const float* nrm = reinterpret_cast<const float*>(st + lay.nrm);
 
-    // ---- KDA pre-pass (thread per key channel): gate, cumulative log gate, decayed window keys ----
+    // ---- KDA: decayed window keys K_j D_j (bf16, in place), D_j = en prod_{j<i<h} e_i; thread per key channel ----
     if (KDA) {
-        const int c = t;
-        const float xg = bf16_to_f(reinterpret_cast<const uint16_t*>(st + lay.a)[c]) + reinterpret_cast<const float*>(st + lay.dtb)[c];
-        float gl;
-        if (P.glb != 0.f) gl = P.glb * (1.0f / (1.0f + __expf(-sc.ea * xg)));
-        else gl = -sc.ea * (xg <= SOFTPLUS_THRESHOLD ? __logf(1.0f + __expf(xg)) : xg);
-        const float gn = reinterpret_cast<const float*>(st + lay.pb)[c] + gl;
-        const float en = __expf(gl);
-        gs.pcs[c] = __expf(gn);
-        gs.ens[c] = en;
-        P.Pbuf[sh * KD + c] = gn;
-        P.Gbuf[(sh * L + h) * KD + c] = f_to_f16(en);
-        uint16_t* kb = reinterpret_cast<uint16_t*>(st + lay.kb);
-        const uint16_t* gb = reinterpret_cast<const uint16_t*>(st + lay.gb);
-        float dcur = en;
-        for (int j = h - 1; j >= 0; --j) {
-            kb[j * KD + c] = f_to_bf16(bf16_to_f(kb[j * KD + c]) * dcur);
-            dcur *= f16_to_f(gb[j * KD + c]);
+        if (t < KD) {
+            uint16_t* kb = reinterpret_cast<uint16_t*>(st + lay.kb);
+            const uint16_t* gb = reinterpret_cast<const uint16_t*>(st + lay.gb);
+            float dcur = nrm[384 + 4 * nrm_chunk(t >> 2) + (t & 3)];
+            for (int j = h - 1; j >= 0; --j) {
+                kb[j * KD + t] = f_to_bf16(bf16_to_f(kb[j * KD + t]) * dcur);
+                dcur *= f16_to_f(gb[j * KD + t]);
+            }
         }
         named_bar(bar, GT);
     }
 
-    // ---- l2 norms of q and k over this lane's 16 columns, reduced over the 8 lanes of the row group ----
+    // ---- k_hat, q_hat of this lane's 16 columns ----
     float2 kn[8], qn[8];
-    float kq;
     {
-        const uint4 q0 = reinterpret_cast<const uint4*>(st + lay.q)[l8 * 2], q1 = reinterpret_cast<const uint4*>(st + lay.q)[l8 * 2 + 1];
-        const uint4 k0 = reinterpret_cast<const uint4*>(st + lay.k)[l8 * 2], k1 = reinterpret_cast<const uint4*>(st + lay.k)[l8 * 2 + 1];
-        const uint32_t qw[8] = {q0.x, q0.y, q0.z, q0.w, q1.x, q1.y, q1.z, q1.w};
-        const uint32_t kw[8] = {k0.x, k0.y, k0.z, k0.w, k1.x, k1.y, k1.z, k1.w};
-        float sq = 0.f, sk = 0.f, skq = 0.f;
+        const float4* kp = reinterpret_cast<const float4*>(nrm);
+        const float4* qp = reinterpret_cast<const float4*>(nrm + 128);
 #pragma unroll
-        for (int i = 0; i < 8; ++i) {
-            qn[i] = bf16x2_to_f2(qw[i]);
-            kn[i] = bf16x2_to_f2(kw[i]);
-            sq = fmaf(qn[i].x, qn[i].x, sq); sq = fmaf(qn[i].y, qn[i].y, sq);
-            sk = fmaf(kn[i].x, kn[i].x, sk); sk = fmaf(kn[i].y, kn[i].y, sk);
-            skq = fmaf(kn[i].x, qn[i].x, skq); skq = fmaf(kn[i].y, qn[i].y, skq);
+        for (int i = 0; i < 4; ++i) {
+            const float4 a = kp[nrm_chunk(l8 * 4 + i)], b = qp[nrm_chunk(l8 * 4 + i)];
+            kn[2 * i] = make_float2(a.x, a.y); kn[2 * i + 1] = make_float2(a.z, a.w);
+            qn[2 * i] = make_float2(b.x, b.y); qn[2 * i + 1] = make_float2(b.z, b.w);
         }
-        sq = oct_sum(sq); sk = oct_sum(sk); skq = oct_sum(skq);
-        const float inq = rsqrtf(sq + 1e-6f) * P.scale, ink = rsqrtf(sk + 1e-6f);
-        kq = skq * inq * ink;
-#pragma unroll
-        for (int i = 0; i < 8; ++i) {
-            qn[i] = __fmul2_rn(qn[i], make_float2(inq, inq));
-            kn[i] = __fmul2_rn(kn[i], make_float2(ink, ink));
-        }
-    }
-    // append k_hat (bf16) to the window: warp 0, row group 0 holds all 128 columns
-    if (w == 0 && g == 0) {
-        uint4 a0, a1;
-        a0.x = f2_to_bf16x2(kn[0].x, kn[0].y); a0.y = f2_to_bf16x2(kn[1].x, kn[1].y);
-        a0.z = f2_to_bf16x2(kn[2].x, kn[2].y); a0.w = f2_to_bf16x2(kn[3].x, kn[3].y);
-        a1.x = f2_to_bf16x2(kn[4].x, kn[4].y); a1.y = f2_to_bf16x2(kn[5].x, kn[5].y);
-        a1.z = f2_to_bf16x2(kn[6].x, kn[6].y); a1.w = f2_to_bf16x2(kn[7].x, kn[7].y);
-        uint4* dst = reinterpret_cast<uint4*>(P.Kbuf + (sh * L + h) * KD) + l8 * 2;
-        dst[0] = a0;
-        dst[1] = a1;
     }
 
+    LQ_PSTAMP(1);
     // ---- window dots dk_j = K_j . k_hat, dq_j = K_j . q_hat: four rows per warp pass, passes dealt round-robin to the warps ----
     const int nch = (h + 3) >> 2;
-    for (int ch = w; ch < nch; ch += 4) {
-        const int j = 4 * ch + g;
-        const bool live = j < h;
-        const int jj = live ? j : 0;
-        const uint4 r0 = reinterpret_cast<const uint4*>(st + lay.kb + jj * 256)[l8 * 2];
-        const uint4 r1 = reinterpret_cast<const uint4*>(st + lay.kb + jj * 256)[l8 * 2 + 1];
-        const uint32_t ww[8] = {r0.x, r0.y, r0.z, r0.w, r1.x, r1.y, r1.z, r1.w};
-        float2 ak = make_float2(0.f, 0.f), aq = make_float2(0.f, 0.f);
+    for (int ch = w; ch < nch; ch += 2 * GW) {               // two passes in flight per warp
+        const int ja = 4 * ch + g, jb = ja + 4 * GW;
+        const bool la = ja < h, lb = jb < h;
+        const char* ra = st + lay.kb + (la ? ja : 0) * 256;
+        const char* rb = st + lay.kb + (lb ? jb : 0) * 256;
+        const uint4 a0 = reinterpret_cast<const uint4*>(ra)[l8 * 2], a1 = reinterpret_cast<const uint4*>(ra)[l8 * 2 + 1];
+        const uint4 b0 = reinterpret_cast<const uint4*>(rb)[l8 * 2], b1 = reinterpret_cast<const uint4*>(rb)[l8 * 2 + 1];
+        const uint32_t wa[8] = {a0.x, a0.y, a0.z, a0.w, a1.x, a1.y, a1.z, a1.w};
+        const uint32_t wb[8] = {b0.x, b0.y, b0.z, b0.w, b1.x, b1.y, b1.z, b1.w};
+        float2 aka = make_float2(0.f, 0.f), aqa = aka, akb = aka, aqb = aka;
 #pragma unroll
         for (int i = 0; i < 8; ++i) {
-            const float2 x = bf16x2_to_f2(ww[i]);
-            ak = __ffma2_rn(x, kn[i], ak);
-            aq = __ffma2_rn(x, qn[i], aq);
+            const float2 xa = bf16x2_to_f2(wa[i]), xb = bf16x2_to_f2(wb[i]);
+            aka = __ffma2_rn(xa, kn[i], aka);
+            aqa = __ffma2_rn(xa, qn[i], aqa);
+            akb = __ffma2_rn(xb, kn[i], akb);
+            aqb = __ffma2_rn(xb, qn[i], aqb);
         }
-        const float dk = oct_sum(ak.x + ak.y), dq = oct_sum(aq.x + aq.y);
-        if (live && l8 == 0) {
-            float wj = reinterpret_cast<const float*>(st + lay.w)[j];
-            if (!KDA) {
-                wj *= alpha;
-                P.Wbuf[sh * L + j] = wj;
-            }
-            gs.wd[j] = make_float2(wj * dk, wj * dq);
+        float dka = aka.x + aka.y, dqa = aqa.x + aqa.y, dkb = akb.x + akb.y, dqb = aqb.x + aqb.y;
+#pragma unroll
+        for (int o = 1; o <= 4; o <<= 1) {
+            dka += __shfl_xor_sync(0xffffffffu, dka, o);
+            dqa += __shfl_xor_sync(0xffffffffu, dqa, o);
+            dkb += __shfl_xor_sync(0xffffffffu, dkb, o);
+            dqb += __shfl_xor_sync(0xffffffffu, dqb, o);
+        }
+        if (l8 == 0) {
+            const float* ws = reinterpret_cast<const float*>(st + lay.w);        // GDN: already decayed by the prologue
+            if (la) { const float wj = ws[ja]; gs.wd[ja] = make_float2(wj * dka, wj * dqa); }
+            if (lb) { const float wj = ws[jb]; gs.wd[jb] = make_float2(wj * dkb, wj * dqb); }
         }
     }
+    LQ_PSTAMP(2);
     // ---- factor dots dU_r . k_hat, dU_r . q_hat (KDA: U_r[c] pc[c]) ----
 #pragma unroll
     for (int cr = 0; cr < R / 4; ++cr) {
-        if (((nch + cr) & 3) == w) {
+        if (((nch + cr) % GW) == w) {
             const int r = 4 * cr + g;
             const uint4 r0 = reinterpret_cast<const uint4*>(st + CK_UQ + r * 512)[l8 * 2];
             const uint4 r1 = reinterpret_cast<const uint4*>(st + CK_UQ + r * 512)[l8 * 2 + 1];
@@ -246,7 +362,7 @@ __device__ __forceinline__ void step_body(const StepParams& P, const ProgScalars
 #pragma unroll
             for (int i = 0; i < 8; ++i) {
                 float2 x = f16x2_to_f2(ww[i]);
-                if (KDA) x = __fmul2_rn(x, *reinterpret_cast<const float2*>(gs.pcs + l8 * 16 + 2 * i));
+                if (KDA) x = __fmul2_rn(x, *reinterpret_cast<const float2*>(nrm + 256 + 4 * nrm_chunk(l8 * 4 + (i >> 1)) + 2 * (i & 1)));
                 ak = __ffma2_rn(x, kn[i], ak);
                 aq = __ffma2_rn(x, qn[i], aq);
             }
@@ -255,30 +371,37 @@ __device__ __forceinline__ void step_body(const StepParams& P, const ProgScalars
         }
     }
 
-    // ---- checkpoint matvec: operands k_hat Sk / 127 (pc), q_hat Sk / 127 (pc) for this lane's columns ----
-    {
+    LQ_PSTAMP(3);
+    // ---- checkpoint matvec operands: GDN from the prologue; KDA k_hat Sk pc / 127 ----
+    if (KDA) {
         const float4* skp = reinterpret_cast<const float4*>(st + CK_SK) + l8 * 4;
+        const float4* pcp = reinterpret_cast<const float4*>(nrm + 256);
 #pragma unroll
         for (int i = 0; i < 4; ++i) {
-            float4 s4 = skp[i];
-            if (KDA) {
-                const float4 p4 = reinterpret_cast<const float4*>(gs.pcs)[l8 * 4 + i];
-                s4.x *= p4.x; s4.y *= p4.y; s4.z *= p4.z; s4.w *= p4.w;
-            }
-            const float2 sa = make_float2(s4.x * (1.0f / QMAX), s4.y * (1.0f / QMAX));
-            const float2 sb = make_float2(s4.z * (1.0f / QMAX), s4.w * (1.0f / QMAX));
+            const float4 s4 = skp[i], p4 = pcp[nrm_chunk(l8 * 4 + i)];
+            const float2 sa = make_float2(s4.x * p4.x * (1.0f / QMAX), s4.y * p4.y * (1.0f / QMAX));
+            const float2 sb = make_float2(s4.z * p4.z * (1.0f / QMAX), s4.w * p4.w * (1.0f / QMAX));
             kn[2 * i] = __fmul2_rn(kn[2 * i], sa);
             qn[2 * i] = __fmul2_rn(qn[2 * i], sa);
             kn[2 * i + 1] = __fmul2_rn(kn[2 * i + 1], sb);
             qn[2 * i + 1] = __fmul2_rn(qn[2 * i + 1], sb);
         }
+    } else {
+        const float4* kp = reinterpret_cast<const float4*>(nrm + 256);
+        const float4* qp = reinterpret_cast<const float4*>(nrm + 384);
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            const float4 a = kp[nrm_chunk(l8 * 4 + i)], b = qp[nrm_chunk(l8 * 4 + i)];
+            kn[2 * i] = make_float2(a.x, a.y); kn[2 * i + 1] = make_float2(a.z, a.w);
+            qn[2 * i] = make_float2(b.x, b.y); qn[2 * i + 1] = make_float2(b.z, b.w);
+        }
     }
-    float pk[8], pq[8];
+    float pk[NPASS], pq[NPASS];
     {
         const uint4* tile = reinterpret_cast<const uint4*>(st + CK_CODES);
 #pragma unroll
-        for (int it = 0; it < 8; ++it) {
-            const int row = 32 * w + 4 * it + g;
+        for (int it = 0; it < NPASS; ++it) {
+            const int row = (VD / GW) * w + 4 * it + g;
             const uint4 cw = tile[row * 8 + l8];
             const uint32_t ww[4] = {cw.x, cw.y, cw.z, cw.w};
             float2 ak = make_float2(0.f, 0.f), aq = make_float2(0.f, 0.f);
@@ -296,20 +419,27 @@ __device__ __forceinline__ void step_body(const StepParams& P, const ProgScalars
         }
     }
     {
-        const float mqr = oct_transpose_sum(pk, l8), yqr = oct_transpose_sum(pq, l8);
-        const int row = 32 * w + 4 * l8 + g;
-        const float svv = reinterpret_cast<const float*>(st + CK_SV)[row];
-        gs.mqy[row] = make_float2(mqr * svv, yqr * svv);
+        const float mqr = pass_transpose_sum(pk, l8), yqr = pass_transpose_sum(pq, l8);
+        if (l8 < NPASS) {                                    // lane l8 owns the row of pass l8
+            const int row = (VD / GW) * w + 4 * l8 + g;
+            const float svv = reinterpret_cast<const float*>(st + CK_SV)[row];
+            gs.mqy[row] = make_float2(mqr * svv, yqr * svv);
+        }
     }
+    LQ_PSTAMP(4);
     named_bar(bar, GT);
+    LQ_PSTAMP(5);
 
-    // ---- contribution of the window and of the rank-R part: thread = (value pair vp, parity of j) ----
-    const int vp = t & 63, jh = t >> 6;
+    // ---- contribution of the window and of the rank-R part.  A warp owns 64 / GW value pairs; within it lane & 7 picks
+    //      the pair and lane >> 3 the phase of j (j mod 4); the four phases are combined with two shuffles. ----
+    constexpr int VPW = 64 / GW;                             // value pairs per warp (8, or 16 with two per lane)
+    static_assert(VPW == 8, "the contribution mapping assumes eight warps per group");
+    const int vp = VPW * w + l8, jh = g;
     float2 ck = make_float2(0.f, 0.f), cq = make_float2(0.f, 0.f), rk = make_float2(0.f, 0.f), rq = make_float2(0.f, 0.f);
     {
         const uint32_t* ub = reinterpret_cast<const uint32_t*>(st + lay.ub);
 #pragma unroll 4
-        for (int j = jh; j < h; j += 2) {
+        for (int j = jh; j < h; j += 4) {
             const float2 u2 = bf16x2_to_f2(ub[j * 64 + vp]);
             const float2 wd = gs.wd[j];
             ck = __ffma2_rn(u2, make_float2(wd.x, wd.x), ck);
@@ -317,42 +447,46 @@ __device__ __forceinline__ void step_body(const StepParams& P, const ProgScalars
         }
         const uint32_t* uq = reinterpret_cast<const uint32_t*>(st + CK_UQ);
 #pragma unroll
-        for (int r = jh; r < R; r += 2) {
+        for (int r = jh; r < R; r += 4) {
             const float2 q2 = f16x2_to_f2(uq[r * 128 + 64 + vp]);
             const float2 dd = gs.wd[64 + r];
             rk = __ffma2_rn(q2, make_float2(dd.x, dd.x), rk);
             rq = __ffma2_rn(q2, make_float2(dd.y, dd.y), rq);
         }
     }
-    if (jh == 1) {
-        gs.part[vp * 2] = make_float4(ck.x, ck.y, cq.x, cq.y);
-        gs.part[vp * 2 + 1] = make_float4(rk.x, rk.y, rq.x, rq.y);
+#pragma unroll
+    for (int o = 8; o <= 16; o <<= 1) {
+        ck.x += __shfl_xor_sync(0xffffffffu, ck.x, o); ck.y += __shfl_xor_sync(0xffffffffu, ck.y, o);
+        cq.x += __shfl_xor_sync(0xffffffffu, cq.x, o); cq.y += __shfl_xor_sync(0xffffffffu, cq.y, o);
+        rk.x += __shfl_xor_sync(0xffffffffu, rk.x, o); rk.y += __shfl_xor_sync(0xffffffffu, rk.y, o);
+        rq.x += __shfl_xor_sync(0xffffffffu, rq.x, o); rq.y += __shfl_xor_sync(0xffffffffu, rq.y, o);
     }
-    named_bar(bar, GT);
+    LQ_PSTAMP(6);
+    float u0 = 0.f, u1 = 0.f, y0 = 0.f, y1 = 0.f, pn = 0.f;
     if (jh == 0) {
-        const float4 pa = gs.part[vp * 2], pb = gs.part[vp * 2 + 1];
-        ck.x += pa.x; ck.y += pa.y; cq.x += pa.z; cq.y += pa.w;
-        rk.x += pb.x; rk.y += pb.y; rq.x += pb.z; rq.y += pb.w;
         const float2 m0 = gs.mqy[2 * vp], m1 = gs.mqy[2 * vp + 1];
         const float2 vv = bf16x2_to_f2(reinterpret_cast<const uint32_t*>(st + lay.v)[vp]);
         const float beta = sc.beta;
-        float u0, u1, y0, y1;
+        const float kq = *reinterpret_cast<const float*>(st + lay.sc + 32);
         if (KDA) {
             u0 = beta * (vv.x - (m0.x + rk.x + ck.x));
             u1 = beta * (vv.y - (m1.x + rk.y + ck.y));
             y0 = m0.y + rq.x + cq.x + kq * u0;
             y1 = m1.y + rq.y + cq.y + kq * u1;
         } else {
-            const float pn = sc.pold * alpha;
+            pn = sc.pold * sc.alpha;
             u0 = beta * (vv.x - (pn * (m0.x + rk.x) + ck.x));
             u1 = beta * (vv.y - (pn * (m1.x + rk.y) + ck.y));
             y0 = pn * (m0.y + rq.x) + cq.x + kq * u0;
             y1 = pn * (m1.y + rq.y) + cq.y + kq * u1;
-            if (t == 0) P.Pbuf[sh] = pn;
         }
+    }
+    release();
+    if (jh == 0) {
         reinterpret_cast<uint32_t*>(P.o)[(int64_t(sc.n) * P.d.HV + sc.hv) * 64 + vp] = f2_to_bf16x2(y0, y1);
         reinterpret_cast<uint32_t*>(P.Ubuf)[(sh * L + h) * 64 + vp] = f2_to_bf16x2(u0, u1);
         if (t == 0) {
+            if (!KDA) P.Pbuf[sh] = pn;
             P.Wbuf[sh * L + h] = 1.f;
             P.hcnt[sh] = h + 1;
         }
@@ -377,7 +511,7 @@ __device__ __forceinline__ void copy16(char* dst, const char* src, int bytes, in
 }
 
 template <int R, bool KDA>
-__global__ void __launch_bounds__(GT, 4) step_direct_kernel(StepParams P) {
+__global__ void __launch_bounds__(GT, 2) step_direct_kernel(StepParams P) {
     extern __shared__ __align__(128) char stage_smem[];
     __shared__ ProgScalars s_sc;
     const int t = threadIdx.x;
@@ -387,7 +521,7 @@ __global__ void __launch_bounds__(GT, 4) step_direct_kernel(StepParams P) {
     if (t == 0) s_sc = load_scalars(P, n, hv, KDA);
     __syncthreads();
     const ProgScalars sc = s_sc;
-    if (sc.slot <= 0 || sc.h >= P.d.L || sc.h < 0) {
+    if (!prog_live(sc, P.d.L)) {
         if (t < 64) reinterpret_cast<uint32_t*>(P.o)[(int64_t(n) * P.d.HV + hv) * 64 + t] = 0u;
         return;
     }
@@ -411,15 +545,25 @@ __global__ void __launch_bounds__(GT, 4) step_direct_kernel(StepParams P) {
         copy16(st + lay.dtb, reinterpret_cast<const char*>(P.dt_bias + int64_t(hv) * KD), 512, t, GT);
     }
     __syncthreads();
+    if (t < 32) step_prologue<KDA>(P, sc, st, lay, t, [] {});
+    __syncthreads();
     const GroupScratch gs = carve_scratch(stage_smem + lay.bytes);
-    step_body<R, KDA>(P, sc, st, lay, gs, t, 1);
+    step_body<R, KDA>(P, sc, st, lay, gs, t, 1, [] {});
 }
 
 // ------------------------------------------------------------------------------------------------------------------
 // driver 2: persistent CTAs, producer warp + bulk asynchronous copies into a ring of stages
 // ------------------------------------------------------------------------------------------------------------------
+#ifdef LQ_TRACE
+// Debug build only: per (CTA, program) cycle stamps -- stage free / data landed / prologue done / program done.
+constexpr int TRACE_PROGS = 256;
+static __device__ long long g_trace[160 * TRACE_PROGS * 4];
+#define LQ_STAMP(i, k) do { if ((i) < TRACE_PROGS && blockIdx.x < 160) g_trace[(blockIdx.x * TRACE_PROGS + (i)) * 4 + (k)] = clock64(); } while (0)
+#else
+#define LQ_STAMP(i, k) do { } while (0)
+#endif
 constexpr uint32_t WAIT_LIMIT = 1u << 22;      // bounded spin: ~seconds at worst, then the kernel records a status and leaves
-constexpr int ST_PRODUCER_TIMEOUT = 1, ST_CONSUMER_TIMEOUT = 2;
+constexpr int ST_PRODUCER_TIMEOUT = 1, ST_CONSUMER_TIMEOUT = 2, ST_PROLOGUE_TIMEOUT = 4;
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return uint32_t(__cvta_generic_to_shared(p)); }
 __device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {
@@ -436,18 +580,24 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
     asm volatile(
         "{\n"
         ".reg .pred p;\n"
-        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n"
         "selp.u32 %0, 1, 0, p;\n"
         "}\n"
         : "=r"(ok)
-        : "r"(smem_u32(bar)), "r"(parity), "r"(2000u)
+        : "r"(smem_u32(bar)), "r"(parity)
         : "memory");
     return ok != 0;
 }
-// waits for the phase with the given parity; gives up after WAIT_LIMIT polls
-__device__ __forceinline__ bool mbar_wait_bounded(uint64_t* bar, uint32_t parity) {
-    for (uint32_t it = 0; it < WAIT_LIMIT; ++it)
-        if (mbar_try_wait(bar, parity)) return true;
+// A whole warp waits for the phase with the given parity: lane 0 tests the barrier, the outcome is broadcast, and every
+// lane takes the same branch, so the warp stays converged (a lane that spins alone leaves the warp split in two, and every
+// later warp-synchronous shuffle then costs a rendezvous of the halves).  Gives up after WAIT_LIMIT polls.
+__device__ __forceinline__ bool warp_wait_bounded(uint64_t* bar, uint32_t parity, int lane) {
+    for (uint32_t it = 0; it < WAIT_LIMIT; ++it) {
+        uint32_t ok = 0;
+        if (lane == 0) ok = mbar_try_wait(bar, parity) ? 1u : 0u;
+        ok = __shfl_sync(0xffffffffu, ok, 0);
+        if (ok) return true;
+    }
     return false;
 }
 // bulk asynchronous copy global -> this CTA's shared memory, completion counted in bytes on `bar`
@@ -473,13 +623,15 @@ __device__ __forceinline__ bool group_all(int bar, int nthreads, bool pred) {
     return r != 0;
 }
 
+// warp 0: producer, warp 1: prologue, warps 2 ..: NG consumer groups of GW warps
 template <int R, bool KDA, int NG>
-__global__ void __launch_bounds__(32 + NG * GT, 1) step_pipelined_kernel(StepParams P, int nstages) {
+__global__ void __launch_bounds__(64 + NG * GT, 1) step_pipelined_kernel(StepParams P, int nstages) {
     extern __shared__ __align__(128) char stage_smem[];
     const StageLayout lay = stage_layout(P.d.L, R, KDA);
     char* scratch0 = stage_smem + size_t(nstages) * lay.bytes;
     uint64_t* full = reinterpret_cast<uint64_t*>(scratch0 + NG * SCRATCH_BYTES);
-    uint64_t* empty = full + nstages;
+    uint64_t* normed = full + nstages;
+    uint64_t* empty = normed + nstages;
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int HV = P.d.HV, H = P.d.H, L = P.d.L;
     const int nprog = P.N * HV;
@@ -489,6 +641,7 @@ __global__ void __launch_bounds__(32 + NG * GT, 1) step_pipelined_kernel(StepPar
     if (tid == 0) {
         for (int s = 0; s < nstages; ++s) {
             mbar_init(full + s, 1);
+            mbar_init(normed + s, 32);
             mbar_init(empty + s, GT);
         }
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -500,6 +653,28 @@ __global__ void __launch_bounds__(32 + NG * GT, 1) step_pipelined_kernel(StepPar
         // ================= producer: scalars of 32 programs per batch, then one stage fill per program =================
         const int MIX = 2 * H * KD + HV * VD;
         const int gqa = HV / H;
+        // Per-lane copy descriptor, fixed for the whole kernel: lane k < ncopy issues copy k of every program from
+        //   src = base + slot * c_slot + hv * c_hv + n * c_n + hk * c_hk,   bytes = b_fix + h * b_h,   into stage + off.
+        const char* c_base = nullptr;
+        uint32_t c_slot = 0, c_hv = 0, c_n = 0, c_hk = 0, b_fix = 0, b_h = 0, c_off = 0;
+        {
+            const uint32_t rowb = uint32_t(L) * 256u;                    // one head's window rows (bf16 / f16) in bytes
+            switch (lane) {
+                case 0: c_base = P.ssm; c_slot = uint32_t(P.d.SS) * 4u; c_hv = VD * KD * 4u; b_fix = ck_bytes(R); c_off = 0; break;
+                case 1: c_base = reinterpret_cast<const char*>(P.Kbuf); c_slot = uint32_t(HV) * rowb; c_hv = rowb; b_h = 256u; c_off = lay.kb; break;
+                case 2: c_base = reinterpret_cast<const char*>(P.Ubuf); c_slot = uint32_t(HV) * rowb; c_hv = rowb; b_h = 256u; c_off = lay.ub; break;
+                case 3: c_base = reinterpret_cast<const char*>(P.Wbuf); c_slot = uint32_t(HV * L) * 4u; c_hv = uint32_t(L) * 4u; b_fix = uint32_t(L) * 4u; c_off = lay.w; break;
+                case 4: c_base = reinterpret_cast<const char*>(P.mixed); c_n = uint32_t(MIX) * 2u; c_hk = 256u; b_fix = 256u; c_off = lay.q; break;
+                case 5: c_base = reinterpret_cast<const char*>(P.mixed) + H * 256; c_n = uint32_t(MIX) * 2u; c_hk = 256u; b_fix = 256u; c_off = lay.k; break;
+                case 6: c_base = reinterpret_cast<const char*>(P.mixed) + 2 * H * 256; c_n = uint32_t(MIX) * 2u; c_hv = 256u; b_fix = 256u; c_off = lay.v; break;
+                case 7: if (KDA) { c_base = reinterpret_cast<const char*>(P.Gbuf); c_slot = uint32_t(HV) * rowb; c_hv = rowb; b_h = 256u; c_off = lay.gb; } break;
+                case 8: if (KDA) { c_base = reinterpret_cast<const char*>(P.Pbuf); c_slot = uint32_t(HV) * 512u; c_hv = 512u; b_fix = 512u; c_off = lay.pb; } break;
+                case 9: if (KDA) { c_base = reinterpret_cast<const char*>(P.a); c_n = uint32_t(HV) * 256u; c_hv = 256u; b_fix = 256u; c_off = lay.a; } break;
+                case 10: if (KDA) { c_base = reinterpret_cast<const char*>(P.dt_bias); c_hv = 512u; b_fix = 512u; c_off = lay.dtb; } break;
+                default: break;
+            }
+            __syncwarp();
+        }
         ProgScalars cur, nxt;
         auto fetch = [&](int i) {
             ProgScalars r;
@@ -521,6 +696,7 @@ __global__ void __launch_bounds__(32 + NG * GT, 1) step_pipelined_kernel(StepPar
                 const int i = base + j;
                 const int s = i % nstages;
                 const uint32_t u = uint32_t(i / nstages);
+                LQ_QSTAMP(0);
                 ProgScalars sc;
                 sc.slot = __shfl_sync(0xffffffffu, cur.slot, j);
                 sc.h = __shfl_sync(0xffffffffu, cur.h, j);
@@ -530,17 +706,17 @@ __global__ void __launch_bounds__(32 + NG * GT, 1) step_pipelined_kernel(StepPar
                 sc.beta = __shfl_sync(0xffffffffu, cur.beta, j);
                 sc.pold = __shfl_sync(0xffffffffu, cur.pold, j);
                 sc.ea = __shfl_sync(0xffffffffu, cur.ea, j);
-                int good = 1;
-                if (lane == 0) good = mbar_wait_bounded(empty + s, (u & 1u) ^ 1u) ? 1 : 0;
-                good = __shfl_sync(0xffffffffu, good, 0);
-                if (!good) {
+                LQ_QSTAMP(1);
+                if (!warp_wait_bounded(empty + s, (u & 1u) ^ 1u, lane)) {
                     if (lane == 0) atomicOr(&g_status, ST_PRODUCER_TIMEOUT);
                     ok = false;
                     break;
                 }
+                LQ_QSTAMP(2);
                 char* st = stage_smem + size_t(s) * lay.bytes;
-                const bool live = sc.slot > 0 && sc.h >= 0 && sc.h < L;
+                const bool live = prog_live(sc, L);
                 if (lane == 0) {
+                    LQ_STAMP(i, 0);
                     *reinterpret_cast<ProgScalars*>(st + lay.sc) = sc;
                     if (live) {
                         uint32_t bytes = ck_bytes(R) + 2u * uint32_t(sc.h) * 256u + uint32_t(L) * 4u + 3u * 256u;
@@ -551,65 +727,82 @@ __global__ void __launch_bounds__(32 + NG * GT, 1) step_pipelined_kernel(StepPar
                     }
                 }
                 __syncwarp();
+                LQ_QSTAMP(3);
                 if (live) {
-                    const int64_t sh = int64_t(sc.slot) * HV + sc.hv;
-                    const char* mrow = reinterpret_cast<const char*>(P.mixed + int64_t(sc.n) * MIX);
-                    const int hk = sc.hv / gqa;
-                    const uint32_t hb = uint32_t(sc.h) * 256u;
-                    switch (lane) {
-                        case 0: bulk_g2s(st, head_base(P.ssm, P.d.SS, sc.slot, sc.hv), ck_bytes(R), full + s); break;
-                        case 1: if (hb) bulk_g2s(st + lay.kb, P.Kbuf + sh * L * KD, hb, full + s); break;
-                        case 2: if (hb) bulk_g2s(st + lay.ub, P.Ubuf + sh * L * VD, hb, full + s); break;
-                        case 3: bulk_g2s(st + lay.w, P.Wbuf + sh * L, uint32_t(L) * 4u, full + s); break;
-                        case 4: bulk_g2s(st + lay.q, mrow + hk * 256, 256u, full + s); break;
-                        case 5: bulk_g2s(st + lay.k, mrow + (H + hk) * 256, 256u, full + s); break;
-                        case 6: bulk_g2s(st + lay.v, mrow + (2 * H + sc.hv) * 256, 256u, full + s); break;
-                        case 7: if (KDA && hb) bulk_g2s(st + lay.gb, P.Gbuf + sh * L * KD, hb, full + s); break;
-                        case 8: if (KDA) bulk_g2s(st + lay.pb, P.Pbuf + sh * KD, 512u, full + s); break;
-                        case 9: if (KDA) bulk_g2s(st + lay.a, P.a + (int64_t(sc.n) * HV + sc.hv) * KD, 256u, full + s); break;
-                        case 10: if (KDA) bulk_g2s(st + lay.dtb, P.dt_bias + int64_t(sc.hv) * KD, 512u, full + s); break;
-                        default: break;
-                    }
-                }
-            }
-        }
-        // Leave only after every stage this warp armed has been consumed (bounded): no copy of this CTA is then in flight.
-        if (lane == 0) {
-            const int last = ok ? nit : 0;
-            for (int s = 0; s < nstages && s < last; ++s) {
-                const int uses = (last - 1 - s) / nstages + 1;            // fills of stage s
-                if (!mbar_wait_bounded(empty + s, uint32_t(uses - 1) & 1u)) {
-                    atomicOr(&g_status, ST_PRODUCER_TIMEOUT);
-                    break;
+                    LQ_QSTAMP(4);
+                    const uint32_t hk = uint32_t(sc.hv) / uint32_t(gqa);
+                    const char* src = c_base + uint64_t(uint32_t(sc.slot)) * c_slot + uint64_t(uint32_t(sc.hv)) * c_hv +
+                                      uint64_t(uint32_t(sc.n)) * c_n + uint64_t(hk) * c_hk;
+                    const uint32_t bytes = b_fix + uint32_t(sc.h) * b_h;
+                    if (bytes) bulk_g2s(st + c_off, src, bytes, full + s);
+                    LQ_QSTAMP(5);
                 }
             }
         }
         return;
     }
 
+    if (warp == 1) {
+        // ================= prologue warp: every stage in fill order =================
+#ifdef LQ_TRACE
+        {   // calibration: 15 dependent shuffles on an idle SM
+            float x = float(lane) * 0.5f + float(bid);
+            const long long t0 = clock64() + (long long)(__float_as_uint(x) & 0u);
+            x = warp_sum(x); x = warp_sum(x * 0.5f); x = warp_sum(x * 0.25f);
+            const long long t1 = clock64() + (long long)(__float_as_uint(x) & 0u);
+            if (lane == 0 && bid < 160) { g_ntrace[(bid * 256 + 255) * 8 + 0] = t1 - t0; g_ntrace[(bid * 256 + 255) * 8 + 1] = (long long)x; }
+        }
+#endif
+        for (int i = 0; i < nit; ++i) {
+            const int s = i % nstages;
+            const uint32_t u = uint32_t(i / nstages);
+            if (!warp_wait_bounded(full + s, u & 1u, lane)) {
+                if (lane == 0) atomicOr(&g_status, ST_PROLOGUE_TIMEOUT);
+                return;
+            }
+            char* st = stage_smem + size_t(s) * lay.bytes;
+            const ProgScalars sc = *reinterpret_cast<const ProgScalars*>(st + lay.sc);
+            if (lane == 0) LQ_STAMP(i, 1);
+            if (prog_live(sc, L)) step_prologue<KDA>(P, sc, st, lay, lane, [&] { mbar_arrive(normed + s); }, i);
+            else mbar_arrive(normed + s);
+        }
+        return;
+    }
+
     // ================= consumers: group g takes programs g, g + NG, ... =================
-    const int g = (warp - 1) >> 2;
-    const int t = tid - 32 - g * GT;
+    const int g = (warp - 2) / GW;
+    const int t = tid - 64 - g * GT;
     const int bar = 1 + g;
     const GroupScratch gs = carve_scratch(scratch0 + g * SCRATCH_BYTES);
+    volatile int* gflag = reinterpret_cast<volatile int*>(empty + nstages) + g;
     for (int i = g; i < nit; i += NG) {
         const int s = i % nstages;
         const uint32_t u = uint32_t(i / nstages);
-        const bool got = mbar_wait_bounded(full + s, u & 1u);
-        if (!group_all(bar, GT, got)) {                 // uniform decision: nobody enters the body unless all saw the data
+        // one lane polls and publishes the outcome; the other warps sleep at the group barrier
+        if (t < 32) {
+            const bool got = warp_wait_bounded(normed + s, u & 1u, t);
+            if (t == 0) *gflag = got ? 1 : 0;
+        }
+        named_bar(bar, GT);
+        if (*gflag == 0) {                              // uniform decision: nobody enters the body unless the data is there
             if (t == 0) atomicOr(&g_status, ST_CONSUMER_TIMEOUT);
             return;
         }
         char* st = stage_smem + size_t(s) * lay.bytes;
         const ProgScalars sc = *reinterpret_cast<const ProgScalars*>(st + lay.sc);
-        if (sc.slot > 0 && sc.h >= 0 && sc.h < L) {
-            step_body<R, KDA>(P, sc, st, lay, gs, t, bar);
+        if (t == 0) LQ_STAMP(i, 2);
+        auto release = [&] {
+            fence_async_smem();                          // generic-proxy accesses to the stage before the next bulk copy lands
+            mbar_arrive(empty + s);
+        };
+        if (prog_live(sc, L)) {
+            step_body<R, KDA>(P, sc, st, lay, gs, t, bar, release, i);
         } else {
+            release();
             const int p = bid + i * grid;
             if (t < 64) reinterpret_cast<uint32_t*>(P.o)[int64_t(p) * 64 + t] = 0u;
         }
-        fence_async_smem();                              // generic-proxy accesses to the stage before the next bulk copy lands
-        mbar_arrive(empty + s);
+        if (t == 0) LQ_STAMP(i, 3);
     }
 }
 
@@ -628,16 +821,16 @@ static int launch_step(const StepParams& P, cudaStream_t st) {
     }
     constexpr int NG = 2;
     const size_t budget = 227 * 1024;
-    const size_t fixed = size_t(NG) * SCRATCH_BYTES + 2 * 16 * sizeof(uint64_t);
+    const size_t fixed = size_t(NG) * SCRATCH_BYTES + 3 * 16 * sizeof(uint64_t) + 64;
     int nstages = int((budget - fixed) / size_t(lay.bytes));
     if (nstages > 16) nstages = 16;
     if (nstages < 2) return LQ_ERR_UNSUPPORTED;
-    const size_t smem = size_t(nstages) * lay.bytes + size_t(NG) * SCRATCH_BYTES + 2 * size_t(nstages) * sizeof(uint64_t);
+    const size_t smem = size_t(nstages) * lay.bytes + size_t(NG) * SCRATCH_BYTES + 3 * size_t(nstages) * sizeof(uint64_t) + 64;
     int rc = ensure_smem((const void*)step_pipelined_kernel<R, KDA, NG>, smem);
     if (rc) return rc;
     const int nprog = P.N * P.d.HV;
     const int grid = nprog < device_sm_count() ? nprog : device_sm_count();
-    step_pipelined_kernel<R, KDA, NG><<<grid, 32 + NG * GT, smem, st>>>(P, nstages);
+    step_pipelined_kernel<R, KDA, NG><<<grid, 64 + NG * GT, smem, st>>>(P, nstages);
     return finish_launch();
 }
 
@@ -668,6 +861,21 @@ static int step_common(const lq_dims* d, void* ssm, void* Kbuf, void* Ubuf, floa
 }
 
 }  // namespace lq
+
+#ifdef LQ_TRACE
+extern "C" int lq_debug_read_trace(long long* out, int n) {
+    return cudaMemcpyFromSymbol(out, lq::g_trace, sizeof(long long) * n) == cudaSuccess ? 0 : -5;
+}
+extern "C" int lq_debug_read_qtrace(long long* out, int n) {
+    return cudaMemcpyFromSymbol(out, lq::g_qtrace, sizeof(long long) * n) == cudaSuccess ? 0 : -5;
+}
+extern "C" int lq_debug_read_ntrace(long long* out, int n) {
+    return cudaMemcpyFromSymbol(out, lq::g_ntrace, sizeof(long long) * n) == cudaSuccess ? 0 : -5;
+}
+extern "C" int lq_debug_read_ptrace(long long* out, int n) {
+    return cudaMemcpyFromSymbol(out, lq::g_ptrace, sizeof(long long) * n) == cudaSuccess ? 0 : -5;
+}
+#endif
 
 extern "C" int lq_set_option(const char* name, int32_t value) {
     if (!name) return LQ_ERR_NULL;
