@@ -32,9 +32,10 @@ WORKLOADS = {
     "gdn": dict(name="gdn_decode_H16_HV32_d128_L64_R4", H=16, HV=32, L=64, R=4, B=256, kda=False),
     "kda": dict(name="kda_decode_H32_HV32_d128_L32_R8", H=32, HV=32, L=32, R=8, B=128, kda=True),
 }
-# DRAM bytes (read + write) per step-kernel launch from an ncu capture of this workload, per (sequence, head) program;
-# None until a capture has been summarised under profiles/.
-NCU_TRAFFIC_PER_PROGRAM = {"gdn": None, "kda": None}
+# DRAM bytes (read + write) of the step kernel relative to its algorithmic bytes, from the ncu capture summarised in
+# profiles/step_pipelined_gdn_B128_ncu.md (150.05 MB + 5.40 MB for 4 096 programs at h = 33 vs 37 928 B algorithmic per
+# program).  `roofline.traffic` scales the live algorithmic bytes per launch by this ratio.  None = not captured.
+NCU_TRAFFIC_RATIO = {"gdn": 1.0006, "kda": None}
 
 
 def step_bytes(h, L, R, gqa, kda):
@@ -354,7 +355,7 @@ def run_b200(args, wl):
         pass
     peak = float(peaks.get("hbm_gbs", 6650.0))
     achieved = alg_launch / (step_ms * 1e-3) / 1e9
-    traffic = NCU_TRAFFIC_PER_PROGRAM["kda" if kda else "gdn"]
+    traffic = NCU_TRAFFIC_RATIO["kda" if kda else "gdn"]
 
     if world > 1:
         tt = torch.tensor([dt, dt_e2e], device=device, dtype=torch.float64)
@@ -382,7 +383,7 @@ def run_b200(args, wl):
                 "gpu_launches": 2 * done,
                 "roofline": {"bound": "hbm", "kernel": "step_pipelined_kernel", "achieved": achieved, "peak": peak,
                              "unit": "GB/s", "frac": achieved / peak, "frac_of_8tbs": achieved / 8000.0,
-                             "traffic": (traffic * B * HV) if traffic else None, "alg_bytes_per_launch": alg_launch,
+                             "traffic": (traffic * alg_launch) if traffic else None, "alg_bytes_per_launch": alg_launch,
                              "ms_per_launch": step_ms, "peak_source": "MEASURED_PEAKS.json" if peaks else "fallback"},
                 "clocks": clocks}
         if cpu_rate is not None:
