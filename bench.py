@@ -241,6 +241,11 @@ class Layer:
         else:
             st.kstep(v["q32"], v["Sk"], v["Sv"], v["skv"], st.Kbuf, st.Ubuf, st.Wbuf, st.Pbuf, st.hcnt, *args)
 
+    def flush_only(self):
+        st, v = self.st, self.st.views(self.ssm)
+        st.kflush(v["q32"], v["Sk"], v["Sv"], v["skv"], st.Kbuf, st.Ubuf, st.Wbuf, st.Pbuf, st.Gbuf if st.kda else st.Gd,
+                  st.hcnt, v["sq16"], v["uq"], st.Q0, self.idx)
+
     def h2d_bytes(self):
         return sum(t[0].numel() * t.element_size() for t in (self.h_mixed, self.h_a, self.h_b))
 
@@ -347,6 +352,14 @@ def run_b200(args, wl):
         if r > 0:
             tk += x
     step_ms = 1e3 * tk / (reps * L)
+    # ---- the flush kernel alone: every head due (state left by the last pass above), then nothing due ----
+    flush_all_ms = 1e3 * timed(lambda: layer.flush_only(), torch.cuda.current_stream())
+
+    def body_f():
+        for _ in range(20):
+            layer.flush_only()
+
+    flush_idle_ms = 1e3 * timed(body_f, torch.cuda.current_stream()) / 20
     alg_launch = B * HV * sum(step_bytes(h, L, R, gqa, kda) for h in range(L)) / L
     peaks = {}
     try:
@@ -385,6 +398,8 @@ def run_b200(args, wl):
                              "unit": "GB/s", "frac": achieved / peak, "frac_of_8tbs": achieved / 8000.0,
                              "traffic": (traffic * alg_launch) if traffic else None, "alg_bytes_per_launch": alg_launch,
                              "ms_per_launch": step_ms, "peak_source": "MEASURED_PEAKS.json" if peaks else "fallback"},
+                "flush": {"all_due_ms": flush_all_ms, "none_due_ms": flush_idle_ms,
+                          "all_due_gbs": B * HV * flush_bytes(L, R, kda) / (flush_all_ms * 1e-3) / 1e9},
                 "clocks": clocks}
         if cpu_rate is not None:
             line["cpu_baseline"] = {"value": cpu_rate, "unit": "head-steps/s", "cores": os.cpu_count() or 1, "kind": "port",
@@ -403,8 +418,12 @@ def main():
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--workload", default="gdn", choices=sorted(WORKLOADS))
     ap.add_argument("--batch", type=int, default=0)
+    ap.add_argument("--step-impl", type=int, default=-1, help="debug: step kernel driver (see lq_set_option)")
     args = ap.parse_args()
     wl = WORKLOADS[args.workload]
+    if args.step_impl >= 0:
+        from leapquant_b200 import _lib
+        _lib.set_option("step_impl", args.step_impl)
     if args.impl == "reference":
         run_reference(args, wl)
     else:

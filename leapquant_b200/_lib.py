@@ -9,7 +9,8 @@ import os
 import torch
 
 _HERE = os.path.dirname(os.path.abspath(__file__))
-LIB_PATH = os.path.join(_HERE, "libleapquant_b200.so")
+# LEAPQUANT_B200_LIB points at another build of the same library (e.g. one compiled with different tuning macros)
+LIB_PATH = os.environ.get("LEAPQUANT_B200_LIB") or os.path.join(_HERE, "libleapquant_b200.so")
 
 EXPORTS = ("lq_version", "lq_strerror", "lq_last_cuda_error", "lq_device_status", "lq_set_option", "lq_gdn_step", "lq_kda_step",
            "lq_flush", "lq_quantize", "lq_dequant", "lq_lowrank")

@@ -12,7 +12,7 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 PKG = os.path.dirname(HERE)
 LIB = os.path.join(PKG, "libleapquant_b200.so")
 SOURCES = ["leapquant_b200.cu"]
-DEPS = ["lq_abi.cu", "lq_quant.cu", "lq_flush.cu", "lq_step.cu", "lq_common.cuh", "lq_linalg.cuh",
+DEPS = ["lq_abi.cu", "lq_quant.cu", "lq_flush.cu", "lq_step.cu", "lq_common.cuh", "lq_linalg.cuh", "lq_step_warp.cuh",
         os.path.join("..", "..", "include", "leapquant_b200.h")]
 
 

@@ -15,29 +15,38 @@
 
 #include "lq_common.cuh"
 
+#ifndef LQ_GW
+#define LQ_GW 4       // warps per consumer group
+#endif
+#ifndef LQ_NG
+#define LQ_NG 3       // consumer groups per CTA
+#endif
+
 namespace lq {
 
-constexpr int GW = 8;                     // warps of one consumer group (a group executes one program at a time)
+constexpr int GW = LQ_GW;                 // warps of one consumer group (a group executes one program at a time)
 constexpr int GT = 32 * GW;               // its threads
 constexpr int NPASS = 32 / GW;            // tile passes per warp (four 128-byte rows per pass)
 static_assert(GW == 4 || GW == 8, "the reductions below are written for 4 or 8 warps per group");
 
-// ---- stage layout (bytes); the checkpoint part mirrors the packed slot so that it is ONE contiguous copy ----
+// ---- stage layout (bytes) of a program with `rows` window rows; the checkpoint part mirrors the packed slot so that it
+//      is ONE contiguous copy.  The pipelined driver sizes every stage for the program's live rows (rows = h), so that a
+//      ring of 220 KB holds ~6 average programs instead of 4 worst-case ones. ----
 struct StageLayout {
     int kb, ub, w, q, k, v, gb, pb, a, dtb, nrm, sc, bytes;
 };
-__host__ __device__ inline StageLayout stage_layout(int L, int R, bool kda) {
+__host__ __device__ inline StageLayout stage_layout(int rows, int L, int R, bool kda) {
     StageLayout s;
     int o = ck_bytes(R);
-    s.kb = o; o += L * 256;
-    s.ub = o; o += L * 256;
-    s.w = o; o += 256;
+    s.kb = o; o += rows * 256;
+    s.ub = o; o += rows * 256;
+    s.w = o; o += L * 4;
     s.q = o; o += 256;
     s.k = o; o += 256;
     s.v = o; o += 256;
     s.gb = s.pb = s.a = s.dtb = 0;
     if (kda) {
-        s.gb = o; o += L * 256;
+        s.gb = o; o += rows * 256;
         s.pb = o; o += 512;
         s.a = o; o += 256;
         s.dtb = o; o += 512;
@@ -430,16 +439,16 @@ __device__ __forceinline__ void step_body(const StepParams& P, const ProgScalars
     named_bar(bar, GT);
     LQ_PSTAMP(5);
 
-    // ---- contribution of the window and of the rank-R part.  A warp owns 64 / GW value pairs; within it lane & 7 picks
-    //      the pair and lane >> 3 the phase of j (j mod 4); the four phases are combined with two shuffles. ----
-    constexpr int VPW = 64 / GW;                             // value pairs per warp (8, or 16 with two per lane)
-    static_assert(VPW == 8, "the contribution mapping assumes eight warps per group");
-    const int vp = VPW * w + l8, jh = g;
+    // ---- contribution of the window and of the rank-R part.  A warp owns VPW = 64 / GW value pairs; lane % VPW picks the
+    //      pair and lane / VPW the phase of j; the phases are combined with shuffles. ----
+    constexpr int VPW = 64 / GW;                             // value pairs per warp
+    constexpr int NPH = 32 / VPW;                            // phases of j handled by the lanes of one value pair
+    const int vp = VPW * w + (lane % VPW), jh = lane / VPW;
     float2 ck = make_float2(0.f, 0.f), cq = make_float2(0.f, 0.f), rk = make_float2(0.f, 0.f), rq = make_float2(0.f, 0.f);
     {
         const uint32_t* ub = reinterpret_cast<const uint32_t*>(st + lay.ub);
 #pragma unroll 4
-        for (int j = jh; j < h; j += 4) {
+        for (int j = jh; j < h; j += NPH) {
             const float2 u2 = bf16x2_to_f2(ub[j * 64 + vp]);
             const float2 wd = gs.wd[j];
             ck = __ffma2_rn(u2, make_float2(wd.x, wd.x), ck);
@@ -447,7 +456,7 @@ __device__ __forceinline__ void step_body(const StepParams& P, const ProgScalars
         }
         const uint32_t* uq = reinterpret_cast<const uint32_t*>(st + CK_UQ);
 #pragma unroll
-        for (int r = jh; r < R; r += 4) {
+        for (int r = jh; r < R; r += NPH) {
             const float2 q2 = f16x2_to_f2(uq[r * 128 + 64 + vp]);
             const float2 dd = gs.wd[64 + r];
             rk = __ffma2_rn(q2, make_float2(dd.x, dd.x), rk);
@@ -455,7 +464,7 @@ __device__ __forceinline__ void step_body(const StepParams& P, const ProgScalars
         }
     }
 #pragma unroll
-    for (int o = 8; o <= 16; o <<= 1) {
+    for (int o = VPW; o < 32; o <<= 1) {
         ck.x += __shfl_xor_sync(0xffffffffu, ck.x, o); ck.y += __shfl_xor_sync(0xffffffffu, ck.y, o);
         cq.x += __shfl_xor_sync(0xffffffffu, cq.x, o); cq.y += __shfl_xor_sync(0xffffffffu, cq.y, o);
         rk.x += __shfl_xor_sync(0xffffffffu, rk.x, o); rk.y += __shfl_xor_sync(0xffffffffu, rk.y, o);
@@ -517,10 +526,10 @@ __global__ void __launch_bounds__(GT, 2) step_direct_kernel(StepParams P) {
     const int t = threadIdx.x;
     const int prog = blockIdx.x;
     const int n = prog / P.d.HV, hv = prog - n * P.d.HV;
-    const StageLayout lay = stage_layout(P.d.L, R, KDA);
     if (t == 0) s_sc = load_scalars(P, n, hv, KDA);
     __syncthreads();
     const ProgScalars sc = s_sc;
+    const StageLayout lay = stage_layout(prog_live(sc, P.d.L) ? sc.h : 0, P.d.L, R, KDA);
     if (!prog_live(sc, P.d.L)) {
         if (t < 64) reinterpret_cast<uint32_t*>(P.o)[(int64_t(n) * P.d.HV + hv) * 64 + t] = 0u;
         return;
@@ -547,9 +556,11 @@ __global__ void __launch_bounds__(GT, 2) step_direct_kernel(StepParams P) {
     __syncthreads();
     if (t < 32) step_prologue<KDA>(P, sc, st, lay, t, [] {});
     __syncthreads();
-    const GroupScratch gs = carve_scratch(stage_smem + lay.bytes);
+    const GroupScratch gs = carve_scratch(stage_smem + stage_layout(P.d.L, P.d.L, R, KDA).bytes);
     step_body<R, KDA>(P, sc, st, lay, gs, t, 1, [] {});
 }
+
+#include "lq_step_warp.cuh"
 
 // ------------------------------------------------------------------------------------------------------------------
 // driver 2: persistent CTAs, producer warp + bulk asynchronous copies into a ring of stages
@@ -623,15 +634,23 @@ __device__ __forceinline__ bool group_all(int bar, int nthreads, bool pred) {
     return r != 0;
 }
 
-// warp 0: producer, warp 1: prologue, warps 2 ..: NG consumer groups of GW warps
+// warp 0: producer, warp 1: prologue, warps 2 ..: NG consumer groups of GW warps.
+// Shared memory: [ring of `ring_bytes`][NG group scratches][ND x (full, normed, empty) mbarriers][ND stage offsets][NG flags]
+// [ND stage row counts].
+// Program i (CTA-local sequence number) uses descriptor i % ND: three mbarriers and the offset of its stage in the ring.
+// Stages are carved from the ring in order, each sized for its program's live window rows, and reclaimed in order.
+constexpr int ND = 8;                          // descriptors = most programs resident in the ring at once
+
 template <int R, bool KDA, int NG>
-__global__ void __launch_bounds__(64 + NG * GT, 1) step_pipelined_kernel(StepParams P, int nstages) {
+__global__ void __launch_bounds__(64 + NG * GT, 1) step_pipelined_kernel(StepParams P, int ring_bytes) {
     extern __shared__ __align__(128) char stage_smem[];
-    const StageLayout lay = stage_layout(P.d.L, R, KDA);
-    char* scratch0 = stage_smem + size_t(nstages) * lay.bytes;
+    char* scratch0 = stage_smem + ring_bytes;
     uint64_t* full = reinterpret_cast<uint64_t*>(scratch0 + NG * SCRATCH_BYTES);
-    uint64_t* normed = full + nstages;
-    uint64_t* empty = normed + nstages;
+    uint64_t* normed = full + ND;
+    uint64_t* empty = normed + ND;
+    volatile int* doff = reinterpret_cast<volatile int*>(empty + ND);
+    volatile int* gflag0 = doff + ND;
+    ProgScalars* pbatch = reinterpret_cast<ProgScalars*>(const_cast<int*>(doff) + 2 * ND + NG + 2);      // [32], 8-byte aligned
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int HV = P.d.HV, H = P.d.H, L = P.d.L;
     const int nprog = P.N * HV;
@@ -639,7 +658,7 @@ __global__ void __launch_bounds__(64 + NG * GT, 1) step_pipelined_kernel(StepPar
     const int nit = (nprog - bid + grid - 1) / grid;
 
     if (tid == 0) {
-        for (int s = 0; s < nstages; ++s) {
+        for (int s = 0; s < ND; ++s) {
             mbar_init(full + s, 1);
             mbar_init(normed + s, 32);
             mbar_init(empty + s, GT);
@@ -654,25 +673,33 @@ __global__ void __launch_bounds__(64 + NG * GT, 1) step_pipelined_kernel(StepPar
         const int MIX = 2 * H * KD + HV * VD;
         const int gqa = HV / H;
         // Per-lane copy descriptor, fixed for the whole kernel: lane k < ncopy issues copy k of every program from
-        //   src = base + slot * c_slot + hv * c_hv + n * c_n + hk * c_hk,   bytes = b_fix + h * b_h,   into stage + off.
+        //   src = base + slot * c_slot + hv * c_hv + n * c_n + hk * c_hk,   bytes = b_fix + h * b_h,
+        // into stage + o_fix + h * o_h (the stage layout moves with the live rows h).
         const char* c_base = nullptr;
-        uint32_t c_slot = 0, c_hv = 0, c_n = 0, c_hk = 0, b_fix = 0, b_h = 0, c_off = 0;
+        uint32_t c_slot = 0, c_hv = 0, c_n = 0, c_hk = 0, b_fix = 0, b_h = 0, o_fix = 0, o_h = 0;
         {
             const uint32_t rowb = uint32_t(L) * 256u;                    // one head's window rows (bf16 / f16) in bytes
+            const StageLayout l0 = stage_layout(0, L, R, KDA), l1 = stage_layout(1, L, R, KDA);
+            int which = -1;                                              // member of the layout this lane copies into
             switch (lane) {
-                case 0: c_base = P.ssm; c_slot = uint32_t(P.d.SS) * 4u; c_hv = VD * KD * 4u; b_fix = ck_bytes(R); c_off = 0; break;
-                case 1: c_base = reinterpret_cast<const char*>(P.Kbuf); c_slot = uint32_t(HV) * rowb; c_hv = rowb; b_h = 256u; c_off = lay.kb; break;
-                case 2: c_base = reinterpret_cast<const char*>(P.Ubuf); c_slot = uint32_t(HV) * rowb; c_hv = rowb; b_h = 256u; c_off = lay.ub; break;
-                case 3: c_base = reinterpret_cast<const char*>(P.Wbuf); c_slot = uint32_t(HV * L) * 4u; c_hv = uint32_t(L) * 4u; b_fix = uint32_t(L) * 4u; c_off = lay.w; break;
-                case 4: c_base = reinterpret_cast<const char*>(P.mixed); c_n = uint32_t(MIX) * 2u; c_hk = 256u; b_fix = 256u; c_off = lay.q; break;
-                case 5: c_base = reinterpret_cast<const char*>(P.mixed) + H * 256; c_n = uint32_t(MIX) * 2u; c_hk = 256u; b_fix = 256u; c_off = lay.k; break;
-                case 6: c_base = reinterpret_cast<const char*>(P.mixed) + 2 * H * 256; c_n = uint32_t(MIX) * 2u; c_hv = 256u; b_fix = 256u; c_off = lay.v; break;
-                case 7: if (KDA) { c_base = reinterpret_cast<const char*>(P.Gbuf); c_slot = uint32_t(HV) * rowb; c_hv = rowb; b_h = 256u; c_off = lay.gb; } break;
-                case 8: if (KDA) { c_base = reinterpret_cast<const char*>(P.Pbuf); c_slot = uint32_t(HV) * 512u; c_hv = 512u; b_fix = 512u; c_off = lay.pb; } break;
-                case 9: if (KDA) { c_base = reinterpret_cast<const char*>(P.a); c_n = uint32_t(HV) * 256u; c_hv = 256u; b_fix = 256u; c_off = lay.a; } break;
-                case 10: if (KDA) { c_base = reinterpret_cast<const char*>(P.dt_bias); c_hv = 512u; b_fix = 512u; c_off = lay.dtb; } break;
+                case 0: c_base = P.ssm; c_slot = uint32_t(P.d.SS) * 4u; c_hv = VD * KD * 4u; b_fix = ck_bytes(R); break;
+                case 1: c_base = reinterpret_cast<const char*>(P.Kbuf); c_slot = uint32_t(HV) * rowb; c_hv = rowb; b_h = 256u; which = 0; break;
+                case 2: c_base = reinterpret_cast<const char*>(P.Ubuf); c_slot = uint32_t(HV) * rowb; c_hv = rowb; b_h = 256u; which = 1; break;
+                case 3: c_base = reinterpret_cast<const char*>(P.Wbuf); c_slot = uint32_t(HV * L) * 4u; c_hv = uint32_t(L) * 4u; b_fix = uint32_t(L) * 4u; which = 2; break;
+                case 4: c_base = reinterpret_cast<const char*>(P.mixed); c_n = uint32_t(MIX) * 2u; c_hk = 256u; b_fix = 256u; which = 3; break;
+                case 5: c_base = reinterpret_cast<const char*>(P.mixed) + H * 256; c_n = uint32_t(MIX) * 2u; c_hk = 256u; b_fix = 256u; which = 4; break;
+                case 6: c_base = reinterpret_cast<const char*>(P.mixed) + 2 * H * 256; c_n = uint32_t(MIX) * 2u; c_hv = 256u; b_fix = 256u; which = 5; break;
+                case 7: if (KDA) { c_base = reinterpret_cast<const char*>(P.Gbuf); c_slot = uint32_t(HV) * rowb; c_hv = rowb; b_h = 256u; which = 6; } break;
+                case 8: if (KDA) { c_base = reinterpret_cast<const char*>(P.Pbuf); c_slot = uint32_t(HV) * 512u; c_hv = 512u; b_fix = 512u; which = 7; } break;
+                case 9: if (KDA) { c_base = reinterpret_cast<const char*>(P.a); c_n = uint32_t(HV) * 256u; c_hv = 256u; b_fix = 256u; which = 8; } break;
+                case 10: if (KDA) { c_base = reinterpret_cast<const char*>(P.dt_bias); c_hv = 512u; b_fix = 512u; which = 9; } break;
                 default: break;
             }
+            const int m0[10] = {l0.kb, l0.ub, l0.w, l0.q, l0.k, l0.v, l0.gb, l0.pb, l0.a, l0.dtb};
+            const int m1[10] = {l1.kb, l1.ub, l1.w, l1.q, l1.k, l1.v, l1.gb, l1.pb, l1.a, l1.dtb};
+#pragma unroll
+            for (int k = 0; k < 10; ++k)
+                if (which == k) { o_fix = uint32_t(m0[k]); o_h = uint32_t(m1[k] - m0[k]); }
             __syncwarp();
         }
         ProgScalars cur, nxt;
@@ -687,43 +714,66 @@ __global__ void __launch_bounds__(64 + NG * GT, 1) step_pipelined_kernel(StepPar
             return r;
         };
         nxt = fetch(lane);
+        int head = 0, tail = 0;                                  // next free ring byte; oldest program not yet reclaimed
+        int r_off = 0, r_end = 0;                                // this lane keeps (offset, end) of program `lane`-th descriptor
         bool ok = true;
         for (int base = 0; base < nit && ok; base += 32) {
             cur = nxt;
+            __syncwarp();
+            pbatch[lane] = cur;                                  // the batch's scalars, one entry per lane
+            __syncwarp();
             nxt = fetch(base + 32 + lane);
             const int cnt = min(32, nit - base);
             for (int j = 0; j < cnt; ++j) {
                 const int i = base + j;
-                const int s = i % nstages;
-                const uint32_t u = uint32_t(i / nstages);
+                const int dsc = i % ND;
                 LQ_QSTAMP(0);
-                ProgScalars sc;
-                sc.slot = __shfl_sync(0xffffffffu, cur.slot, j);
-                sc.h = __shfl_sync(0xffffffffu, cur.h, j);
-                sc.n = __shfl_sync(0xffffffffu, cur.n, j);
-                sc.hv = __shfl_sync(0xffffffffu, cur.hv, j);
-                sc.alpha = __shfl_sync(0xffffffffu, cur.alpha, j);
-                sc.beta = __shfl_sync(0xffffffffu, cur.beta, j);
-                sc.pold = __shfl_sync(0xffffffffu, cur.pold, j);
-                sc.ea = __shfl_sync(0xffffffffu, cur.ea, j);
+                const ProgScalars sc = *const_cast<const ProgScalars*>(&pbatch[j]);      // broadcast read
+                const bool live = prog_live(sc, L);
+                const int rows = live ? sc.h : 0;
+                const int size = stage_layout(rows, L, R, KDA).bytes;
+                // place the stage: at the head, or at the start of the ring if it does not fit before the end
+                const int off = (head + size <= ring_bytes) ? head : 0;
+                // in-flight programs tail .. i-1 keep (offset, end) in lane (program % ND); find the newest one that the new
+                // stage [off, off + size) would overwrite -- and every program from i - ND on, whose descriptor is needed
+                int need = max(tail, i - ND + 1);
+                {
+                    const int jprog = i - 1 - ((i - 1 - lane) & (ND - 1)) ;   // newest program < i whose descriptor is `lane`
+                    const bool mine = lane < ND && jprog >= tail && jprog >= 0;
+                    const bool hit = mine && r_off < off + size && off < r_end;
+                    const uint32_t hits = __ballot_sync(0xffffffffu, hit);
+                    int newest = -1;
+#pragma unroll
+                    for (int k = 0; k < ND; ++k) {
+                        const int jp = i - 1 - ((i - 1 - k) & (ND - 1));
+                        if ((hits >> k) & 1u) newest = max(newest, jp);
+                    }
+                    need = max(need, newest + 1);
+                }
                 LQ_QSTAMP(1);
-                if (!warp_wait_bounded(empty + s, (u & 1u) ^ 1u, lane)) {
+                while (tail < need) {                            // reclaim in order
+                    if (!warp_wait_bounded(empty + (tail % ND), uint32_t(tail / ND) & 1u, lane)) { ok = false; break; }
+                    ++tail;
+                }
+                if (!ok) {
                     if (lane == 0) atomicOr(&g_status, ST_PRODUCER_TIMEOUT);
-                    ok = false;
                     break;
                 }
                 LQ_QSTAMP(2);
-                char* st = stage_smem + size_t(s) * lay.bytes;
-                const bool live = prog_live(sc, L);
+                if (lane == dsc) { r_off = off; r_end = off + size; }
+                head = off + size;
+                char* st = stage_smem + off;
                 if (lane == 0) {
                     LQ_STAMP(i, 0);
-                    *reinterpret_cast<ProgScalars*>(st + lay.sc) = sc;
+                    doff[dsc] = off;
+                    doff[ND + NG + dsc] = rows;
+                    *reinterpret_cast<ProgScalars*>(st + stage_layout(rows, L, R, KDA).sc) = sc;
                     if (live) {
                         uint32_t bytes = ck_bytes(R) + 2u * uint32_t(sc.h) * 256u + uint32_t(L) * 4u + 3u * 256u;
                         if (KDA) bytes += uint32_t(sc.h) * 256u + 512u + 256u + 512u;
-                        mbar_arrive_expect_tx(full + s, bytes);
+                        mbar_arrive_expect_tx(full + dsc, bytes);
                     } else {
-                        mbar_arrive(full + s);
+                        mbar_arrive(full + dsc);
                     }
                 }
                 __syncwarp();
@@ -734,7 +784,7 @@ __global__ void __launch_bounds__(64 + NG * GT, 1) step_pipelined_kernel(StepPar
                     const char* src = c_base + uint64_t(uint32_t(sc.slot)) * c_slot + uint64_t(uint32_t(sc.hv)) * c_hv +
                                       uint64_t(uint32_t(sc.n)) * c_n + uint64_t(hk) * c_hk;
                     const uint32_t bytes = b_fix + uint32_t(sc.h) * b_h;
-                    if (bytes) bulk_g2s(st + c_off, src, bytes, full + s);
+                    if (bytes) bulk_g2s(st + o_fix + uint32_t(sc.h) * o_h, src, bytes, full + dsc);
                     LQ_QSTAMP(5);
                 }
             }
@@ -743,28 +793,23 @@ __global__ void __launch_bounds__(64 + NG * GT, 1) step_pipelined_kernel(StepPar
     }
 
     if (warp == 1) {
-        // ================= prologue warp: every stage in fill order =================
-#ifdef LQ_TRACE
-        {   // calibration: 15 dependent shuffles on an idle SM
-            float x = float(lane) * 0.5f + float(bid);
-            const long long t0 = clock64() + (long long)(__float_as_uint(x) & 0u);
-            x = warp_sum(x); x = warp_sum(x * 0.5f); x = warp_sum(x * 0.25f);
-            const long long t1 = clock64() + (long long)(__float_as_uint(x) & 0u);
-            if (lane == 0 && bid < 160) { g_ntrace[(bid * 256 + 255) * 8 + 0] = t1 - t0; g_ntrace[(bid * 256 + 255) * 8 + 1] = (long long)x; }
-        }
-#endif
+        // ================= prologue warp: every program in fill order =================
         for (int i = 0; i < nit; ++i) {
-            const int s = i % nstages;
-            const uint32_t u = uint32_t(i / nstages);
-            if (!warp_wait_bounded(full + s, u & 1u, lane)) {
+            const int dsc = i % ND;
+            if (!warp_wait_bounded(full + dsc, uint32_t(i / ND) & 1u, lane)) {
                 if (lane == 0) atomicOr(&g_status, ST_PROLOGUE_TIMEOUT);
                 return;
             }
-            char* st = stage_smem + size_t(s) * lay.bytes;
-            const ProgScalars sc = *reinterpret_cast<const ProgScalars*>(st + lay.sc);
+            char* st = stage_smem + doff[dsc];
+            const int rows = doff[ND + NG + dsc];                  // rows the stage was sized for (h, or 0 for a dead program)
+            const ProgScalars sc = *reinterpret_cast<const ProgScalars*>(st + stage_layout(rows, L, R, KDA).sc);
             if (lane == 0) LQ_STAMP(i, 1);
-            if (prog_live(sc, L)) step_prologue<KDA>(P, sc, st, lay, lane, [&] { mbar_arrive(normed + s); }, i);
-            else mbar_arrive(normed + s);
+            if (prog_live(sc, L)) {
+                const StageLayout lay = stage_layout(sc.h, L, R, KDA);
+                step_prologue<KDA>(P, sc, st, lay, lane, [&] { mbar_arrive(normed + dsc); }, i);
+            } else {
+                mbar_arrive(normed + dsc);
+            }
         }
         return;
     }
@@ -774,13 +819,12 @@ __global__ void __launch_bounds__(64 + NG * GT, 1) step_pipelined_kernel(StepPar
     const int t = tid - 64 - g * GT;
     const int bar = 1 + g;
     const GroupScratch gs = carve_scratch(scratch0 + g * SCRATCH_BYTES);
-    volatile int* gflag = reinterpret_cast<volatile int*>(empty + nstages) + g;
+    volatile int* gflag = gflag0 + g;
     for (int i = g; i < nit; i += NG) {
-        const int s = i % nstages;
-        const uint32_t u = uint32_t(i / nstages);
-        // one lane polls and publishes the outcome; the other warps sleep at the group barrier
+        const int dsc = i % ND;
+        // one warp polls and publishes the outcome; the other warps sleep at the group barrier
         if (t < 32) {
-            const bool got = warp_wait_bounded(normed + s, u & 1u, t);
+            const bool got = warp_wait_bounded(normed + dsc, uint32_t(i / ND) & 1u, t);
             if (t == 0) *gflag = got ? 1 : 0;
         }
         named_bar(bar, GT);
@@ -788,12 +832,14 @@ __global__ void __launch_bounds__(64 + NG * GT, 1) step_pipelined_kernel(StepPar
             if (t == 0) atomicOr(&g_status, ST_CONSUMER_TIMEOUT);
             return;
         }
-        char* st = stage_smem + size_t(s) * lay.bytes;
+        char* st = stage_smem + doff[dsc];
+        const int rows = doff[ND + NG + dsc];
+        const StageLayout lay = stage_layout(rows, L, R, KDA);
         const ProgScalars sc = *reinterpret_cast<const ProgScalars*>(st + lay.sc);
         if (t == 0) LQ_STAMP(i, 2);
         auto release = [&] {
             fence_async_smem();                          // generic-proxy accesses to the stage before the next bulk copy lands
-            mbar_arrive(empty + s);
+            mbar_arrive(empty + dsc);
         };
         if (prog_live(sc, L)) {
             step_body<R, KDA>(P, sc, st, lay, gs, t, bar, release, i);
@@ -806,12 +852,12 @@ __global__ void __launch_bounds__(64 + NG * GT, 1) step_pipelined_kernel(StepPar
     }
 }
 
-// 0 = pipelined (default), 1 = direct
+// 0 = pipelined, 1 = direct, 2 = one warp per program (GDN; KDA falls back to the pipelined driver)
 static int g_step_impl = 0;
 
 template <int R, bool KDA>
 static int launch_step(const StepParams& P, cudaStream_t st) {
-    const StageLayout lay = stage_layout(P.d.L, R, KDA);
+    const StageLayout lay = stage_layout(P.d.L, P.d.L, R, KDA);
     if (g_step_impl == 1) {
         const size_t smem = size_t(lay.bytes) + SCRATCH_BYTES;
         int rc = ensure_smem((const void*)step_direct_kernel<R, KDA>, smem);
@@ -819,18 +865,24 @@ static int launch_step(const StepParams& P, cudaStream_t st) {
         step_direct_kernel<R, KDA><<<unsigned(P.N) * P.d.HV, GT, smem, st>>>(P);
         return finish_launch();
     }
-    constexpr int NG = 2;
+    if (g_step_impl == 2 && !KDA) {
+        const int nprog = P.N * P.d.HV;
+        const int want = (nprog + WK_WARPS - 1) / WK_WARPS;
+        const int cap = device_sm_count() * 4;
+        step_warp_gdn_kernel<R><<<want < cap ? want : cap, 32 * WK_WARPS, 0, st>>>(P);
+        return finish_launch();
+    }
+    constexpr int NG = LQ_NG;
     const size_t budget = 227 * 1024;
-    const size_t fixed = size_t(NG) * SCRATCH_BYTES + 3 * 16 * sizeof(uint64_t) + 64;
-    int nstages = int((budget - fixed) / size_t(lay.bytes));
-    if (nstages > 16) nstages = 16;
-    if (nstages < 2) return LQ_ERR_UNSUPPORTED;
-    const size_t smem = size_t(nstages) * lay.bytes + size_t(NG) * SCRATCH_BYTES + 3 * size_t(nstages) * sizeof(uint64_t) + 64;
+    const size_t fixed = size_t(NG) * SCRATCH_BYTES + 3 * ND * sizeof(uint64_t) + (2 * ND + NG + 4) * sizeof(int) + 32 * sizeof(ProgScalars);
+    const int ring_bytes = int((budget - fixed) & ~size_t(127));
+    if (ring_bytes < stage_layout(P.d.L, P.d.L, R, KDA).bytes) return LQ_ERR_UNSUPPORTED;
+    const size_t smem = size_t(ring_bytes) + fixed;
     int rc = ensure_smem((const void*)step_pipelined_kernel<R, KDA, NG>, smem);
     if (rc) return rc;
     const int nprog = P.N * P.d.HV;
     const int grid = nprog < device_sm_count() ? nprog : device_sm_count();
-    step_pipelined_kernel<R, KDA, NG><<<grid, 64 + NG * GT, smem, st>>>(P, nstages);
+    step_pipelined_kernel<R, KDA, NG><<<grid, 64 + NG * GT, smem, st>>>(P, ring_bytes);
     return finish_launch();
 }
 
@@ -880,7 +932,7 @@ extern "C" int lq_debug_read_ptrace(long long* out, int n) {
 extern "C" int lq_set_option(const char* name, int32_t value) {
     if (!name) return LQ_ERR_NULL;
     if (strcmp(name, "step_impl") == 0) {
-        if (value != 0 && value != 1) return LQ_ERR_RANGE;
+        if (value < 0 || value > 2) return LQ_ERR_RANGE;
         lq::g_step_impl = value;
         return LQ_OK;
     }

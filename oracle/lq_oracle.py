@@ -355,8 +355,8 @@ def flush_rebuild(q8, Sk, Sv, Kb, Ub, w, P, G, uq_old, kda):
     GDN (leapquant/kernels.py:1471,1483,1512-1563): p = max(Pbuf, 1e-20); B = q8 * (Sv p / 127) * Sk + sum_j (w_j u_j) k_j^T.
     KDA (leapquant/kernels.py:1448-1468,1519): pc = exp(Pbuf); keys pre-decayed by w_j D_j (D_{L-1} = 1, D_j = D_{j+1} e_{j+1});
     old U^T scaled by pc; B = q8 * (Sv / 127) * (Sk pc) + sum_j u_j (w_j D_j k_j)^T; p = 1.
-    The reference holds w_j u_j (GDN) / the decayed keys (KDA) as bf16 hi + lo, pc * U^T as fp16 and B as fp16;
-    all fp32 here."""
+    The reference holds w_j u_j (GDN) / the decayed keys (KDA) as bf16 hi + lo (16 mantissa bits), pc * U^T as fp16 and
+    B as fp16; all fp32 here (the CUDA kernel keeps the bf16 hi + lo operand and an fp32 B)."""
     K = q8.shape[-1]
     Ut, Qt = uq_old[..., :K].to(torch.float32), uq_old[..., K:].to(torch.float32)
     x = q8.to(torch.float32)
