@@ -326,36 +326,44 @@ __device__ __forceinline__ void step_body(const StepParams& P, const ProgScalars
     LQ_PSTAMP(1);
     // ---- window dots dk_j = K_j . k_hat, dq_j = K_j . q_hat: four rows per warp pass, passes dealt round-robin to the warps ----
     const int nch = (h + 3) >> 2;
-    for (int ch = w; ch < nch; ch += 2 * GW) {               // two passes in flight per warp
-        const int ja = 4 * ch + g, jb = ja + 4 * GW;
-        const bool la = ja < h, lb = jb < h;
-        const char* ra = st + lay.kb + (la ? ja : 0) * 256;
-        const char* rb = st + lay.kb + (lb ? jb : 0) * 256;
-        const uint4 a0 = reinterpret_cast<const uint4*>(ra)[l8 * 2], a1 = reinterpret_cast<const uint4*>(ra)[l8 * 2 + 1];
-        const uint4 b0 = reinterpret_cast<const uint4*>(rb)[l8 * 2], b1 = reinterpret_cast<const uint4*>(rb)[l8 * 2 + 1];
-        const uint32_t wa[8] = {a0.x, a0.y, a0.z, a0.w, a1.x, a1.y, a1.z, a1.w};
-        const uint32_t wb[8] = {b0.x, b0.y, b0.z, b0.w, b1.x, b1.y, b1.z, b1.w};
-        float2 aka = make_float2(0.f, 0.f), aqa = aka, akb = aka, aqb = aka;
+    constexpr int DP = 4;                                     // passes in flight per warp (covers L = 64 with four warps)
+    for (int ch = w; ch < nch; ch += DP * GW) {
+        uint4 r0[DP], r1[DP];
+        int jrow[DP];
 #pragma unroll
-        for (int i = 0; i < 8; ++i) {
-            const float2 xa = bf16x2_to_f2(wa[i]), xb = bf16x2_to_f2(wb[i]);
-            aka = __ffma2_rn(xa, kn[i], aka);
-            aqa = __ffma2_rn(xa, qn[i], aqa);
-            akb = __ffma2_rn(xb, kn[i], akb);
-            aqb = __ffma2_rn(xb, qn[i], aqb);
+        for (int u = 0; u < DP; ++u) {
+            jrow[u] = 4 * (ch + u * GW) + g;
+            const char* rp = st + lay.kb + (jrow[u] < h ? jrow[u] : 0) * 256;
+            r0[u] = reinterpret_cast<const uint4*>(rp)[l8 * 2];
+            r1[u] = reinterpret_cast<const uint4*>(rp)[l8 * 2 + 1];
         }
-        float dka = aka.x + aka.y, dqa = aqa.x + aqa.y, dkb = akb.x + akb.y, dqb = aqb.x + aqb.y;
+        float dk[DP], dq[DP];
+#pragma unroll
+        for (int u = 0; u < DP; ++u) {
+            const uint32_t ww[8] = {r0[u].x, r0[u].y, r0[u].z, r0[u].w, r1[u].x, r1[u].y, r1[u].z, r1[u].w};
+            float2 ak = make_float2(0.f, 0.f), aq = ak;
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+                const float2 x = bf16x2_to_f2(ww[i]);
+                ak = __ffma2_rn(x, kn[i], ak);
+                aq = __ffma2_rn(x, qn[i], aq);
+            }
+            dk[u] = ak.x + ak.y;
+            dq[u] = aq.x + aq.y;
+        }
 #pragma unroll
         for (int o = 1; o <= 4; o <<= 1) {
-            dka += __shfl_xor_sync(0xffffffffu, dka, o);
-            dqa += __shfl_xor_sync(0xffffffffu, dqa, o);
-            dkb += __shfl_xor_sync(0xffffffffu, dkb, o);
-            dqb += __shfl_xor_sync(0xffffffffu, dqb, o);
+#pragma unroll
+            for (int u = 0; u < DP; ++u) {
+                dk[u] += __shfl_xor_sync(0xffffffffu, dk[u], o);
+                dq[u] += __shfl_xor_sync(0xffffffffu, dq[u], o);
+            }
         }
         if (l8 == 0) {
             const float* ws = reinterpret_cast<const float*>(st + lay.w);        // GDN: already decayed by the prologue
-            if (la) { const float wj = ws[ja]; gs.wd[ja] = make_float2(wj * dka, wj * dqa); }
-            if (lb) { const float wj = ws[jb]; gs.wd[jb] = make_float2(wj * dkb, wj * dqb); }
+#pragma unroll
+            for (int u = 0; u < DP; ++u)
+                if (jrow[u] < h) { const float wj = ws[jrow[u]]; gs.wd[jrow[u]] = make_float2(wj * dk[u], wj * dq[u]); }
         }
     }
     LQ_PSTAMP(2);
@@ -634,7 +642,8 @@ __device__ __forceinline__ bool group_all(int bar, int nthreads, bool pred) {
     return r != 0;
 }
 
-// warp 0: producer, warp 1: prologue, warps 2 ..: NG consumer groups of GW warps.
+// warp 0: producer (places stages, publishes scalars), warp 1: copy issue, warp 2: prologue, warps 3 ..: NG consumer groups
+// of GW warps.
 // Shared memory: [ring of `ring_bytes`][NG group scratches][ND x (full, normed, empty) mbarriers][ND stage offsets][NG flags]
 // [ND stage row counts].
 // Program i (CTA-local sequence number) uses descriptor i % ND: three mbarriers and the offset of its stage in the ring.
@@ -642,13 +651,14 @@ __device__ __forceinline__ bool group_all(int bar, int nthreads, bool pred) {
 constexpr int ND = 8;                          // descriptors = most programs resident in the ring at once
 
 template <int R, bool KDA, int NG>
-__global__ void __launch_bounds__(64 + NG * GT, 1) step_pipelined_kernel(StepParams P, int ring_bytes) {
+__global__ void __launch_bounds__(96 + NG * GT, 1) step_pipelined_kernel(StepParams P, int ring_bytes) {
     extern __shared__ __align__(128) char stage_smem[];
     char* scratch0 = stage_smem + ring_bytes;
     uint64_t* full = reinterpret_cast<uint64_t*>(scratch0 + NG * SCRATCH_BYTES);
     uint64_t* normed = full + ND;
     uint64_t* empty = normed + ND;
-    volatile int* doff = reinterpret_cast<volatile int*>(empty + ND);
+    uint64_t* ready = empty + ND;                 // stage placed, scalars written: the copy-issue warp may go
+    volatile int* doff = reinterpret_cast<volatile int*>(ready + ND);
     volatile int* gflag0 = doff + ND;
     ProgScalars* pbatch = reinterpret_cast<ProgScalars*>(const_cast<int*>(doff) + 2 * ND + NG + 2);      // [32], 8-byte aligned
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
@@ -662,6 +672,7 @@ __global__ void __launch_bounds__(64 + NG * GT, 1) step_pipelined_kernel(StepPar
             mbar_init(full + s, 1);
             mbar_init(normed + s, 32);
             mbar_init(empty + s, GT);
+            mbar_init(ready + s, 1);
         }
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
         fence_async_smem();
@@ -669,39 +680,7 @@ __global__ void __launch_bounds__(64 + NG * GT, 1) step_pipelined_kernel(StepPar
     __syncthreads();
 
     if (warp == 0) {
-        // ================= producer: scalars of 32 programs per batch, then one stage fill per program =================
-        const int MIX = 2 * H * KD + HV * VD;
-        const int gqa = HV / H;
-        // Per-lane copy descriptor, fixed for the whole kernel: lane k < ncopy issues copy k of every program from
-        //   src = base + slot * c_slot + hv * c_hv + n * c_n + hk * c_hk,   bytes = b_fix + h * b_h,
-        // into stage + o_fix + h * o_h (the stage layout moves with the live rows h).
-        const char* c_base = nullptr;
-        uint32_t c_slot = 0, c_hv = 0, c_n = 0, c_hk = 0, b_fix = 0, b_h = 0, o_fix = 0, o_h = 0;
-        {
-            const uint32_t rowb = uint32_t(L) * 256u;                    // one head's window rows (bf16 / f16) in bytes
-            const StageLayout l0 = stage_layout(0, L, R, KDA), l1 = stage_layout(1, L, R, KDA);
-            int which = -1;                                              // member of the layout this lane copies into
-            switch (lane) {
-                case 0: c_base = P.ssm; c_slot = uint32_t(P.d.SS) * 4u; c_hv = VD * KD * 4u; b_fix = ck_bytes(R); break;
-                case 1: c_base = reinterpret_cast<const char*>(P.Kbuf); c_slot = uint32_t(HV) * rowb; c_hv = rowb; b_h = 256u; which = 0; break;
-                case 2: c_base = reinterpret_cast<const char*>(P.Ubuf); c_slot = uint32_t(HV) * rowb; c_hv = rowb; b_h = 256u; which = 1; break;
-                case 3: c_base = reinterpret_cast<const char*>(P.Wbuf); c_slot = uint32_t(HV * L) * 4u; c_hv = uint32_t(L) * 4u; b_fix = uint32_t(L) * 4u; which = 2; break;
-                case 4: c_base = reinterpret_cast<const char*>(P.mixed); c_n = uint32_t(MIX) * 2u; c_hk = 256u; b_fix = 256u; which = 3; break;
-                case 5: c_base = reinterpret_cast<const char*>(P.mixed) + H * 256; c_n = uint32_t(MIX) * 2u; c_hk = 256u; b_fix = 256u; which = 4; break;
-                case 6: c_base = reinterpret_cast<const char*>(P.mixed) + 2 * H * 256; c_n = uint32_t(MIX) * 2u; c_hv = 256u; b_fix = 256u; which = 5; break;
-                case 7: if (KDA) { c_base = reinterpret_cast<const char*>(P.Gbuf); c_slot = uint32_t(HV) * rowb; c_hv = rowb; b_h = 256u; which = 6; } break;
-                case 8: if (KDA) { c_base = reinterpret_cast<const char*>(P.Pbuf); c_slot = uint32_t(HV) * 512u; c_hv = 512u; b_fix = 512u; which = 7; } break;
-                case 9: if (KDA) { c_base = reinterpret_cast<const char*>(P.a); c_n = uint32_t(HV) * 256u; c_hv = 256u; b_fix = 256u; which = 8; } break;
-                case 10: if (KDA) { c_base = reinterpret_cast<const char*>(P.dt_bias); c_hv = 512u; b_fix = 512u; which = 9; } break;
-                default: break;
-            }
-            const int m0[10] = {l0.kb, l0.ub, l0.w, l0.q, l0.k, l0.v, l0.gb, l0.pb, l0.a, l0.dtb};
-            const int m1[10] = {l1.kb, l1.ub, l1.w, l1.q, l1.k, l1.v, l1.gb, l1.pb, l1.a, l1.dtb};
-#pragma unroll
-            for (int k = 0; k < 10; ++k)
-                if (which == k) { o_fix = uint32_t(m0[k]); o_h = uint32_t(m1[k] - m0[k]); }
-            __syncwarp();
-        }
+        // ================= producer: scalars of 32 programs per batch, then one stage placement per program =================
         ProgScalars cur, nxt;
         auto fetch = [&](int i) {
             ProgScalars r;
@@ -778,21 +757,73 @@ __global__ void __launch_bounds__(64 + NG * GT, 1) step_pipelined_kernel(StepPar
                 }
                 __syncwarp();
                 LQ_QSTAMP(3);
-                if (live) {
-                    LQ_QSTAMP(4);
-                    const uint32_t hk = uint32_t(sc.hv) / uint32_t(gqa);
-                    const char* src = c_base + uint64_t(uint32_t(sc.slot)) * c_slot + uint64_t(uint32_t(sc.hv)) * c_hv +
-                                      uint64_t(uint32_t(sc.n)) * c_n + uint64_t(hk) * c_hk;
-                    const uint32_t bytes = b_fix + uint32_t(sc.h) * b_h;
-                    if (bytes) bulk_g2s(st + o_fix + uint32_t(sc.h) * o_h, src, bytes, full + dsc);
-                    LQ_QSTAMP(5);
-                }
+                if (lane == 0) mbar_arrive(ready + dsc);
             }
         }
         return;
     }
 
     if (warp == 1) {
+        // ================= copy issue: one bulk asynchronous copy per lane and program =================
+        const int MIX = 2 * H * KD + HV * VD;
+        const int gqa = HV / H;
+        // Per-lane copy descriptor, fixed for the whole kernel: lane k < ncopy issues copy k of every program from
+        //   src = base + slot * c_slot + hv * c_hv + n * c_n + hk * c_hk,   bytes = b_fix + h * b_h,
+        // into stage + o_fix + h * o_h (the stage layout moves with the live rows h).
+        const char* c_base = nullptr;
+        uint32_t c_slot = 0, c_hv = 0, c_n = 0, c_hk = 0, b_fix = 0, b_h = 0, o_fix = 0, o_h = 0;
+        {
+            const uint32_t rowb = uint32_t(L) * 256u;                    // one head's window rows (bf16 / f16) in bytes
+            const StageLayout l0 = stage_layout(0, L, R, KDA), l1 = stage_layout(1, L, R, KDA);
+            int which = -1;                                              // member of the layout this lane copies into
+            switch (lane) {
+                case 0: c_base = P.ssm; c_slot = uint32_t(P.d.SS) * 4u; c_hv = VD * KD * 4u; b_fix = ck_bytes(R); break;
+                case 1: c_base = reinterpret_cast<const char*>(P.Kbuf); c_slot = uint32_t(HV) * rowb; c_hv = rowb; b_h = 256u; which = 0; break;
+                case 2: c_base = reinterpret_cast<const char*>(P.Ubuf); c_slot = uint32_t(HV) * rowb; c_hv = rowb; b_h = 256u; which = 1; break;
+                case 3: c_base = reinterpret_cast<const char*>(P.Wbuf); c_slot = uint32_t(HV * L) * 4u; c_hv = uint32_t(L) * 4u; b_fix = uint32_t(L) * 4u; which = 2; break;
+                case 4: c_base = reinterpret_cast<const char*>(P.mixed); c_n = uint32_t(MIX) * 2u; c_hk = 256u; b_fix = 256u; which = 3; break;
+                case 5: c_base = reinterpret_cast<const char*>(P.mixed) + H * 256; c_n = uint32_t(MIX) * 2u; c_hk = 256u; b_fix = 256u; which = 4; break;
+                case 6: c_base = reinterpret_cast<const char*>(P.mixed) + 2 * H * 256; c_n = uint32_t(MIX) * 2u; c_hv = 256u; b_fix = 256u; which = 5; break;
+                case 7: if (KDA) { c_base = reinterpret_cast<const char*>(P.Gbuf); c_slot = uint32_t(HV) * rowb; c_hv = rowb; b_h = 256u; which = 6; } break;
+                case 8: if (KDA) { c_base = reinterpret_cast<const char*>(P.Pbuf); c_slot = uint32_t(HV) * 512u; c_hv = 512u; b_fix = 512u; which = 7; } break;
+                case 9: if (KDA) { c_base = reinterpret_cast<const char*>(P.a); c_n = uint32_t(HV) * 256u; c_hv = 256u; b_fix = 256u; which = 8; } break;
+                case 10: if (KDA) { c_base = reinterpret_cast<const char*>(P.dt_bias); c_hv = 512u; b_fix = 512u; which = 9; } break;
+                default: break;
+            }
+            const int m0[10] = {l0.kb, l0.ub, l0.w, l0.q, l0.k, l0.v, l0.gb, l0.pb, l0.a, l0.dtb};
+            const int m1[10] = {l1.kb, l1.ub, l1.w, l1.q, l1.k, l1.v, l1.gb, l1.pb, l1.a, l1.dtb};
+#pragma unroll
+            for (int k = 0; k < 10; ++k)
+                if (which == k) { o_fix = uint32_t(m0[k]); o_h = uint32_t(m1[k] - m0[k]); }
+            __syncwarp();
+        }
+        for (int i = 0; i < nit; ++i) {
+            const int dsc = i % ND;
+            if (!warp_wait_bounded(ready + dsc, uint32_t(i / ND) & 1u, lane)) {
+                if (lane == 0) atomicOr(&g_status, ST_PRODUCER_TIMEOUT);
+                return;
+            }
+            char* st = stage_smem + doff[dsc];
+            const int rows = doff[ND + NG + dsc];
+            const ProgScalars sc = *reinterpret_cast<const ProgScalars*>(st + stage_layout(rows, L, R, KDA).sc);
+            if (prog_live(sc, L)) {
+                LQ_QSTAMP(4);
+                // The ring bytes under this stage were read and written through the generic proxy by the previous tenants'
+                // prologue and consumers; their accesses are visible here through the empty -> ready barrier chain, and this
+                // fence orders them before the asynchronous-proxy writes issued below.
+                fence_async_smem();
+                const uint32_t hk = uint32_t(sc.hv) / uint32_t(gqa);
+                const char* src = c_base + uint64_t(uint32_t(sc.slot)) * c_slot + uint64_t(uint32_t(sc.hv)) * c_hv +
+                                  uint64_t(uint32_t(sc.n)) * c_n + uint64_t(hk) * c_hk;
+                const uint32_t bytes = b_fix + uint32_t(sc.h) * b_h;
+                if (bytes) bulk_g2s(st + o_fix + uint32_t(sc.h) * o_h, src, bytes, full + dsc);
+                LQ_QSTAMP(5);
+            }
+        }
+        return;
+    }
+
+    if (warp == 2) {
         // ================= prologue warp: every program in fill order =================
         for (int i = 0; i < nit; ++i) {
             const int dsc = i % ND;
@@ -815,8 +846,8 @@ __global__ void __launch_bounds__(64 + NG * GT, 1) step_pipelined_kernel(StepPar
     }
 
     // ================= consumers: group g takes programs g, g + NG, ... =================
-    const int g = (warp - 2) / GW;
-    const int t = tid - 64 - g * GT;
+    const int g = (warp - 3) / GW;
+    const int t = tid - 96 - g * GT;
     const int bar = 1 + g;
     const GroupScratch gs = carve_scratch(scratch0 + g * SCRATCH_BYTES);
     volatile int* gflag = gflag0 + g;
@@ -837,10 +868,7 @@ __global__ void __launch_bounds__(64 + NG * GT, 1) step_pipelined_kernel(StepPar
         const StageLayout lay = stage_layout(rows, L, R, KDA);
         const ProgScalars sc = *reinterpret_cast<const ProgScalars*>(st + lay.sc);
         if (t == 0) LQ_STAMP(i, 2);
-        auto release = [&] {
-            fence_async_smem();                          // generic-proxy accesses to the stage before the next bulk copy lands
-            mbar_arrive(empty + dsc);
-        };
+        auto release = [&] { mbar_arrive(empty + dsc); };
         if (prog_live(sc, L)) {
             step_body<R, KDA>(P, sc, st, lay, gs, t, bar, release, i);
         } else {
@@ -874,7 +902,7 @@ static int launch_step(const StepParams& P, cudaStream_t st) {
     }
     constexpr int NG = LQ_NG;
     const size_t budget = 227 * 1024;
-    const size_t fixed = size_t(NG) * SCRATCH_BYTES + 3 * ND * sizeof(uint64_t) + (2 * ND + NG + 4) * sizeof(int) + 32 * sizeof(ProgScalars);
+    const size_t fixed = size_t(NG) * SCRATCH_BYTES + 4 * ND * sizeof(uint64_t) + (2 * ND + NG + 4) * sizeof(int) + 32 * sizeof(ProgScalars);
     const int ring_bytes = int((budget - fixed) & ~size_t(127));
     if (ring_bytes < stage_layout(P.d.L, P.d.L, R, KDA).bytes) return LQ_ERR_UNSUPPORTED;
     const size_t smem = size_t(ring_bytes) + fixed;
@@ -882,7 +910,7 @@ static int launch_step(const StepParams& P, cudaStream_t st) {
     if (rc) return rc;
     const int nprog = P.N * P.d.HV;
     const int grid = nprog < device_sm_count() ? nprog : device_sm_count();
-    step_pipelined_kernel<R, KDA, NG><<<grid, 64 + NG * GT, smem, st>>>(P, ring_bytes);
+    step_pipelined_kernel<R, KDA, NG><<<grid, 96 + NG * GT, smem, st>>>(P, ring_bytes);
     return finish_launch();
 }
 
