@@ -454,6 +454,28 @@ def test_sharded_equals_unsharded():
     assert torch.equal(bits(gpu_all.ssm[1:5]), bits(gpu_a.ssm[1:5])) and torch.equal(bits(gpu_all.ssm[5:9]), bits(gpu_b.ssm[5:9]))
 
 
+def test_host_staged_decode_equals_direct():
+    """Steps fed from pinned host memory through the double-buffered staging give bit-identical outputs and state."""
+    from leapquant_b200.host_io import HostStagedDecoder
+    NS, HV, H, L, R, N, T = 9, 4, 2, 16, 4, 8, 40
+    cpu, gpu_d = make_pair(NS, HV, H, L, R, seed=6)
+    gpu_h = GpuSide(cpu)
+    idx = torch.arange(1, N + 1, dtype=torch.int32).cuda()
+    mixed, a, b_, A_log, dtb = step_inputs(N, H, HV, T, 4, False)
+    hm, ha, hb = mixed.pin_memory(), a.contiguous().pin_memory(), b_.pin_memory()
+    h_out = torch.zeros(T, N, HV, V, dtype=torch.bfloat16).pin_memory()
+    dec = HostStagedDecoder(gpu_h.st, gpu_h.ssm, A_log, dtb, idx, hm[0], ha[0], hb[0], h_out[0])
+    for t in range(T):
+        dec.submit(hm[t], ha[t], hb[t], h_out[t])
+    dec.drain()
+    o = torch.zeros(N, HV, V, dtype=torch.bfloat16, device="cuda")
+    for t in range(T):
+        gpu_d.st.decode(gpu_d.ssm, mixed[t].cuda(), a[t].cuda(), b_[t].cuda(), A_log.cuda(), dtb.cuda(), idx, o)
+        assert torch.equal(o.cpu(), h_out[t]), t
+    bits = lambda x: x.view(torch.int32)
+    assert torch.equal(bits(gpu_d.ssm), bits(gpu_h.ssm))
+
+
 def test_cpu_tensor_is_refused():
     from leapquant_b200.state import LeapQuantState
     with pytest.raises(RuntimeError):
