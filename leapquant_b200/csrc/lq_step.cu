@@ -33,7 +33,7 @@ static_assert(GW == 4 || GW == 8, "the reductions below are written for 4 or 8 w
 //      is ONE contiguous copy.  The pipelined driver sizes every stage for the program's live rows (rows = h), so that a
 //      ring of 220 KB holds ~6 average programs instead of 4 worst-case ones. ----
 struct StageLayout {
-    int kb, ub, w, q, k, v, gb, pb, a, dtb, nrm, sc, bytes;
+    int kb, ub, w, q, k, v, gb, pb, a, dtb, nrm, bop, sc, bytes;
 };
 __host__ __device__ inline StageLayout stage_layout(int rows, int L, int R, bool kda) {
     StageLayout s;
@@ -51,8 +51,9 @@ __host__ __device__ inline StageLayout stage_layout(int rows, int L, int R, bool
         s.a = o; o += 256;
         s.dtb = o; o += 512;
     }
-    s.nrm = o; o += 4 * 512;                // prologue output: k_hat, q_hat, then GDN: kf, qf | KDA: pc, en  (f32[128] each)
-    s.sc = o; o += 64;                      // ProgScalars (producer) + k_hat . q_hat (prologue)
+    s.nrm = o; o += (kda ? 4 : 2) * 512;    // prologue output: k_hat, q_hat, then KDA: pc, en  (f32[128] each)
+    s.bop = o; o += 4 * 256;                // prologue output: matvec operands as f16[128] x {k hi, k lo, q hi, q lo}
+    s.sc = o; o += 64;                      // ProgScalars (producer) + k_hat . q_hat and the operand unscale (prologue)
     s.bytes = (o + 127) & ~127;
     return s;
 }
@@ -180,6 +181,24 @@ static __device__ long long g_ntrace[160 * 256 * 8];
 // bits 3..4 of c, which spreads the eight lanes of a quarter-warp over all eight 16-byte bank groups.
 __device__ __forceinline__ int nrm_chunk(int c) { return (c & ~3) | ((c & 3) ^ ((c >> 3) & 3)); }
 
+// Four signed bytes -> two f16 pairs, exactly: byte ^ 0x80 is the code + 128 as an unsigned byte u, the f16 with bits
+// 0x6400 | u is 1024 + u, and subtracting 1152 leaves the code.  lo gets bytes 0, 1 and hi bytes 2, 3.
+__device__ __forceinline__ void s8x4_to_h2x2(uint32_t w, uint32_t& lo, uint32_t& hi) {
+    const uint32_t u = w ^ 0x80808080u;
+    const uint32_t p0 = __byte_perm(u, 0x64646464u, 0x4140), p1 = __byte_perm(u, 0x64646464u, 0x4342);
+    const __half2 off = __floats2half2_rn(1152.f, 1152.f);
+    const __half2 r0 = __hsub2(*reinterpret_cast<const __half2*>(&p0), off), r1 = __hsub2(*reinterpret_cast<const __half2*>(&p1), off);
+    lo = *reinterpret_cast<const uint32_t*>(&r0);
+    hi = *reinterpret_cast<const uint32_t*>(&r1);
+}
+// D += A B for one m16n8k16 tile, f16 operands, f32 accumulator (warp-wide)
+__device__ __forceinline__ void mma_f16_16816(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0,
+                                              uint32_t b1) {
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+                 : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+                 : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+
 // ------------------------------------------------------------------------------------------------------------------
 // prologue: ONE warp, lane owns key channels 4 lane .. 4 lane + 3
 // ------------------------------------------------------------------------------------------------------------------
@@ -195,39 +214,14 @@ __device__ __forceinline__ void step_prologue(const StepParams& P, const ProgSca
     float q[4], k[4];
     q[0] = bf16lo(qw.x); q[1] = bf16hi(qw.x); q[2] = bf16lo(qw.y); q[3] = bf16hi(qw.y);
     k[0] = bf16lo(kw.x); k[1] = bf16hi(kw.x); k[2] = bf16lo(kw.y); k[3] = bf16hi(kw.y);
-    float sq = 0.f, sk = 0.f, skq = 0.f;
-#pragma unroll
-    for (int i = 0; i < 4; ++i) {
-        sq = fmaf(q[i], q[i], sq);
-        sk = fmaf(k[i], k[i], sk);
-        skq = fmaf(k[i], q[i], skq);
-    }
-    LQ_NSTAMPD(1, sq + sk + skq);
-    sq = warp_sum(sq);
-    LQ_NSTAMPD(7, sq);
-    sk = warp_sum(sk); skq = warp_sum(skq);
-    LQ_NSTAMPD(2, sq + sk + skq);
-    const float inq = rsqrtf(sq + 1e-6f) * P.scale, ink = rsqrtf(sk + 1e-6f);
-#pragma unroll
-    for (int i = 0; i < 4; ++i) {
-        q[i] *= inq;
-        k[i] *= ink;
-    }
-    float4* nrm = reinterpret_cast<float4*>(st + lay.nrm);
-    const int sl = nrm_chunk(lane);                       // swizzled 16-byte chunk of this lane's four channels
-    nrm[sl] = make_float4(k[0], k[1], k[2], k[3]);
-    nrm[32 + sl] = make_float4(q[0], q[1], q[2], q[3]);
-    if (lane == 0) *reinterpret_cast<float*>(st + lay.sc + 32) = skq * inq * ink;
-    LQ_NSTAMP(3);
-    const uint2 kapp = make_uint2(f2_to_bf16x2(k[0], k[1]), f2_to_bf16x2(k[2], k[3]));      // k_hat (bf16) for the window
+    // KDA per-channel gate: log-decay g, cumulative log gate gn, pc = exp(gn), step factor en = exp(g)
+    float gn[4], en[4], pc[4] = {1.f, 1.f, 1.f, 1.f};
     if (KDA) {
-        // per-channel gate: log-decay g, cumulative log gate gn, pc = exp(gn), step factor en = exp(g)
         const uint2 aw = reinterpret_cast<const uint2*>(st + lay.a)[lane];
         const float4 db = reinterpret_cast<const float4*>(st + lay.dtb)[lane];
         const float4 pb = reinterpret_cast<const float4*>(st + lay.pb)[lane];
         const float xa[4] = {bf16lo(aw.x) + db.x, bf16hi(aw.x) + db.y, bf16lo(aw.y) + db.z, bf16hi(aw.y) + db.w};
         const float pbv[4] = {pb.x, pb.y, pb.z, pb.w};
-        float gn[4], en[4], pc[4];
 #pragma unroll
         for (int i = 0; i < 4; ++i) {
             float gl;
@@ -237,6 +231,74 @@ __device__ __forceinline__ void step_prologue(const StepParams& P, const ProgSca
             en[i] = __expf(gl);
             pc[i] = __expf(gn[i]);
         }
+    }
+    // column weights of the checkpoint matvec: Sk / 127 (KDA: times pc)
+    const float4 s4 = reinterpret_cast<const float4*>(st + CK_SK)[lane];
+    float s[4] = {s4.x * (1.0f / QMAX), s4.y * (1.0f / QMAX), s4.z * (1.0f / QMAX), s4.w * (1.0f / QMAX)};
+    if (KDA) {
+#pragma unroll
+        for (int i = 0; i < 4; ++i) s[i] *= pc[i];
+    }
+    // one butterfly for |q|^2, |k|^2, k.q and the largest |k s|, |q s| (their maxima give the f16 operand scale)
+    float sq = 0.f, sk = 0.f, skq = 0.f, mk = 0.f, mq = 0.f;
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        sq = fmaf(q[i], q[i], sq);
+        sk = fmaf(k[i], k[i], sk);
+        skq = fmaf(k[i], q[i], skq);
+        mk = fmaxf(mk, fabsf(k[i] * s[i]));
+        mq = fmaxf(mq, fabsf(q[i] * s[i]));
+    }
+    LQ_NSTAMP(1);
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+        const float a0 = __shfl_xor_sync(0xffffffffu, sq, o), a1 = __shfl_xor_sync(0xffffffffu, sk, o);
+        const float a2 = __shfl_xor_sync(0xffffffffu, skq, o), a3 = __shfl_xor_sync(0xffffffffu, mk, o);
+        const float a4 = __shfl_xor_sync(0xffffffffu, mq, o);
+        sq += a0; sk += a1; skq += a2; mk = fmaxf(mk, a3); mq = fmaxf(mq, a4);
+    }
+    LQ_NSTAMP(2);
+    const float inq = rsqrtf(sq + 1e-6f) * P.scale, ink = rsqrtf(sk + 1e-6f);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        q[i] *= inq;
+        k[i] *= ink;
+    }
+    // The matvec runs on the tensor cores in f16 with an f32 accumulator.  The operands k_hat s and q_hat s are scaled by a
+    // power of two that puts the largest of them in [2^13, 2^14) and split into an f16 head and an f16 remainder, which keeps
+    // 22 bits of every operand that matters at the size of the largest one.
+    const float mx = fmaxf(mk * ink, mq * inq);
+    uint32_t eb = __float_as_uint(mx) & 0x7F800000u;
+    eb = eb < 0x0C800000u ? 0x0C800000u : eb;
+    const uint32_t sbits = (267u << 23) - eb;
+    const float oscale = __uint_as_float(sbits);
+    {
+        uint32_t hw[4][2];
+#pragma unroll
+        for (int n = 0; n < 2; ++n) {
+            float x[4];
+#pragma unroll
+            for (int i = 0; i < 4; ++i) x[i] = (n == 0 ? k[i] : q[i]) * s[i] * oscale;
+            const __half2 h01 = __floats2half2_rn(x[0], x[1]), h23 = __floats2half2_rn(x[2], x[3]);
+            const float2 f01 = __half22float2(h01), f23 = __half22float2(h23);
+            const __half2 l01 = __floats2half2_rn(x[0] - f01.x, x[1] - f01.y), l23 = __floats2half2_rn(x[2] - f23.x, x[3] - f23.y);
+            hw[2 * n][0] = *reinterpret_cast<const uint32_t*>(&h01); hw[2 * n][1] = *reinterpret_cast<const uint32_t*>(&h23);
+            hw[2 * n + 1][0] = *reinterpret_cast<const uint32_t*>(&l01); hw[2 * n + 1][1] = *reinterpret_cast<const uint32_t*>(&l23);
+        }
+#pragma unroll
+        for (int n = 0; n < 4; ++n) reinterpret_cast<uint2*>(st + lay.bop + n * 256)[lane] = make_uint2(hw[n][0], hw[n][1]);
+    }
+    float4* nrm = reinterpret_cast<float4*>(st + lay.nrm);
+    const int sl = nrm_chunk(lane);                       // swizzled 16-byte chunk of this lane's four channels
+    nrm[sl] = make_float4(k[0], k[1], k[2], k[3]);
+    nrm[32 + sl] = make_float4(q[0], q[1], q[2], q[3]);
+    if (lane == 0) {
+        *reinterpret_cast<float*>(st + lay.sc + 32) = skq * inq * ink;
+        *reinterpret_cast<uint32_t*>(st + lay.sc + 36) = (254u << 23) - sbits;       // 1 / oscale
+    }
+    LQ_NSTAMP(3);
+    const uint2 kapp = make_uint2(f2_to_bf16x2(k[0], k[1]), f2_to_bf16x2(k[2], k[3]));      // k_hat (bf16) for the window
+    if (KDA) {
         nrm[64 + sl] = make_float4(pc[0], pc[1], pc[2], pc[3]);
         nrm[96 + sl] = make_float4(en[0], en[1], en[2], en[3]);
         signal();
@@ -246,11 +308,6 @@ __device__ __forceinline__ void step_prologue(const StepParams& P, const ProgSca
         reinterpret_cast<uint2*>(P.Gbuf + (sh * L + h) * KD)[lane] =
             make_uint2(*reinterpret_cast<uint32_t*>(&e01), *reinterpret_cast<uint32_t*>(&e23));
     } else {
-        // matvec operands k_hat Sk / 127 and q_hat Sk / 127
-        const float4 s4 = reinterpret_cast<const float4*>(st + CK_SK)[lane];
-        const float s[4] = {s4.x * (1.0f / QMAX), s4.y * (1.0f / QMAX), s4.z * (1.0f / QMAX), s4.w * (1.0f / QMAX)};
-        nrm[64 + sl] = make_float4(k[0] * s[0], k[1] * s[1], k[2] * s[2], k[3] * s[3]);
-        nrm[96 + sl] = make_float4(q[0] * s[0], q[1] * s[1], q[2] * s[2], q[3] * s[3]);
         // window weights decay: w_j <- w_j alpha for the live entries, in the stage and (after the signal) in global memory
         float* ws = reinterpret_cast<float*>(st + lay.w);
         float wj[2] = {0.f, 0.f};
@@ -326,7 +383,10 @@ __device__ __forceinline__ void step_body(const StepParams& P, const ProgScalars
     LQ_PSTAMP(1);
     // ---- window dots dk_j = K_j . k_hat, dq_j = K_j . q_hat: four rows per warp pass, passes dealt round-robin to the warps ----
     const int nch = (h + 3) >> 2;
-    constexpr int DP = 4;                                     // passes in flight per warp (covers L = 64 with four warps)
+#ifndef LQ_DP
+#define LQ_DP 2
+#endif
+    constexpr int DP = LQ_DP;                                 // passes in flight per warp (window rows 4*GW*DP per trip)
     for (int ch = w; ch < nch; ch += DP * GW) {
         uint4 r0[DP], r1[DP];
         int jrow[DP];
@@ -389,58 +449,47 @@ __device__ __forceinline__ void step_body(const StepParams& P, const ProgScalars
     }
 
     LQ_PSTAMP(3);
-    // ---- checkpoint matvec operands: GDN from the prologue; KDA k_hat Sk pc / 127 ----
-    if (KDA) {
-        const float4* skp = reinterpret_cast<const float4*>(st + CK_SK) + l8 * 4;
-        const float4* pcp = reinterpret_cast<const float4*>(nrm + 256);
-#pragma unroll
-        for (int i = 0; i < 4; ++i) {
-            const float4 s4 = skp[i], p4 = pcp[nrm_chunk(l8 * 4 + i)];
-            const float2 sa = make_float2(s4.x * p4.x * (1.0f / QMAX), s4.y * p4.y * (1.0f / QMAX));
-            const float2 sb = make_float2(s4.z * p4.z * (1.0f / QMAX), s4.w * p4.w * (1.0f / QMAX));
-            kn[2 * i] = __fmul2_rn(kn[2 * i], sa);
-            qn[2 * i] = __fmul2_rn(qn[2 * i], sa);
-            kn[2 * i + 1] = __fmul2_rn(kn[2 * i + 1], sb);
-            qn[2 * i + 1] = __fmul2_rn(qn[2 * i + 1], sb);
-        }
-    } else {
-        const float4* kp = reinterpret_cast<const float4*>(nrm + 256);
-        const float4* qp = reinterpret_cast<const float4*>(nrm + 384);
-#pragma unroll
-        for (int i = 0; i < 4; ++i) {
-            const float4 a = kp[nrm_chunk(l8 * 4 + i)], b = qp[nrm_chunk(l8 * 4 + i)];
-            kn[2 * i] = make_float2(a.x, a.y); kn[2 * i + 1] = make_float2(a.z, a.w);
-            qn[2 * i] = make_float2(b.x, b.y); qn[2 * i + 1] = make_float2(b.z, b.w);
-        }
-    }
-    float pk[NPASS], pq[NPASS];
+    // ---- checkpoint matvec on the tensor cores: D[v][n] = sum_c codes[v][c] B[c][n], n = {k hi, k lo, q hi, q lo}.
+    //      A warp owns 32 rows = two m16 tiles; lane (gid, tig) holds rows gid and gid + 8 of a tile and, of each row, the
+    //      sixteen codes at columns 16 tig and the sixteen at 64 + 16 tig: word s of those eight words feeds k-step s, so
+    //      the k index of the instruction is a permutation of the columns that the B fragments below follow. ----
     {
-        const uint4* tile = reinterpret_cast<const uint4*>(st + CK_CODES);
-#pragma unroll
-        for (int it = 0; it < NPASS; ++it) {
-            const int row = (VD / GW) * w + 4 * it + g;
-            const uint4 cw = tile[row * 8 + l8];
-            const uint32_t ww[4] = {cw.x, cw.y, cw.z, cw.w};
-            float2 ak = make_float2(0.f, 0.f), aq = make_float2(0.f, 0.f);
-#pragma unroll
-            for (int m = 0; m < 4; ++m) {
-                float2 xa, xb;
-                s8x4_to_f2x2(ww[m], xa, xb);
-                ak = __ffma2_rn(xa, kn[2 * m], ak);
-                aq = __ffma2_rn(xa, qn[2 * m], aq);
-                ak = __ffma2_rn(xb, kn[2 * m + 1], ak);
-                aq = __ffma2_rn(xb, qn[2 * m + 1], aq);
+        const int gid = lane >> 2, tig = lane & 3;
+        uint32_t bfr[16];
+        {
+            uint4 x[4] = {make_uint4(0, 0, 0, 0), make_uint4(0, 0, 0, 0), make_uint4(0, 0, 0, 0), make_uint4(0, 0, 0, 0)};
+            if (gid < 4) {
+                const uint4* bp = reinterpret_cast<const uint4*>(st + lay.bop + gid * 256);
+                x[0] = bp[tig * 2]; x[1] = bp[tig * 2 + 1]; x[2] = bp[8 + tig * 2]; x[3] = bp[8 + tig * 2 + 1];
             }
-            pk[it] = ak.x + ak.y;
-            pq[it] = aq.x + aq.y;
+#pragma unroll
+            for (int i = 0; i < 4; ++i) { bfr[4 * i] = x[i].x; bfr[4 * i + 1] = x[i].y; bfr[4 * i + 2] = x[i].z; bfr[4 * i + 3] = x[i].w; }
         }
-    }
-    {
-        const float mqr = pass_transpose_sum(pk, l8), yqr = pass_transpose_sum(pq, l8);
-        if (l8 < NPASS) {                                    // lane l8 owns the row of pass l8
-            const int row = (VD / GW) * w + 4 * l8 + g;
-            const float svv = reinterpret_cast<const float*>(st + CK_SV)[row];
-            gs.mqy[row] = make_float2(mqr * svv, yqr * svv);
+        const float unscale = *reinterpret_cast<const float*>(st + lay.sc + 36);
+        const uint4* tile = reinterpret_cast<const uint4*>(st + CK_CODES);
+        float* mqyf = reinterpret_cast<float*>(gs.mqy);
+#pragma unroll
+        for (int mt = 0; mt < (VD / GW) / 16; ++mt) {
+            const int rlo = (VD / GW) * w + 16 * mt + gid, rhi = rlo + 8;
+            const uint4 l0 = tile[rlo * 8 + tig], l1 = tile[rlo * 8 + 4 + tig];
+            const uint4 h0 = tile[rhi * 8 + tig], h1 = tile[rhi * 8 + 4 + tig];
+            const uint32_t lw[8] = {l0.x, l0.y, l0.z, l0.w, l1.x, l1.y, l1.z, l1.w};
+            const uint32_t hw[8] = {h0.x, h0.y, h0.z, h0.w, h1.x, h1.y, h1.z, h1.w};
+            float d[4] = {0.f, 0.f, 0.f, 0.f}, e[4] = {0.f, 0.f, 0.f, 0.f};      // two accumulator chains per tile
+#pragma unroll
+            for (int ks = 0; ks < 8; ++ks) {
+                uint32_t a0, a1, a2, a3;
+                s8x4_to_h2x2(lw[ks], a0, a2);
+                s8x4_to_h2x2(hw[ks], a1, a3);
+                mma_f16_16816((ks & 1) ? e : d, a0, a1, a2, a3, bfr[2 * ks], bfr[2 * ks + 1]);
+            }
+#pragma unroll
+            for (int i = 0; i < 4; ++i) d[i] += e[i];
+            if (tig < 2) {                                   // tig 0 holds (k hi, k lo), tig 1 holds (q hi, q lo)
+                const float* svp = reinterpret_cast<const float*>(st + CK_SV);
+                mqyf[2 * rlo + tig] = (d[0] + d[1]) * unscale * svp[rlo];
+                mqyf[2 * rhi + tig] = (d[2] + d[3]) * unscale * svp[rhi];
+            }
         }
     }
     LQ_PSTAMP(4);
@@ -868,7 +917,11 @@ __global__ void __launch_bounds__(96 + NG * GT, 1) step_pipelined_kernel(StepPar
         const StageLayout lay = stage_layout(rows, L, R, KDA);
         const ProgScalars sc = *reinterpret_cast<const ProgScalars*>(st + lay.sc);
         if (t == 0) LQ_STAMP(i, 2);
+#ifdef LQ_FENCE_CONSUMER
+        auto release = [&] { fence_async_smem(); mbar_arrive(empty + dsc); };
+#else
         auto release = [&] { mbar_arrive(empty + dsc); };
+#endif
         if (prog_live(sc, L)) {
             step_body<R, KDA>(P, sc, st, lay, gs, t, bar, release, i);
         } else {
