@@ -344,9 +344,15 @@ static __device__ long long g_ptrace[160 * 256 * 8];
 // ------------------------------------------------------------------------------------------------------------------
 // `release()` is called by every thread after its last read of the stage and BEFORE the program's global stores: the
 // stage hand-back is an mbarrier arrive with release semantics, which would otherwise wait for those stores to drain.
-template <int R, bool KDA, typename Release>
+//
+// The int8 tile comes either from the stage (REGC false: `st` holds the whole checkpoint) or from the registers `ac`, which
+// the caller filled with plain global loads issued one program ahead (REGC true: the stage then starts at Sk and `st` is a
+// virtual origin CK_SK bytes below it).  `refill()` is called once the tile phase has consumed `ac`.
+constexpr int MT = (VD / GW) / 16;                 // m16 tiles of tile rows per warp
+template <int R, bool KDA, bool REGC, typename Release, typename Refill>
 __device__ __forceinline__ void step_body(const StepParams& P, const ProgScalars& sc, char* st, const StageLayout& lay,
-                                          const GroupScratch& gs, int t, int bar, Release release, int pi = -1) {
+                                          const GroupScratch& gs, int t, int bar, Release release, uint4 (&ac)[4 * MT],
+                                          Refill refill, int pi = -1) {
     const int w = t >> 5, lane = t & 31, l8 = lane & 7, g = lane >> 3;
     const int L = P.d.L, h = sc.h;
     const int64_t sh = int64_t(sc.slot) * P.d.HV + sc.hv;
@@ -367,6 +373,59 @@ __device__ __forceinline__ void step_body(const StepParams& P, const ProgScalars
         named_bar(bar, GT);
     }
 
+    // ---- checkpoint matvec on the tensor cores: D[v][n] = sum_c codes[v][c] B[c][n], n = {k hi, k lo, q hi, q lo}.
+    //      A warp owns 32 rows = two m16 tiles; lane (gid, tig) holds rows gid and gid + 8 of a tile and, of each row, the
+    //      sixteen codes at columns 16 tig and the sixteen at 64 + 16 tig: word s of those eight words feeds k-step s, so
+    //      the k index of the instruction is a permutation of the columns that the B fragments below follow. ----
+    {
+        const int gid = lane >> 2, tig = lane & 3;
+        uint32_t bfr[16];
+        {
+            uint4 x[4] = {make_uint4(0, 0, 0, 0), make_uint4(0, 0, 0, 0), make_uint4(0, 0, 0, 0), make_uint4(0, 0, 0, 0)};
+            if (gid < 4) {
+                const uint4* bp = reinterpret_cast<const uint4*>(st + lay.bop + gid * 256);
+                x[0] = bp[tig * 2]; x[1] = bp[tig * 2 + 1]; x[2] = bp[8 + tig * 2]; x[3] = bp[8 + tig * 2 + 1];
+            }
+#pragma unroll
+            for (int i = 0; i < 4; ++i) { bfr[4 * i] = x[i].x; bfr[4 * i + 1] = x[i].y; bfr[4 * i + 2] = x[i].z; bfr[4 * i + 3] = x[i].w; }
+        }
+        const float unscale = *reinterpret_cast<const float*>(st + lay.sc + 36);
+        if (!REGC) {
+            const uint4* tile = reinterpret_cast<const uint4*>(st + CK_CODES);
+#pragma unroll
+            for (int mt = 0; mt < MT; ++mt) {
+                const int rlo = (VD / GW) * w + 16 * mt + gid, rhi = rlo + 8;
+                ac[4 * mt] = tile[rlo * 8 + tig]; ac[4 * mt + 1] = tile[rlo * 8 + 4 + tig];
+                ac[4 * mt + 2] = tile[rhi * 8 + tig]; ac[4 * mt + 3] = tile[rhi * 8 + 4 + tig];
+            }
+        }
+        float* mqyf = reinterpret_cast<float*>(gs.mqy);
+#pragma unroll
+        for (int mt = 0; mt < MT; ++mt) {
+            const int rlo = (VD / GW) * w + 16 * mt + gid, rhi = rlo + 8;
+            const uint4 l0 = ac[4 * mt], l1 = ac[4 * mt + 1], h0 = ac[4 * mt + 2], h1 = ac[4 * mt + 3];
+            const uint32_t lw[8] = {l0.x, l0.y, l0.z, l0.w, l1.x, l1.y, l1.z, l1.w};
+            const uint32_t hw[8] = {h0.x, h0.y, h0.z, h0.w, h1.x, h1.y, h1.z, h1.w};
+            float d[4] = {0.f, 0.f, 0.f, 0.f}, e[4] = {0.f, 0.f, 0.f, 0.f};      // two accumulator chains per tile
+#pragma unroll
+            for (int ks = 0; ks < 8; ++ks) {
+                uint32_t a0, a1, a2, a3;
+                s8x4_to_h2x2(lw[ks], a0, a2);
+                s8x4_to_h2x2(hw[ks], a1, a3);
+                mma_f16_16816((ks & 1) ? e : d, a0, a1, a2, a3, bfr[2 * ks], bfr[2 * ks + 1]);
+            }
+#pragma unroll
+            for (int i = 0; i < 4; ++i) d[i] += e[i];
+            if (tig < 2) {                                   // tig 0 holds (k hi, k lo), tig 1 holds (q hi, q lo)
+                const float* svp = reinterpret_cast<const float*>(st + CK_SV);
+                mqyf[2 * rlo + tig] = (d[0] + d[1]) * unscale * svp[rlo];
+                mqyf[2 * rhi + tig] = (d[2] + d[3]) * unscale * svp[rhi];
+            }
+        }
+    }
+    refill();
+    LQ_PSTAMP(1);
+
     // ---- k_hat, q_hat of this lane's 16 columns ----
     float2 kn[8], qn[8];
     {
@@ -380,7 +439,6 @@ __device__ __forceinline__ void step_body(const StepParams& P, const ProgScalars
         }
     }
 
-    LQ_PSTAMP(1);
     // ---- window dots dk_j = K_j . k_hat, dq_j = K_j . q_hat: four rows per warp pass, passes dealt round-robin to the warps ----
     const int nch = (h + 3) >> 2;
 #ifndef LQ_DP
@@ -449,49 +507,6 @@ __device__ __forceinline__ void step_body(const StepParams& P, const ProgScalars
     }
 
     LQ_PSTAMP(3);
-    // ---- checkpoint matvec on the tensor cores: D[v][n] = sum_c codes[v][c] B[c][n], n = {k hi, k lo, q hi, q lo}.
-    //      A warp owns 32 rows = two m16 tiles; lane (gid, tig) holds rows gid and gid + 8 of a tile and, of each row, the
-    //      sixteen codes at columns 16 tig and the sixteen at 64 + 16 tig: word s of those eight words feeds k-step s, so
-    //      the k index of the instruction is a permutation of the columns that the B fragments below follow. ----
-    {
-        const int gid = lane >> 2, tig = lane & 3;
-        uint32_t bfr[16];
-        {
-            uint4 x[4] = {make_uint4(0, 0, 0, 0), make_uint4(0, 0, 0, 0), make_uint4(0, 0, 0, 0), make_uint4(0, 0, 0, 0)};
-            if (gid < 4) {
-                const uint4* bp = reinterpret_cast<const uint4*>(st + lay.bop + gid * 256);
-                x[0] = bp[tig * 2]; x[1] = bp[tig * 2 + 1]; x[2] = bp[8 + tig * 2]; x[3] = bp[8 + tig * 2 + 1];
-            }
-#pragma unroll
-            for (int i = 0; i < 4; ++i) { bfr[4 * i] = x[i].x; bfr[4 * i + 1] = x[i].y; bfr[4 * i + 2] = x[i].z; bfr[4 * i + 3] = x[i].w; }
-        }
-        const float unscale = *reinterpret_cast<const float*>(st + lay.sc + 36);
-        const uint4* tile = reinterpret_cast<const uint4*>(st + CK_CODES);
-        float* mqyf = reinterpret_cast<float*>(gs.mqy);
-#pragma unroll
-        for (int mt = 0; mt < (VD / GW) / 16; ++mt) {
-            const int rlo = (VD / GW) * w + 16 * mt + gid, rhi = rlo + 8;
-            const uint4 l0 = tile[rlo * 8 + tig], l1 = tile[rlo * 8 + 4 + tig];
-            const uint4 h0 = tile[rhi * 8 + tig], h1 = tile[rhi * 8 + 4 + tig];
-            const uint32_t lw[8] = {l0.x, l0.y, l0.z, l0.w, l1.x, l1.y, l1.z, l1.w};
-            const uint32_t hw[8] = {h0.x, h0.y, h0.z, h0.w, h1.x, h1.y, h1.z, h1.w};
-            float d[4] = {0.f, 0.f, 0.f, 0.f}, e[4] = {0.f, 0.f, 0.f, 0.f};      // two accumulator chains per tile
-#pragma unroll
-            for (int ks = 0; ks < 8; ++ks) {
-                uint32_t a0, a1, a2, a3;
-                s8x4_to_h2x2(lw[ks], a0, a2);
-                s8x4_to_h2x2(hw[ks], a1, a3);
-                mma_f16_16816((ks & 1) ? e : d, a0, a1, a2, a3, bfr[2 * ks], bfr[2 * ks + 1]);
-            }
-#pragma unroll
-            for (int i = 0; i < 4; ++i) d[i] += e[i];
-            if (tig < 2) {                                   // tig 0 holds (k hi, k lo), tig 1 holds (q hi, q lo)
-                const float* svp = reinterpret_cast<const float*>(st + CK_SV);
-                mqyf[2 * rlo + tig] = (d[0] + d[1]) * unscale * svp[rlo];
-                mqyf[2 * rhi + tig] = (d[2] + d[3]) * unscale * svp[rhi];
-            }
-        }
-    }
     LQ_PSTAMP(4);
     named_bar(bar, GT);
     LQ_PSTAMP(5);
@@ -614,7 +629,8 @@ __global__ void __launch_bounds__(GT, 2) step_direct_kernel(StepParams P) {
     if (t < 32) step_prologue<KDA>(P, sc, st, lay, t, [] {});
     __syncthreads();
     const GroupScratch gs = carve_scratch(stage_smem + stage_layout(P.d.L, P.d.L, R, KDA).bytes);
-    step_body<R, KDA>(P, sc, st, lay, gs, t, 1, [] {});
+    uint4 ac[4 * MT];
+    step_body<R, KDA, false>(P, sc, st, lay, gs, t, 1, [] {}, ac, [] {});
 }
 
 #include "lq_step_warp.cuh"
@@ -697,10 +713,20 @@ __device__ __forceinline__ bool group_all(int bar, int nthreads, bool pred) {
 // [ND stage row counts].
 // Program i (CTA-local sequence number) uses descriptor i % ND: three mbarriers and the offset of its stage in the ring.
 // Stages are carved from the ring in order, each sized for its program's live window rows, and reclaimed in order.
-constexpr int ND = 8;                          // descriptors = most programs resident in the ring at once
+#ifndef LQ_REGC
+#define LQ_REGC 0
+#endif
+#ifndef LQ_NPW
+#define LQ_NPW 2
+#endif
+constexpr int NPW = LQ_NPW;                     // prologue warps; warp 2 + k takes the programs i = k (mod NPW)
+constexpr int UT = 32 * (2 + NPW);              // utility threads ahead of the consumer groups: producer, copy issue, prologues
+constexpr bool REGC = LQ_REGC != 0;             // int8 tile through registers (plain loads one program ahead), not the ring
+constexpr int SKIP = REGC ? CK_SK : 0;          // stage bytes not held in the ring; `st` is a virtual origin SKIP bytes below
+constexpr int ND = 16;                         // descriptors = most programs resident in the ring at once
 
 template <int R, bool KDA, int NG>
-__global__ void __launch_bounds__(96 + NG * GT, 1) step_pipelined_kernel(StepParams P, int ring_bytes) {
+__global__ void __launch_bounds__(UT + NG * GT, 1) step_pipelined_kernel(StepParams P, int ring_bytes) {
     extern __shared__ __align__(128) char stage_smem[];
     char* scratch0 = stage_smem + ring_bytes;
     uint64_t* full = reinterpret_cast<uint64_t*>(scratch0 + NG * SCRATCH_BYTES);
@@ -742,8 +768,12 @@ __global__ void __launch_bounds__(96 + NG * GT, 1) step_pipelined_kernel(StepPar
             return r;
         };
         nxt = fetch(lane);
+        // The ring is a FIFO: stages are placed in program order and reclaimed in program order.  Space is accounted in
+        // virtual bytes: a stage that does not fit before the end of the ring starts at 0 and the skipped tail counts as
+        // allocated, so the virtual position modulo the ring size is always the physical offset and the live programs
+        // tail .. i-1 occupy the virtual range [start of tail, vhead), which must never exceed the ring size.
         int head = 0, tail = 0;                                  // next free ring byte; oldest program not yet reclaimed
-        int r_off = 0, r_end = 0;                                // this lane keeps (offset, end) of program `lane`-th descriptor
+        uint32_t vhead = 0, r_vs = 0;                            // virtual head; lane (i % ND) keeps the virtual start of program i
         bool ok = true;
         for (int base = 0; base < nit && ok; base += 32) {
             cur = nxt;
@@ -759,27 +789,16 @@ __global__ void __launch_bounds__(96 + NG * GT, 1) step_pipelined_kernel(StepPar
                 const ProgScalars sc = *const_cast<const ProgScalars*>(&pbatch[j]);      // broadcast read
                 const bool live = prog_live(sc, L);
                 const int rows = live ? sc.h : 0;
-                const int size = stage_layout(rows, L, R, KDA).bytes;
-                // place the stage: at the head, or at the start of the ring if it does not fit before the end
-                const int off = (head + size <= ring_bytes) ? head : 0;
-                // in-flight programs tail .. i-1 keep (offset, end) in lane (program % ND); find the newest one that the new
-                // stage [off, off + size) would overwrite -- and every program from i - ND on, whose descriptor is needed
-                int need = max(tail, i - ND + 1);
-                {
-                    const int jprog = i - 1 - ((i - 1 - lane) & (ND - 1)) ;   // newest program < i whose descriptor is `lane`
-                    const bool mine = lane < ND && jprog >= tail && jprog >= 0;
-                    const bool hit = mine && r_off < off + size && off < r_end;
-                    const uint32_t hits = __ballot_sync(0xffffffffu, hit);
-                    int newest = -1;
-#pragma unroll
-                    for (int k = 0; k < ND; ++k) {
-                        const int jp = i - 1 - ((i - 1 - k) & (ND - 1));
-                        if ((hits >> k) & 1u) newest = max(newest, jp);
-                    }
-                    need = max(need, newest + 1);
-                }
+                const StageLayout lay = stage_layout(rows, L, R, KDA);
+                const int size = lay.bytes - SKIP;
+                int off = head;
+                uint32_t v0 = vhead;
+                if (head + size > ring_bytes) { v0 += uint32_t(ring_bytes - head); off = 0; }
+                const uint32_t v1 = v0 + uint32_t(size);
                 LQ_QSTAMP(1);
-                while (tail < need) {                            // reclaim in order
+                while (tail < i) {                               // reclaim in order until the stage and its descriptor are free
+                    const uint32_t vt = __shfl_sync(0xffffffffu, r_vs, tail % ND);
+                    if (v1 - vt <= uint32_t(ring_bytes) && i - tail < ND) break;
                     if (!warp_wait_bounded(empty + (tail % ND), uint32_t(tail / ND) & 1u, lane)) { ok = false; break; }
                     ++tail;
                 }
@@ -788,16 +807,17 @@ __global__ void __launch_bounds__(96 + NG * GT, 1) step_pipelined_kernel(StepPar
                     break;
                 }
                 LQ_QSTAMP(2);
-                if (lane == dsc) { r_off = off; r_end = off + size; }
+                if (lane == dsc) r_vs = v0;
                 head = off + size;
-                char* st = stage_smem + off;
+                vhead = v1;
+                char* st = stage_smem + off - SKIP;
                 if (lane == 0) {
                     LQ_STAMP(i, 0);
                     doff[dsc] = off;
                     doff[ND + NG + dsc] = rows;
-                    *reinterpret_cast<ProgScalars*>(st + stage_layout(rows, L, R, KDA).sc) = sc;
+                    *reinterpret_cast<ProgScalars*>(st + lay.sc) = sc;
                     if (live) {
-                        uint32_t bytes = ck_bytes(R) + 2u * uint32_t(sc.h) * 256u + uint32_t(L) * 4u + 3u * 256u;
+                        uint32_t bytes = uint32_t(ck_bytes(R) - SKIP) + 2u * uint32_t(sc.h) * 256u + uint32_t(L) * 4u + 3u * 256u;
                         if (KDA) bytes += uint32_t(sc.h) * 256u + 512u + 256u + 512u;
                         mbar_arrive_expect_tx(full + dsc, bytes);
                     } else {
@@ -826,7 +846,7 @@ __global__ void __launch_bounds__(96 + NG * GT, 1) step_pipelined_kernel(StepPar
             const StageLayout l0 = stage_layout(0, L, R, KDA), l1 = stage_layout(1, L, R, KDA);
             int which = -1;                                              // member of the layout this lane copies into
             switch (lane) {
-                case 0: c_base = P.ssm; c_slot = uint32_t(P.d.SS) * 4u; c_hv = VD * KD * 4u; b_fix = ck_bytes(R); break;
+                case 0: c_base = P.ssm + SKIP; c_slot = uint32_t(P.d.SS) * 4u; c_hv = VD * KD * 4u; b_fix = ck_bytes(R) - SKIP; o_fix = SKIP; break;
                 case 1: c_base = reinterpret_cast<const char*>(P.Kbuf); c_slot = uint32_t(HV) * rowb; c_hv = rowb; b_h = 256u; which = 0; break;
                 case 2: c_base = reinterpret_cast<const char*>(P.Ubuf); c_slot = uint32_t(HV) * rowb; c_hv = rowb; b_h = 256u; which = 1; break;
                 case 3: c_base = reinterpret_cast<const char*>(P.Wbuf); c_slot = uint32_t(HV * L) * 4u; c_hv = uint32_t(L) * 4u; b_fix = uint32_t(L) * 4u; which = 2; break;
@@ -852,7 +872,7 @@ __global__ void __launch_bounds__(96 + NG * GT, 1) step_pipelined_kernel(StepPar
                 if (lane == 0) atomicOr(&g_status, ST_PRODUCER_TIMEOUT);
                 return;
             }
-            char* st = stage_smem + doff[dsc];
+            char* st = stage_smem + doff[dsc] - SKIP;
             const int rows = doff[ND + NG + dsc];
             const ProgScalars sc = *reinterpret_cast<const ProgScalars*>(st + stage_layout(rows, L, R, KDA).sc);
             if (prog_live(sc, L)) {
@@ -872,15 +892,18 @@ __global__ void __launch_bounds__(96 + NG * GT, 1) step_pipelined_kernel(StepPar
         return;
     }
 
-    if (warp == 2) {
-        // ================= prologue warp: every program in fill order =================
-        for (int i = 0; i < nit; ++i) {
+    if (warp < 2 + NPW) {
+        // ================= prologue warps: programs dealt round-robin, each warp in fill order =================
+        for (int i = warp - 2; i < nit; i += NPW) {
             const int dsc = i % ND;
+#ifdef LQ_TRACE
+            if (i < 256 && blockIdx.x < 160 && lane == 0) g_ntrace[(blockIdx.x * 256 + i) * 8 + 7] = clock64();
+#endif
             if (!warp_wait_bounded(full + dsc, uint32_t(i / ND) & 1u, lane)) {
                 if (lane == 0) atomicOr(&g_status, ST_PROLOGUE_TIMEOUT);
                 return;
             }
-            char* st = stage_smem + doff[dsc];
+            char* st = stage_smem + doff[dsc] - SKIP;
             const int rows = doff[ND + NG + dsc];                  // rows the stage was sized for (h, or 0 for a dead program)
             const ProgScalars sc = *reinterpret_cast<const ProgScalars*>(st + stage_layout(rows, L, R, KDA).sc);
             if (lane == 0) LQ_STAMP(i, 1);
@@ -895,12 +918,44 @@ __global__ void __launch_bounds__(96 + NG * GT, 1) step_pipelined_kernel(StepPar
     }
 
     // ================= consumers: group g takes programs g, g + NG, ... =================
-    const int g = (warp - 3) / GW;
-    const int t = tid - 96 - g * GT;
+    const int g = (warp - 2 - NPW) / GW;
+    const int t = tid - UT - g * GT;
     const int bar = 1 + g;
     const GroupScratch gs = carve_scratch(scratch0 + g * SCRATCH_BYTES);
     volatile int* gflag = gflag0 + g;
+    // Register path of the int8 tile: lane (gid, tig) of warp w keeps, for each of its m16 tiles, rows gid and gid + 8 at
+    // columns 16 tig and 64 + 16 tig (the fragment order of step_body).  The loads of program i + NG are issued when the
+    // tile phase of program i has consumed the registers; the slot of the program after that is fetched at the same time.
+    uint4 ac[4 * MT];
+    int slot_n = 0;                                              // slot of the next program of this group (<= 0: no loads)
+    auto slot_of = [&](int i2) -> int {
+        if (!REGC || i2 >= nit) return 0;
+        return P.idx[(bid + i2 * grid) / HV];
+    };
+    auto load_codes = [&](int i2, int slot) {
+        if (!REGC || i2 >= nit || slot <= 0) return;
+        const int p2 = bid + i2 * grid;
+        const int hv2 = p2 - (p2 / HV) * HV;
+        const int lane = t & 31, gid = lane >> 2, tig = lane & 3;
+        const char* base = P.ssm + (int64_t(slot) * P.d.SS + int64_t(hv2) * VD * KD) * 4 +
+                           ((VD / GW) * (t >> 5) + gid) * KD + tig * 16;
+#pragma unroll
+        for (int mt = 0; mt < MT; ++mt) {
+            ac[4 * mt] = ldg_stream(base + (16 * mt) * KD);
+            ac[4 * mt + 1] = ldg_stream(base + (16 * mt) * KD + 64);
+            ac[4 * mt + 2] = ldg_stream(base + (16 * mt + 8) * KD);
+            ac[4 * mt + 3] = ldg_stream(base + (16 * mt + 8) * KD + 64);
+        }
+    };
+    if (REGC) {
+        load_codes(g, slot_of(g));
+        slot_n = slot_of(g + NG);
+    }
     for (int i = g; i < nit; i += NG) {
+        auto refill = [&] {
+            load_codes(i + NG, slot_n);
+            slot_n = slot_of(i + 2 * NG);
+        };
         const int dsc = i % ND;
         // one warp polls and publishes the outcome; the other warps sleep at the group barrier
         if (t < 32) {
@@ -912,7 +967,7 @@ __global__ void __launch_bounds__(96 + NG * GT, 1) step_pipelined_kernel(StepPar
             if (t == 0) atomicOr(&g_status, ST_CONSUMER_TIMEOUT);
             return;
         }
-        char* st = stage_smem + doff[dsc];
+        char* st = stage_smem + doff[dsc] - SKIP;
         const int rows = doff[ND + NG + dsc];
         const StageLayout lay = stage_layout(rows, L, R, KDA);
         const ProgScalars sc = *reinterpret_cast<const ProgScalars*>(st + lay.sc);
@@ -922,10 +977,18 @@ __global__ void __launch_bounds__(96 + NG * GT, 1) step_pipelined_kernel(StepPar
 #else
         auto release = [&] { mbar_arrive(empty + dsc); };
 #endif
+#ifdef LQ_NOBODY
+        if (false) {
+#else
         if (prog_live(sc, L)) {
-            step_body<R, KDA>(P, sc, st, lay, gs, t, bar, release, i);
+#endif
+            step_body<R, KDA, REGC>(P, sc, st, lay, gs, t, bar, release, ac, refill, i);
         } else {
+            refill();
             release();
+#ifdef LQ_NOBODY
+            if (t == 0 && prog_live(sc, L)) P.hcnt[int64_t(sc.slot) * P.d.HV + sc.hv] = sc.h + 1;
+#endif
             const int p = bid + i * grid;
             if (t < 64) reinterpret_cast<uint32_t*>(P.o)[int64_t(p) * 64 + t] = 0u;
         }
@@ -963,7 +1026,7 @@ static int launch_step(const StepParams& P, cudaStream_t st) {
     if (rc) return rc;
     const int nprog = P.N * P.d.HV;
     const int grid = nprog < device_sm_count() ? nprog : device_sm_count();
-    step_pipelined_kernel<R, KDA, NG><<<grid, 96 + NG * GT, smem, st>>>(P, ring_bytes);
+    step_pipelined_kernel<R, KDA, NG><<<grid, UT + NG * GT, smem, st>>>(P, ring_bytes);
     return finish_launch();
 }
 
