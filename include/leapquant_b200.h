@@ -60,7 +60,8 @@ int lq_last_cuda_error(void);
 int lq_device_status(int* status);
 
 /* Tuning / debugging switch, process-wide; no reference counterpart.  "step_impl": 0 = persistent CTAs fed by bulk
- * asynchronous copies (default), 1 = one CTA per (row, head) with plain loads.  Both run the same arithmetic. */
+ * asynchronous copies (default), 1 = one CTA per (row, head) with plain loads and the same arithmetic, 2 = one warp per
+ * (row, head) in registers (GDN only; KDA keeps the default).  1 and 2 exist for debugging and comparison. */
 int lq_set_option(const char* name, int32_t value);
 
 /* GDN decode step.  Replaces the kernel built by make_gdn_step (reference leapquant/kernels.py:27-692, launch
