@@ -1,54 +1,72 @@
 // Window-flush kernel (sm_100a): rebuild -> rank-R subspace iteration -> residual -> smoothing scales -> INT8.
 //
-// Persistent CTAs of 256 threads.  Every CTA scans the due flags of all (row, head) programs of the call, ranks the
-// due ones in a fixed order and keeps the ranks congruent to its block index, so the work is balanced to +-1 head
-// per CTA whatever the pattern of full windows, and the launch shape never depends on device data.
-// The rebuilt 128 x 128 state B and the residual E stay in shared memory as fp32 for the whole program.
+// Persistent CTAs of 256 threads, two per SM.  Every CTA scans the due flags of all (row, head) programs of the call,
+// ranks the due ones in a fixed order and keeps the ranks congruent to its block index, so the work is balanced to +-1
+// head per CTA whatever the pattern of full windows, and the launch shape never depends on device data.
+//
+// All matrix products of a head run on the tensor cores (mma.sync m16n8k16, fp32 accumulate): the window product that
+// rebuilds the state B (bf16 operands, the scaled one as head + remainder), the tall-skinny products of the subspace
+// iteration with their rank-R corrections, and the residual.  B lives in shared memory as an f16 tile like the
+// reference's (leapquant/kernels.py:1156,1483); the residual E stays in registers in fp32 until it has become codes.
 #include "lq_linalg.cuh"
 
 namespace lq {
 
-constexpr int TS = 136;          // row stride (bf16 elements) of the staged window tiles: 272 B keeps ldmatrix rows conflict-free
+constexpr int TS = 136;          // row stride (16-bit elements) of the window tiles and of the f16 state tile: 272 B moves
+                                 // every row one 16-byte bank group on, so ldmatrix and fragment loads are conflict-free
+constexpr int HS = TS;           // row stride of the factor rows [r][128]
+
+template <int R> struct FlushK { static constexpr int KC = (R == 4) ? 16 : 32, KS = KC + 8; };  // residual operand rows
 
 struct FlushSmem {
-    float* B;        // [128][LDB]
-    uint16_t* Kt;    // [Lp][TS] window keys, bf16 as stored (rows L.. zero)
-    uint16_t* Ut;    // [Lp][TS] window values, bf16 as stored (rows L.. zero)
-    float* tab;      // KDA: [L][128] scale of key (j, c): w_j D_j[c]
-    float* scr;      // [128][R]   (aliases the window tiles: used after the rebuild only)
-    float* colpart;  // [16][128]  (aliases the window tiles)
-    float* Uo;       // [R][128] old U^T (KDA: times pc)
-    float* Qo;       // [R][128] old Q^T
-    float* Un;       // [128][R] P / new U
-    float* Qn;       // [128][R] Q
-    float* Msm;      // [R][R]
-    float* sk;       // [128] column scale operand of the dequant (KDA: Sk pc); later 1 / Sk_new
-    float* sv;       // [128]
-    float* pc;       // [128]
-    float* w;        // [64]
-    int* wcnt;       // [8]
-    int* dlist;      // [maxd]
+    uint16_t* Bh;      // [128][TS] f16 state tile B[v][c]; at the end a warp's 16 rows hold its int8 codes for the coalesced store
+    uint16_t* Kt;      // [Lp][TS] window keys, bf16 as stored (rows L.. zero)
+    uint16_t* Ut;      // [Lp][TS] window values, bf16 as stored (rows L.. zero)
+    // the window tiles are dead after the rebuild; the region then holds:
+    uint16_t* Ac;      // [128][KS] f16 residual operand, row v:  Q | p Q_old head | p Q_old remainder | 0
+    uint16_t* Bc;      // [128][KS] f16 residual operand, row c: -U |   U_old      |   U_old           | 0
+    float* colpart;    // [8][128] per-warp column sums of |E|
+    float* Qn;         // [128][R] fp32 Q for CholeskyQR
+    float* tab;        // KDA: [L][128] scale of key (j, c): w_j D_j[c]
+    uint16_t* Qh;      // [R][HS] f16 Q^T  (current iterate)
+    uint16_t* Ph;      // [R][HS] f16 P^T = new U^T
+    uint16_t* Qoh;     // [R][HS] f16 old Q^T
+    uint16_t* Uoh;     // [R][HS] f16 old U^T (KDA: times pc, rounded to f16 like the reference, leapquant/kernels.py:1448-1466)
+    uint16_t* QoT;     // [128][8] f16 old Q, zero-padded columns R..7
+    uint16_t* UoT;     // [128][8] f16 old U
+    float* sk;         // [128] column scale operand of the dequant (KDA: Sk pc); later 1 / Sk_new
+    float* sv;         // [128]
+    float* pc;         // [128]
+    float* w;          // [64]
+    int* wcnt;         // [8]
+    int* dlist;        // [maxd]
 };
 
 __host__ __device__ inline int flush_lp(int L) { return (L + 15) & ~15; }
-// floats of the region shared by the window tiles (rebuild) and scr + colpart (afterwards)
+// bytes of the region shared by the window tiles (rebuild) and Ac + Bc + colpart + Qn (afterwards)
 template <int R>
-__host__ __device__ inline int flush_region_floats(int L) {
-    const int tiles = flush_lp(L) * TS;                     // two bf16 tiles = Lp * TS floats
-    const int later = 128 * R + 16 * 128;
+__host__ __device__ inline int flush_region_bytes(int L) {
+    const int tiles = 2 * flush_lp(L) * TS * 2;
+    const int later = 2 * 128 * FlushK<R>::KS * 2 + 8 * 128 * 4 + 128 * R * 4;
     return tiles > later ? tiles : later;
 }
 template <int R>
-__host__ __device__ inline size_t flush_smem_floats(int L, int maxd, bool kda) {
-    return size_t(128) * LDB + flush_region_floats<R>(L) + (kda ? size_t(L) * 128 : 0) + 2 * R * 128 + 2 * 128 * R + 64 +
-           3 * 128 + 64 + 8 + maxd;
+__host__ __device__ inline size_t flush_smem_bytes(int L, int maxd, bool kda) {
+    return size_t(128) * TS * 2 + flush_region_bytes<R>(L) + (kda ? size_t(L) * 128 * 4 : 0) + 4 * R * HS * 2 + 2 * 128 * 8 * 2 +
+           3 * 128 * 4 + 64 * 4 + 8 * 4 + size_t(maxd) * 4 + 16;
 }
 
-// ---- warp-level tensor-core helpers (legacy mma.sync path; the rebuild is a real 128 x 128 x L product) ----
+// ---- warp-level tensor-core helpers (mma.sync path) ----
 __device__ __forceinline__ void mma_bf16_16816(float (&c)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
     asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
                  : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
                  : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ void mma_h_16816(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0,
+                                            uint32_t b1) {
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+                 : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+                 : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
 }
 __device__ __forceinline__ void ldmatrix_x4_trans(uint32_t (&r)[4], const void* smem_row) {
     const uint32_t addr = uint32_t(__cvta_generic_to_shared(smem_row));
@@ -56,12 +74,65 @@ __device__ __forceinline__ void ldmatrix_x4_trans(uint32_t (&r)[4], const void* 
                  : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3])
                  : "r"(addr));
 }
+__device__ __forceinline__ void ldmatrix_x4(uint32_t (&r)[4], const void* smem_row) {
+    const uint32_t addr = uint32_t(__cvta_generic_to_shared(smem_row));
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3])
+                 : "r"(addr));
+}
+__device__ __forceinline__ uint32_t pack_h2(float a, float b) {
+    const __half2 h = __floats2half2_rn(a, b);
+    return *reinterpret_cast<const uint32_t*>(&h);
+}
+__device__ __forceinline__ float2 unpack_h2(uint32_t x) { return __half22float2(*reinterpret_cast<const __half2*>(&x)); }
 // x (fp32) ~ hi + lo as two bf16 pieces (16 mantissa bits, relative error 2^-17): the split the reference uses for the
 // same operand (reference leapquant/kernels.py:1508-1511).  The tensor pipe bounds the rebuild, so a third piece
 // would cost 50 % more time for accuracy far below the INT8 step.
 __device__ __forceinline__ void split2(float x, float& hi, float& lo) {
     hi = round_bf16(x);
     lo = round_bf16(x - hi);
+}
+
+// One tall-skinny product of the subspace iteration with its rank-R correction, all eight warps, all in registers:
+//   TRANS:  Y[c][r] = sum_v B[v][c] X[v][r] + p sum_r' Z[r'][c] (sum_v W[r'][v] X[v][r])     (P = T^T Q:  X = Q, W = Q_old, Z = U_old)
+//   !TRANS: Y[v][r] = sum_c B[v][c] X[c][r] + p sum_r' Z[r'][v] (sum_c W[r'][c] X[c][r])     (Q = T P:    X = P, W = U_old, Z = Q_old)
+// Xh, Wh: f16 rows [r][128] (stride HS); ZT: f16 [128][8] (Z transposed, columns R..7 zero).  All operands are f16 values by
+// definition of the algorithm (B tile, rounded iterates, stored factors), so one mma per tile is exact up to the fp32
+// accumulation; the small Gram matrix M^T = X^T W^T comes out of a second mma in exactly the fragment a third mma needs
+// as its B operand (times p, as head + remainder).  Warp w owns the output rows 16 w .. 16 w + 15; lane (gid, tig) returns
+// d = { Y[16w+gid][2tig], Y[16w+gid][2tig+1], Y[16w+gid+8][2tig], Y[16w+gid+8][2tig+1] }, meaningful for 2 tig < R.
+template <int R, bool TRANS>
+__device__ __forceinline__ void tall_product(const uint16_t* __restrict__ Bh, const uint16_t* __restrict__ Xh,
+                                             const uint16_t* __restrict__ Wh, const uint16_t* __restrict__ ZT, float p,
+                                             int warp, int lane, float (&d)[4]) {
+    const int gid = lane >> 2, tig = lane & 3, m0 = warp * 16;
+    const bool on = gid < R;
+    float g[4] = {0.f, 0.f, 0.f, 0.f};
+    d[0] = d[1] = d[2] = d[3] = 0.f;
+    const uint16_t* xr = Xh + (on ? gid : 0) * HS + 2 * tig;
+    const uint16_t* wr = Wh + (on ? gid : 0) * HS + 2 * tig;
+    const uint16_t* arow = TRANS ? Bh + ((lane & 7) + 8 * (lane >> 4)) * TS + m0 + 8 * ((lane >> 3) & 1)
+                                 : Bh + (m0 + (lane & 7) + 8 * ((lane >> 3) & 1)) * TS + 8 * (lane >> 4);
+#pragma unroll
+    for (int ks = 0; ks < 8; ++ks) {
+        uint32_t a[4];
+        if (TRANS) ldmatrix_x4_trans(a, arow + ks * 16 * TS);
+        else ldmatrix_x4(a, arow + ks * 16);
+        const uint32_t x0 = on ? *reinterpret_cast<const uint32_t*>(xr + ks * 16) : 0u;
+        const uint32_t x1 = on ? *reinterpret_cast<const uint32_t*>(xr + ks * 16 + 8) : 0u;
+        const uint32_t w0 = on ? *reinterpret_cast<const uint32_t*>(wr + ks * 16) : 0u;
+        const uint32_t w1 = on ? *reinterpret_cast<const uint32_t*>(wr + ks * 16 + 8) : 0u;
+        mma_h_16816(d, a[0], a[1], a[2], a[3], x0, x1);
+        mma_h_16816(g, x0, 0u, x1, 0u, w0, w1);              // rows 0..7 of the tile: (M^T)[r = gid][r' = 2 tig, 2 tig + 1]
+    }
+    const float c0 = p * g[0], c1 = p * g[1];
+    const __half2 hh = __floats2half2_rn(c0, c1);
+    const float2 hf = __half22float2(hh);
+    const uint32_t bh = *reinterpret_cast<const uint32_t*>(&hh), bl = pack_h2(c0 - hf.x, c1 - hf.y);
+    const uint32_t z0 = *reinterpret_cast<const uint32_t*>(ZT + (m0 + gid) * 8 + 2 * tig);
+    const uint32_t z1 = *reinterpret_cast<const uint32_t*>(ZT + (m0 + gid + 8) * 8 + 2 * tig);
+    mma_h_16816(d, z0, z1, 0u, 0u, bh, 0u);
+    mma_h_16816(d, z0, z1, 0u, 0u, bl, 0u);
 }
 
 #ifdef LQ_TRACE
@@ -72,32 +143,36 @@ static __device__ long long g_ftrace[320 * 16];
 #endif
 
 template <int R, bool KDA>
-__global__ void __launch_bounds__(NT_LA, (R == 4 ? 2 : 1))
+__global__ void __launch_bounds__(NT_LA, 2)
 flush_kernel(lq_dims d, char* __restrict__ ssm, const uint16_t* __restrict__ Kbuf, const uint16_t* __restrict__ Ubuf,
              float* __restrict__ Wbuf, float* __restrict__ Pbuf, uint16_t* __restrict__ Gbuf, int32_t* __restrict__ hcnt,
              const float* __restrict__ Q0, const int32_t* __restrict__ idx, int N, int iters, int maxd) {
     extern __shared__ __align__(16) float smem[];
+    constexpr int KC = FlushK<R>::KC, KS = FlushK<R>::KS;
     FlushSmem s;
     const int Lp = flush_lp(d.L);
     {
-        float* p = smem;
-        s.B = p; p += 128 * LDB;
+        char* p = reinterpret_cast<char*>(smem);
+        s.Bh = reinterpret_cast<uint16_t*>(p); p += 128 * TS * 2;
         s.Kt = reinterpret_cast<uint16_t*>(p);
         s.Ut = s.Kt + Lp * TS;
-        s.scr = p;
-        s.colpart = p + 128 * R;
-        p += flush_region_floats<R>(d.L);
-        s.tab = p; p += KDA ? d.L * 128 : 0;
-        s.Uo = p; p += R * 128;
-        s.Qo = p; p += R * 128;
-        s.Un = p; p += 128 * R;
-        s.Qn = p; p += 128 * R;
-        s.Msm = p; p += 64;
-        s.sk = p; p += 128;
-        s.sv = p; p += 128;
-        s.pc = p; p += 128;
-        s.w = p; p += 64;
-        s.wcnt = reinterpret_cast<int*>(p); p += 8;
+        s.Ac = reinterpret_cast<uint16_t*>(p);
+        s.Bc = s.Ac + 128 * KS;
+        s.colpart = reinterpret_cast<float*>(s.Bc + 128 * KS);
+        s.Qn = s.colpart + 8 * 128;
+        p += flush_region_bytes<R>(d.L);
+        s.tab = reinterpret_cast<float*>(p); p += KDA ? d.L * 128 * 4 : 0;
+        s.Qh = reinterpret_cast<uint16_t*>(p); p += R * HS * 2;
+        s.Ph = reinterpret_cast<uint16_t*>(p); p += R * HS * 2;
+        s.Qoh = reinterpret_cast<uint16_t*>(p); p += R * HS * 2;
+        s.Uoh = reinterpret_cast<uint16_t*>(p); p += R * HS * 2;
+        s.QoT = reinterpret_cast<uint16_t*>(p); p += 128 * 8 * 2;
+        s.UoT = reinterpret_cast<uint16_t*>(p); p += 128 * 8 * 2;
+        s.sk = reinterpret_cast<float*>(p); p += 128 * 4;
+        s.sv = reinterpret_cast<float*>(p); p += 128 * 4;
+        s.pc = reinterpret_cast<float*>(p); p += 128 * 4;
+        s.w = reinterpret_cast<float*>(p); p += 64 * 4;
+        s.wcnt = reinterpret_cast<int*>(p); p += 8 * 4;
         s.dlist = reinterpret_cast<int*>(p);
     }
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
@@ -160,7 +235,14 @@ flush_kernel(lq_dims d, char* __restrict__ ssm, const uint16_t* __restrict__ Kbu
     const int mine = (ndue > bid) ? min((ndue - bid + G - 1) / G, maxd) : 0;
     __syncthreads();
 
-    const int ty = tid >> 4, tx = tid & 15, v0 = ty * 8;
+    const int gid = lane >> 2, tig = lane & 3;
+    if (R < 8) {                                               // zero padding of the transposed old factors, written once
+        for (int i = tid; i < 128 * (8 - R); i += NT_LA) {
+            const int c = i / (8 - R), r = R + i % (8 - R);
+            s.UoT[c * 8 + r] = 0;
+            s.QoT[c * 8 + r] = 0;
+        }
+    }
 #ifdef LQ_TRACE
     long long facc[16] = {0}, flast = clock64();
 #endif
@@ -183,11 +265,17 @@ flush_kernel(lq_dims d, char* __restrict__ ssm, const uint16_t* __restrict__ Kbu
             s.sv[tid] = reinterpret_cast<const float*>(base + CK_SV)[tid];
         }
         {
+            // old factors as stored (f16); KDA: U^T times pc, rounded to f16.  Kept as rows [r][128] and transposed [128][8].
             const uint16_t* uq = reinterpret_cast<const uint16_t*>(base + CK_UQ);
             for (int i = tid; i < R * 128; i += NT_LA) {
                 const int r = i >> 7, c = i & 127;
-                s.Uo[i] = f16_to_f(uq[r * (KD + VD) + c]);
-                s.Qo[i] = f16_to_f(uq[r * (KD + VD) + KD + c]);
+                uint16_t u = uq[r * (KD + VD) + c];
+                const uint16_t qv = uq[r * (KD + VD) + KD + c];
+                if (KDA) u = f_to_f16(f16_to_f(u) * expf(Pbuf[sh * KD + c]));
+                s.Uoh[r * HS + c] = u;
+                s.Qoh[r * HS + c] = qv;
+                s.UoT[c * 8 + r] = u;
+                s.QoT[c * 8 + r] = qv;
             }
         }
         LQ_FSTAMP(1);
@@ -204,16 +292,13 @@ flush_kernel(lq_dims d, char* __restrict__ ssm, const uint16_t* __restrict__ Kbu
         }
         __syncthreads();
         if (KDA && tid < 128) {
-            // key scale w_j D_j[c] with D_{L-1} = 1, D_j = D_{j+1} e_{j+1}; old U^T times pc
+            // key scale w_j D_j[c] with D_{L-1} = 1, D_j = D_{j+1} e_{j+1}
             float dcur = 1.f;
             const uint16_t* gb = Gbuf + sh * L * KD + tid;
             for (int j = L - 1; j >= 0; --j) {
                 s.tab[j * 128 + tid] = s.w[j] * dcur;
                 dcur *= f16_to_f(gb[j * KD]);
             }
-            const float pcv = s.pc[tid];
-#pragma unroll
-            for (int r = 0; r < R; ++r) s.Uo[r * 128 + tid] *= pcv;
         }
         if (KDA) __syncthreads();
 
@@ -283,7 +368,7 @@ flush_kernel(lq_dims d, char* __restrict__ ssm, const uint16_t* __restrict__ Kbu
                 }
             }
             LQ_FSTAMP(13);
-            // add the dequantised checkpoint and store B[v][c]; accumulator (e, nt): row m0 + r + 8 (e >> 1), col 8 nt + q2 + (e & 1)
+            // add the dequantised checkpoint and store B[v][c] as f16; accumulator (e, nt): row m0 + r + 8 (e >> 1), col 8 nt + q2 + (e & 1)
             const float pq = KDA ? (1.0f / QMAX) : (p / QMAX);
 #pragma unroll
             for (int nt = 0; nt < 16; ++nt) {
@@ -291,108 +376,138 @@ flush_kernel(lq_dims d, char* __restrict__ ssm, const uint16_t* __restrict__ Kbu
                 for (int hrow = 0; hrow < 2; ++hrow) {
                     const int mm = m0 + r + 8 * hrow, nn = 8 * nt + q2;
                     const uint32_t cw = (cpre[nt] >> (16 * hrow)) & 0xffffu;
+                    const float f0 = float(int(int8_t(cw & 0xff))), f1 = float(int(int8_t(cw >> 8)));
                     if (!KDA) {                                 // (v, c) = (mm, nn), (mm, nn + 1): two adjacent codes
                         const float svr = s.sv[mm] * pq;
-                        const float f0 = float(int(int8_t(cw & 0xff))), f1 = float(int(int8_t(cw >> 8)));
                         const float o0 = (f0 * svr) * s.sk[nn] + acc[nt][2 * hrow];
                         const float o1 = (f1 * svr) * s.sk[nn + 1] + acc[nt][2 * hrow + 1];
-                        *reinterpret_cast<float2*>(s.B + mm * LDB + nn) = make_float2(o0, o1);
+                        *reinterpret_cast<uint32_t*>(s.Bh + mm * TS + nn) = pack_h2(o0, o1);
                     } else {                                    // (c, v) = (mm, nn), (mm, nn + 1): codes of rows nn, nn + 1
-                        const float f0 = float(int(int8_t(cw & 0xff))), f1 = float(int(int8_t(cw >> 8)));
                         const float skc = s.sk[mm];
-                        s.B[nn * LDB + mm] = (f0 * (s.sv[nn] * pq)) * skc + acc[nt][2 * hrow];
-                        s.B[(nn + 1) * LDB + mm] = (f1 * (s.sv[nn + 1] * pq)) * skc + acc[nt][2 * hrow + 1];
+                        s.Bh[nn * TS + mm] = f_to_f16((f0 * (s.sv[nn] * pq)) * skc + acc[nt][2 * hrow]);
+                        s.Bh[(nn + 1) * TS + mm] = f_to_f16((f1 * (s.sv[nn + 1] * pq)) * skc + acc[nt][2 * hrow + 1]);
                     }
                 }
             }
         }
-        __syncthreads();                                        // the window tiles are dead: scr / colpart may use the region
+        __syncthreads();                                        // the window tiles are dead: the region may be reused
         LQ_FSTAMP(3);
-        for (int i = tid; i < 128 * R; i += NT_LA) s.Qn[i] = round_f16(Q0[i]);
+        for (int i = tid; i < 128 * R; i += NT_LA) s.Qh[(i % R) * HS + i / R] = f_to_f16(Q0[i]);
         __syncthreads();
 
         LQ_FSTAMP(4);
         // ---- stage C: subspace iteration on T = B + p Q_old U_old^T ----
-        // P = T^T Q  (rounded to fp16 values)
-        coldot<R>(s.B, s.Qn, s.Un, s.scr, tid);
-        factor_gram<R>(s.Qo, s.Qn, s.Msm, tid);
-        factor_apply<R, true>(s.Uo, s.Msm, s.Un, p, tid);
+        const int m0w = warp * 16;
+        float dd[4];
+        auto store_p = [&] {                                    // P (rounded to f16) as rows [r][c]
+            if (2 * tig < R) {
+                s.Ph[(2 * tig) * HS + m0w + gid] = f_to_f16(dd[0]);
+                s.Ph[(2 * tig + 1) * HS + m0w + gid] = f_to_f16(dd[1]);
+                s.Ph[(2 * tig) * HS + m0w + gid + 8] = f_to_f16(dd[2]);
+                s.Ph[(2 * tig + 1) * HS + m0w + gid + 8] = f_to_f16(dd[3]);
+            }
+        };
+        tall_product<R, true>(s.Bh, s.Qh, s.Qoh, s.UoT, p, warp, lane, dd);         // P = T^T Q
+        store_p();
+        __syncthreads();
         LQ_FSTAMP(5);
         for (int it = 0; it < iters; ++it) {
-            rowdot<R>(s.B, s.Un, s.Qn, s.scr, tid);          // Q = T P
-            factor_gram<R>(s.Uo, s.Un, s.Msm, tid);
-            factor_apply<R, false>(s.Qo, s.Msm, s.Qn, p, tid);
+            tall_product<R, false>(s.Bh, s.Ph, s.Uoh, s.QoT, p, warp, lane, dd);    // Q = T P
+            if (2 * tig < R) {
+                *reinterpret_cast<float2*>(s.Qn + (m0w + gid) * R + 2 * tig) = make_float2(dd[0], dd[1]);
+                *reinterpret_cast<float2*>(s.Qn + (m0w + gid + 8) * R + 2 * tig) = make_float2(dd[2], dd[3]);
+            }
+            __syncthreads();
             LQ_FSTAMP(6);
             cholqr2_f16<R>(s.Qn, tid);
+            for (int i = tid; i < 128 * R; i += NT_LA) s.Qh[(i % R) * HS + i / R] = f_to_f16(s.Qn[i]);
+            __syncthreads();
             LQ_FSTAMP(7);
-            coldot<R>(s.B, s.Qn, s.Un, s.scr, tid);          // P = T^T Q
-            factor_gram<R>(s.Qo, s.Qn, s.Msm, tid);
-            factor_apply<R, true>(s.Uo, s.Msm, s.Un, p, tid);
+            tall_product<R, true>(s.Bh, s.Qh, s.Qoh, s.UoT, p, warp, lane, dd);     // P = T^T Q
+            store_p();
+            __syncthreads();
         }
 
         LQ_FSTAMP(8);
-        // ---- stage D: new factors to the checkpoint ----
-        {
-            uint16_t* uq = reinterpret_cast<uint16_t*>(base + CK_UQ);
-            for (int i = tid; i < R * 128; i += NT_LA) {
-                const int r = i >> 7, c = i & 127;
-                uq[r * (KD + VD) + c] = f_to_f16(s.Un[c * R + r]);
-                uq[r * (KD + VD) + KD + c] = f_to_f16(s.Qn[c * R + r]);
-            }
+        // ---- stage D: new factors to the checkpoint (16-byte copies of the f16 rows); operands of the residual ----
+        if (tid < R * 32) {
+            const int r = tid >> 5, j = tid & 31;
+            const uint16_t* src = (j < 16) ? s.Ph + r * HS + j * 8 : s.Qh + r * HS + (j - 16) * 8;
+            reinterpret_cast<uint4*>(base + CK_UQ)[r * 32 + j] = *reinterpret_cast<const uint4*>(src);
         }
+        if (tid < 128) {
+            uint16_t* row = s.Ac + tid * KS;
+#pragma unroll
+            for (int r = 0; r < R; ++r) {
+                row[r] = s.Qh[r * HS + tid];
+                const float x = p * f16_to_f(s.Qoh[r * HS + tid]);
+                const uint16_t hi = f_to_f16(x);
+                row[R + r] = hi;
+                row[2 * R + r] = f_to_f16(x - f16_to_f(hi));
+            }
+#pragma unroll
+            for (int c = 3 * R; c < KC; ++c) row[c] = 0;
+        } else {
+            const int c = tid - 128;
+            uint16_t* row = s.Bc + c * KS;
+#pragma unroll
+            for (int r = 0; r < R; ++r) {
+                row[r] = s.Ph[r * HS + c] ^ 0x8000u;
+                row[R + r] = row[2 * R + r] = s.Uoh[r * HS + c];
+            }
+#pragma unroll
+            for (int c2 = 3 * R; c2 < KC; ++c2) row[c2] = 0;
+        }
+        __syncthreads();
 
         LQ_FSTAMP(9);
-        // ---- stage E: residual E = B + p Q_old U_old^T - Q U^T in place, column sums of |E| ----
+        // ---- stage E: residual E = B + p Q_old U_old^T - Q U^T on the tensor cores, fp32 in registers: warp w owns rows
+        //      16 w .. 16 w + 15, lane (gid, tig) holds rows gid, gid + 8 at columns 8 nt + 2 tig, + 1 ----
+        float e[16][4];
         {
-            float colp[8];
+            const uint16_t* b0p = s.Bh + (m0w + gid) * TS + 2 * tig;
 #pragma unroll
-            for (int c = 0; c < 8; ++c) colp[c] = 0.f;
-            float uo[R][8], un[R][8];
-#pragma unroll
-            for (int r = 0; r < R; ++r)
-#pragma unroll
-                for (int c = 0; c < 4; ++c) {
-                    uo[r][c] = s.Uo[r * 128 + 4 * tx + c];
-                    uo[r][4 + c] = s.Uo[r * 128 + 64 + 4 * tx + c];
-                    un[r][c] = s.Un[(4 * tx + c) * R + r];
-                    un[r][4 + c] = s.Un[(64 + 4 * tx + c) * R + r];
-                }
-#pragma unroll
-            for (int i = 0; i < 8; ++i) {
-                float qo[R], qn[R];
-#pragma unroll
-                for (int r = 0; r < R; ++r) {
-                    qo[r] = s.Qo[r * 128 + v0 + i];
-                    qn[r] = s.Qn[(v0 + i) * R + r];
-                }
-                float4 ba = *reinterpret_cast<const float4*>(s.B + (v0 + i) * LDB + 4 * tx);
-                float4 bb = *reinterpret_cast<const float4*>(s.B + (v0 + i) * LDB + 64 + 4 * tx);
-                float e[8] = {ba.x, ba.y, ba.z, ba.w, bb.x, bb.y, bb.z, bb.w};
-#pragma unroll
-                for (int c = 0; c < 8; ++c) {
-                    float t1 = 0.f, t2 = 0.f;
-#pragma unroll
-                    for (int r = 0; r < R; ++r) {
-                        t1 = fmaf(qo[r], uo[r][c], t1);
-                        t2 = fmaf(qn[r], un[r][c], t2);
-                    }
-                    e[c] = fmaf(p, t1, e[c]) - t2;
-                    colp[c] += fabsf(e[c]);
-                }
-                *reinterpret_cast<float4*>(s.B + (v0 + i) * LDB + 4 * tx) = make_float4(e[0], e[1], e[2], e[3]);
-                *reinterpret_cast<float4*>(s.B + (v0 + i) * LDB + 64 + 4 * tx) = make_float4(e[4], e[5], e[6], e[7]);
+            for (int nt = 0; nt < 16; ++nt) {
+                const float2 lo = unpack_h2(*reinterpret_cast<const uint32_t*>(b0p + 8 * nt));
+                const float2 hi = unpack_h2(*reinterpret_cast<const uint32_t*>(b0p + 8 * TS + 8 * nt));
+                e[nt][0] = lo.x; e[nt][1] = lo.y; e[nt][2] = hi.x; e[nt][3] = hi.y;
             }
 #pragma unroll
-            for (int c = 0; c < 4; ++c) {
-                s.colpart[ty * 128 + 4 * tx + c] = colp[c];
-                s.colpart[ty * 128 + 64 + 4 * tx + c] = colp[4 + c];
+            for (int ks = 0; ks < KC; ks += 16) {
+                const uint16_t* ap = s.Ac + (m0w + gid) * KS + ks + 2 * tig;
+                const uint32_t a0 = *reinterpret_cast<const uint32_t*>(ap), a1 = *reinterpret_cast<const uint32_t*>(ap + 8 * KS);
+                const uint32_t a2 = *reinterpret_cast<const uint32_t*>(ap + 8), a3 = *reinterpret_cast<const uint32_t*>(ap + 8 * KS + 8);
+#pragma unroll
+                for (int nt = 0; nt < 16; ++nt) {
+                    const uint16_t* bp = s.Bc + (8 * nt + gid) * KS + ks + 2 * tig;
+                    mma_h_16816(e[nt], a0, a1, a2, a3, *reinterpret_cast<const uint32_t*>(bp), *reinterpret_cast<const uint32_t*>(bp + 8));
+                }
             }
+        }
+        // column sums of |E|: 32 partial sums per lane (two rows each), folded over the eight row groups of the warp by
+        // three exchange levels that halve the number of values a lane keeps
+        {
+            const bool h4 = (lane & 16) != 0, h3 = (lane & 8) != 0, h2 = (lane & 4) != 0;
+            float c16[16], c8[8], c4[4];
+#pragma unroll
+            for (int i = 0; i < 16; ++i) {
+                const float a = fabsf(e[i >> 1][i & 1]) + fabsf(e[i >> 1][2 + (i & 1)]);
+                const float b = fabsf(e[8 + (i >> 1)][i & 1]) + fabsf(e[8 + (i >> 1)][2 + (i & 1)]);
+                c16[i] = (h4 ? b : a) + __shfl_xor_sync(0xffffffffu, h4 ? a : b, 16);
+            }
+#pragma unroll
+            for (int i = 0; i < 8; ++i) c8[i] = (h3 ? c16[8 + i] : c16[i]) + __shfl_xor_sync(0xffffffffu, h3 ? c16[i] : c16[8 + i], 8);
+#pragma unroll
+            for (int i = 0; i < 4; ++i) c4[i] = (h2 ? c8[4 + i] : c8[i]) + __shfl_xor_sync(0xffffffffu, h2 ? c8[i] : c8[4 + i], 4);
+            const int nt0 = (h4 ? 8 : 0) + (h3 ? 4 : 0) + (h2 ? 2 : 0);
+            *reinterpret_cast<float2*>(s.colpart + warp * 128 + 8 * nt0 + 2 * tig) = make_float2(c4[0], c4[1]);
+            *reinterpret_cast<float2*>(s.colpart + warp * 128 + 8 * (nt0 + 1) + 2 * tig) = make_float2(c4[2], c4[3]);
         }
         __syncthreads();
         if (tid < 128) {
             float m = 0.f;
 #pragma unroll
-            for (int t2 = 0; t2 < 16; ++t2) m += s.colpart[t2 * 128 + tid];
+            for (int t2 = 0; t2 < 8; ++t2) m += s.colpart[t2 * 128 + tid];
             m *= (1.0f / float(VD));
             const float skn = fmaxf(sqrtf(m), EPS);
             reinterpret_cast<float*>(base + CK_SK)[tid] = skn;
@@ -401,43 +516,39 @@ flush_kernel(lq_dims d, char* __restrict__ ssm, const uint16_t* __restrict__ Kbu
         __syncthreads();
 
         LQ_FSTAMP(10);
-        // ---- stage F: row scales and INT8 codes ----
+        // ---- stage F: row scales and INT8 codes, staged in the warp's own rows of the (dead) state tile ----
         {
-            const int l8 = lane & 7, g = lane >> 3;
-            uint32_t* codes = reinterpret_cast<uint32_t*>(base + CK_CODES);
-            float* svg = reinterpret_cast<float*>(base + CK_SV);
-            float rk[16];
+            float r0 = 0.f, r1 = 0.f;
 #pragma unroll
-            for (int i = 0; i < 4; ++i) {
-                const float4 r4 = *reinterpret_cast<const float4*>(s.sk + i * 32 + l8 * 4);
-                rk[4 * i + 0] = r4.x; rk[4 * i + 1] = r4.y; rk[4 * i + 2] = r4.z; rk[4 * i + 3] = r4.w;
+            for (int nt = 0; nt < 16; ++nt) {
+                const float2 rk = *reinterpret_cast<const float2*>(s.sk + 8 * nt + 2 * tig);
+                e[nt][0] *= rk.x; e[nt][1] *= rk.y; e[nt][2] *= rk.x; e[nt][3] *= rk.y;
+                r0 = fmaxf(r0, fmaxf(fabsf(e[nt][0]), fabsf(e[nt][1])));
+                r1 = fmaxf(r1, fmaxf(fabsf(e[nt][2]), fabsf(e[nt][3])));
             }
-#pragma unroll 1
-            for (int it = 0; it < 4; ++it) {
-                const int row = warp * 16 + it * 4 + g;
-                float x[16];
-                float rmax = 0.f;
-#pragma unroll
-                for (int i = 0; i < 4; ++i) {
-                    const float4 ev = *reinterpret_cast<const float4*>(s.B + row * LDB + i * 32 + l8 * 4);
-                    x[4 * i + 0] = ev.x * rk[4 * i + 0];
-                    x[4 * i + 1] = ev.y * rk[4 * i + 1];
-                    x[4 * i + 2] = ev.z * rk[4 * i + 2];
-                    x[4 * i + 3] = ev.w * rk[4 * i + 3];
-                }
-#pragma unroll
-                for (int i = 0; i < 16; ++i) rmax = fmaxf(rmax, fabsf(x[i]));
-                rmax = fmaxf(rmax, __shfl_xor_sync(0xffffffffu, rmax, 1));
-                rmax = fmaxf(rmax, __shfl_xor_sync(0xffffffffu, rmax, 2));
-                rmax = fmaxf(rmax, __shfl_xor_sync(0xffffffffu, rmax, 4));
-                const float svv = fmaxf(rmax, EPS);
-                const float rm = QMAX * __frcp_rn(svv);
-                if (l8 == 0) svg[row] = svv;
-#pragma unroll
-                for (int i = 0; i < 4; ++i)
-                    codes[row * 32 + i * 8 + l8] = pack4(rne_code(x[4 * i + 0], rm), rne_code(x[4 * i + 1], rm),
-                                                         rne_code(x[4 * i + 2], rm), rne_code(x[4 * i + 3], rm));
+            r0 = fmaxf(r0, __shfl_xor_sync(0xffffffffu, r0, 1)); r1 = fmaxf(r1, __shfl_xor_sync(0xffffffffu, r1, 1));
+            r0 = fmaxf(r0, __shfl_xor_sync(0xffffffffu, r0, 2)); r1 = fmaxf(r1, __shfl_xor_sync(0xffffffffu, r1, 2));
+            const float sv0 = fmaxf(r0, EPS), sv1 = fmaxf(r1, EPS);
+            const float rm0 = QMAX * __frcp_rn(sv0), rm1 = QMAX * __frcp_rn(sv1);
+            if (tig == 0) {
+                float* svg = reinterpret_cast<float*>(base + CK_SV);
+                svg[m0w + gid] = sv0;
+                svg[m0w + gid + 8] = sv1;
             }
+            char* cw = reinterpret_cast<char*>(s.Bh) + (m0w + gid) * (TS * 2) + 2 * tig;
+#pragma unroll
+            for (int nt = 0; nt < 16; ++nt) {
+                const uint32_t lo = __byte_perm(rne_code(e[nt][0], rm0), rne_code(e[nt][1], rm0), 0x0040);
+                const uint32_t hi = __byte_perm(rne_code(e[nt][2], rm1), rne_code(e[nt][3], rm1), 0x0040);
+                *reinterpret_cast<uint16_t*>(cw + 8 * nt) = uint16_t(lo);
+                *reinterpret_cast<uint16_t*>(cw + 8 * (TS * 2) + 8 * nt) = uint16_t(hi);
+            }
+            __syncwarp();
+            const int row = m0w + (lane >> 1), half = lane & 1;
+            const uint4* src = reinterpret_cast<const uint4*>(reinterpret_cast<const char*>(s.Bh) + row * (TS * 2) + half * 64);
+            uint4* dst = reinterpret_cast<uint4*>(base + CK_CODES + row * KD + half * 64);
+#pragma unroll
+            for (int i = 0; i < 4; ++i) dst[i] = src[i];
         }
         LQ_FSTAMP(11);
         // ---- stage G: window reset ----
@@ -463,17 +574,17 @@ template <int R, bool KDA>
 static int launch_flush(const lq_dims* d, void* ssm, void* Kbuf, void* Ubuf, float* Wbuf, float* Pbuf, void* Gbuf,
                         int32_t* hcnt, const float* Q0, const int32_t* idx, int N, int iters, cudaStream_t st) {
     const int total = N * d->HV;
-    // two CTAs per SM when the shared memory of one allows it (R = 4): a flush is a chain of short phases, and a second
-    // head in flight on the SM hides most of their latency
+    // two CTAs per SM when the shared memory of one allows it: a flush is a chain of short phases, and a second head in
+    // flight on the SM hides most of their latency
     int per_sm = 1;
-    if (R == 4) {
+    {
         const int g2 = min(2 * device_sm_count(), total);
-        const size_t s2 = sizeof(float) * flush_smem_floats<R>(d->L, (total + g2 - 1) / g2 + 1, KDA);
+        const size_t s2 = flush_smem_bytes<R>(d->L, (total + g2 - 1) / g2 + 1, KDA);
         if (s2 <= 113 * 1024) per_sm = 2;
     }
     const int G = min(per_sm * device_sm_count(), total);
     const int maxd = (total + G - 1) / G + 1;
-    const size_t smem = sizeof(float) * flush_smem_floats<R>(d->L, maxd, KDA);
+    const size_t smem = flush_smem_bytes<R>(d->L, maxd, KDA);
     if (smem > 227 * 1024) return LQ_ERR_UNSUPPORTED;
     int rc = ensure_smem((const void*)flush_kernel<R, KDA>, smem);
     if (rc) return rc;

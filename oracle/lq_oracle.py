@@ -349,14 +349,16 @@ def column_scales(E):
     return sk, 1.0 / sk
 
 
-def flush_rebuild(q8, Sk, Sv, Kb, Ub, w, P, G, uq_old, kda):
+def flush_rebuild(q8, Sk, Sv, Kb, Ub, w, P, G, uq_old, kda, round_b=True):
     """B (the window-rebuilt state without the old rank-R part), the scaled old factors and the scalar decay p.
 
     GDN (leapquant/kernels.py:1471,1483,1512-1563): p = max(Pbuf, 1e-20); B = q8 * (Sv p / 127) * Sk + sum_j (w_j u_j) k_j^T.
     KDA (leapquant/kernels.py:1448-1468,1519): pc = exp(Pbuf); keys pre-decayed by w_j D_j (D_{L-1} = 1, D_j = D_{j+1} e_{j+1});
     old U^T scaled by pc; B = q8 * (Sv / 127) * (Sk pc) + sum_j u_j (w_j D_j k_j)^T; p = 1.
-    The reference holds w_j u_j (GDN) / the decayed keys (KDA) as bf16 hi + lo (16 mantissa bits), pc * U^T as fp16 and
-    B as fp16; all fp32 here (the CUDA kernel keeps the bf16 hi + lo operand and an fp32 B)."""
+    The reference holds w_j u_j (GDN) / the decayed keys (KDA) as bf16 hi + lo (16 mantissa bits): fp32 here (the split
+    keeps 16 mantissa bits, below every tolerance of the parity tests).  pc * U^T and B are rounded to fp16 like the
+    reference's operand tiles (leapquant/kernels.py:1466,1483): B is the A operand of every later tensor-core product.
+    round_b=False returns B before that rounding (the tests use it to find the elements that sit on a rounding midpoint)."""
     K = q8.shape[-1]
     Ut, Qt = uq_old[..., :K].to(torch.float32), uq_old[..., K:].to(torch.float32)
     x = q8.to(torch.float32)
@@ -368,11 +370,11 @@ def flush_rebuild(q8, Sk, Sv, Kb, Ub, w, P, G, uq_old, kda):
         kd = Kb.to(torch.float32) * (w[..., None] * Dj)
         B = x * (Sv * (1.0 / QMAX))[..., :, None] * (Sk * pc)[..., None, :]
         B = B + torch.einsum("djv,djc->dvc", Ub.to(torch.float32), kd)
-        return B, Ut * pc[..., None, :], Qt, torch.ones(P.shape[:-1])
+        return (_f16(B) if round_b else B), _f16(Ut * pc[..., None, :]), Qt, torch.ones(P.shape[:-1])
     p = torch.clamp(P[..., 0], min=PNMIN)
     B = x * (Sv * (p / QMAX)[..., None])[..., :, None] * Sk[..., None, :]
     B = B + torch.einsum("djv,djc->dvc", w[..., None] * Ub.to(torch.float32), Kb.to(torch.float32))
-    return B, Ut, Qt, p
+    return (_f16(B) if round_b else B), Ut, Qt, p
 
 
 def flush_factors(B, Ut_old, Qt_old, p, Q0, iters=1):

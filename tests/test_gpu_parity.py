@@ -293,6 +293,12 @@ def check_flush(cpu, gpu, idx, slots, what, code_tol=5e-3, code_frac=0.002, stri
     B, Ut_o, Qt_o, p = O.flush_rebuild(v["Sq"][ss, hh], v["Sk"][ss, hh], v["Sv"][ss, hh], b.Kbuf[ss, hh], b.Ubuf[ss, hh],
                                        b.Wbuf[ss, hh], b.Pbuf[ss, hh], b.Gbuf[ss, hh] if kda else None, v["uq"][ss, hh], kda)
     T = B + p[:, None, None] * torch.einsum("drv,drc->dvc", Qt_o, Ut_o)
+    # B is an fp16 tile on both sides.  Where the fp32 value sits within the device's evaluation noise of a rounding midpoint
+    # the two sides may round to neighbouring fp16 numbers: those elements carry one fp16 ulp of B as extra noise.
+    B32 = O.flush_rebuild(v["Sq"][ss, hh], v["Sk"][ss, hh], v["Sv"][ss, hh], b.Kbuf[ss, hh], b.Ubuf[ss, hh], b.Wbuf[ss, hh],
+                          b.Pbuf[ss, hh], b.Gbuf[ss, hh] if kda else None, v["uq"][ss, hh], kda, round_b=False)[0]
+    ulp16 = torch.clamp(torch.exp2(torch.floor(torch.log2(torch.clamp(B.abs(), min=2.0 ** -24))) - 10.0), min=2.0 ** -24)
+    midpoint = (0.5 * ulp16 - (B32 - B).abs()) <= 4e-6 * float(B32.abs().max())
     before_c = cpu.full_state(slots)
     nfl = cpu.flush(idx)
     assert nfl == int(due.sum())
@@ -329,15 +335,23 @@ def check_flush(cpu, gpu, idx, slots, what, code_tol=5e-3, code_frac=0.002, stri
     eps_T = 1e-6 * mag
     if not stagewise:       # heads without a meaningful residual (all zero, or decayed away): only the state is compared
         eps_T = float("inf")
-    assert bool(((sk_g * sk_g - sk_c * sk_c).abs() <= 1e-4 * sk_c * sk_c + eps_T).all()), what + ": Sk given the stored factors"
+    noise_E = eps_T + midpoint.float() * ulp16                               # [D, V, K]
+    assert bool(((sk_g * sk_g - sk_c * sk_c).abs() <= 1e-4 * sk_c * sk_c + noise_E.mean(-2)).all()), what + ": Sk given the stored factors"
     x = E * (1.0 / sk_g)[:, None, :]
-    noise_x = eps_T / sk_g                                                   # [D, K], in units of E / Sk
+    noise_x = noise_E / sk_g[:, None, :]                                     # in units of E / Sk
     sv_c = torch.clamp(x.abs().amax(-1), min=1e-12)
-    assert bool(((sv_g - sv_c).abs() <= 1e-4 * sv_c + noise_x.amax(-1, keepdim=True)).all()), what + ": Sv given the stored factors"
+    assert bool(((sv_g - sv_c).abs() <= 1e-4 * sv_c + noise_x.amax(-1)).all()), what + ": Sv given the stored factors"
     xs = x.double() * (127.0 * (1.0 / sv_g)).double()[:, :, None]
     if stagewise:
-        tol = code_tol + noise_x[:, None, :] * 127.0 / sv_g[:, :, None]
-        nb = near_boundary_only(gv["Sq"][ss, hh], xs, tol=tol)
+        tol = code_tol + noise_x * 127.0 / sv_g[:, :, None]                  # in code units
+        codes_g = gv["Sq"][ss, hh].double()
+        loose = tol > 0.25                  # a neighbouring fp16 value of B moves these by a sizeable part of a code
+        # (a numerically rank-deficient head has a residual at the level of B's fp16 spacing: most of its codes are loose)
+        if strict_factors:
+            assert int(loose.sum()) <= 0.02 * loose.numel(), what + ": too many elements on an fp16 midpoint of B"
+        assert bool(((codes_g - torch.round(xs)).abs()[loose] <= torch.ceil(tol[loose]) + 1).all()), what + ": midpoint codes"
+        codes_g = torch.where(loose, torch.round(xs), codes_g)
+        nb = near_boundary_only(codes_g, xs, tol=tol)
         assert nb <= code_frac * xs.numel(), f"{what}: {nb} codes off by one"
     # the flushed state equals the state before the flush up to the INT8 step, on both sides alike
     after_g = gpu.full_state(slots)
