@@ -28,6 +28,7 @@ struct FlushSmem {
     float* colpart;    // [8][128] per-warp column sums of |E|
     float* Qn;         // [128][R] fp32 Q for CholeskyQR
     float* tab;        // KDA: [L][128] scale of key (j, c): w_j D_j[c]
+    uint16_t* Q0h;     // [R][HS] f16 Q0^T, the fixed start of the iteration (written once per CTA)
     uint16_t* Qh;      // [R][HS] f16 Q^T  (current iterate)
     uint16_t* Ph;      // [R][HS] f16 P^T = new U^T
     uint16_t* Qoh;     // [R][HS] f16 old Q^T
@@ -52,7 +53,7 @@ __host__ __device__ inline int flush_region_bytes(int L) {
 }
 template <int R>
 __host__ __device__ inline size_t flush_smem_bytes(int L, int maxd, bool kda) {
-    return size_t(128) * TS * 2 + flush_region_bytes<R>(L) + (kda ? size_t(L) * 128 * 4 : 0) + 4 * R * HS * 2 + 2 * 128 * 8 * 2 +
+    return size_t(128) * TS * 2 + flush_region_bytes<R>(L) + (kda ? size_t(L) * 128 * 4 : 0) + 5 * R * HS * 2 + 2 * 128 * 8 * 2 +
            3 * 128 * 4 + 64 * 4 + 8 * 4 + size_t(maxd) * 4 + 16;
 }
 
@@ -162,6 +163,7 @@ flush_kernel(lq_dims d, char* __restrict__ ssm, const uint16_t* __restrict__ Kbu
         s.Qn = s.colpart + 8 * 128;
         p += flush_region_bytes<R>(d.L);
         s.tab = reinterpret_cast<float*>(p); p += KDA ? d.L * 128 * 4 : 0;
+        s.Q0h = reinterpret_cast<uint16_t*>(p); p += R * HS * 2;
         s.Qh = reinterpret_cast<uint16_t*>(p); p += R * HS * 2;
         s.Ph = reinterpret_cast<uint16_t*>(p); p += R * HS * 2;
         s.Qoh = reinterpret_cast<uint16_t*>(p); p += R * HS * 2;
@@ -243,6 +245,7 @@ flush_kernel(lq_dims d, char* __restrict__ ssm, const uint16_t* __restrict__ Kbu
             s.QoT[c * 8 + r] = 0;
         }
     }
+    for (int i = tid; i < 128 * R; i += NT_LA) s.Q0h[(i % R) * HS + i / R] = f_to_f16(Q0[i]);      // leapquant/kernels.py:1573-1577
 #ifdef LQ_TRACE
     long long facc[16] = {0}, flast = clock64();
 #endif
@@ -256,38 +259,65 @@ flush_kernel(lq_dims d, char* __restrict__ ssm, const uint16_t* __restrict__ Kbu
         float p = 1.f;
         if (!KDA) p = fmaxf(Pbuf[sh], PNMIN);
 
-        // ---- stage A: operands to shared memory ----
-        if (tid < L) s.w[tid] = Wbuf[sh * L + tid];
-        if (tid < 128) {
-            const float pcv = KDA ? expf(Pbuf[sh * KD + tid]) : 1.f;
-            s.pc[tid] = pcv;
-            s.sk[tid] = reinterpret_cast<const float*>(base + CK_SK)[tid] * pcv;
-            s.sv[tid] = reinterpret_cast<const float*>(base + CK_SV)[tid];
-        }
+        // ---- stage A: operands to shared memory; every global load of the stage is issued before the first store so that
+        //      their latencies overlap (the stores would otherwise fence the loads behind them) ----
         {
-            // old factors as stored (f16); KDA: U^T times pc, rounded to f16.  Kept as rows [r][128] and transposed [128][8].
             const uint16_t* uq = reinterpret_cast<const uint16_t*>(base + CK_UQ);
-            for (int i = tid; i < R * 128; i += NT_LA) {
-                const int r = i >> 7, c = i & 127;
-                uint16_t u = uq[r * (KD + VD) + c];
-                const uint16_t qv = uq[r * (KD + VD) + KD + c];
-                if (KDA) u = f_to_f16(f16_to_f(u) * expf(Pbuf[sh * KD + c]));
-                s.Uoh[r * HS + c] = u;
-                s.Qoh[r * HS + c] = qv;
-                s.UoT[c * 8 + r] = u;
-                s.QoT[c * 8 + r] = qv;
-            }
-        }
-        LQ_FSTAMP(1);
-        // window rows as stored (bf16), 16 bytes at a time into the padded tiles; rows L .. Lp-1 are zero
-        {
             const uint4* kb = reinterpret_cast<const uint4*>(Kbuf + sh * L * KD);
             const uint4* ub = reinterpret_cast<const uint4*>(Ubuf + sh * L * VD);
-            for (int i = tid; i < Lp * 16; i += NT_LA) {
-                const int j = i >> 4, c8 = i & 15;
-                const uint4 z = make_uint4(0u, 0u, 0u, 0u);
-                *reinterpret_cast<uint4*>(s.Kt + j * TS + c8 * 8) = j < L ? kb[i] : z;
-                *reinterpret_cast<uint4*>(s.Ut + j * TS + c8 * 8) = j < L ? ub[i] : z;
+            constexpr int NF = R * 128 / NT_LA;                 // factor elements per thread
+            constexpr int NTC = 4;                              // window-tile chunks per thread and pass (Lp <= 64)
+            float wv = 0.f, pcv = 1.f, skv = 0.f, svv = 0.f, pcf[NF];
+            uint16_t fu[NF], fq[NF];
+            uint4 tk[NTC], tu[NTC];
+            if (tid < L) wv = Wbuf[sh * L + tid];
+            if (tid < 128) {
+                if (KDA) pcv = Pbuf[sh * KD + tid];
+                skv = reinterpret_cast<const float*>(base + CK_SK)[tid];
+                svv = reinterpret_cast<const float*>(base + CK_SV)[tid];
+            }
+#pragma unroll
+            for (int u = 0; u < NF; ++u) {
+                const int i = tid + u * NT_LA, r = i >> 7, c = i & 127;
+                fu[u] = uq[r * (KD + VD) + c];
+                fq[u] = uq[r * (KD + VD) + KD + c];
+                pcf[u] = KDA ? Pbuf[sh * KD + c] : 0.f;
+            }
+#pragma unroll
+            for (int u = 0; u < NTC; ++u) {
+                const int i = tid + u * NT_LA;
+                const bool in = i < L * 16;
+                tk[u] = in ? kb[i] : make_uint4(0u, 0u, 0u, 0u);
+                tu[u] = in ? ub[i] : make_uint4(0u, 0u, 0u, 0u);
+            }
+            if (tid < L) s.w[tid] = wv;
+            if (tid < 128) {
+                pcv = KDA ? expf(pcv) : 1.f;
+                s.pc[tid] = pcv;
+                s.sk[tid] = skv * pcv;
+                s.sv[tid] = svv;
+            }
+            // old factors as stored (f16); KDA: U^T times pc, rounded to f16.  Kept as rows [r][128] and transposed [128][8].
+#pragma unroll
+            for (int u = 0; u < NF; ++u) {
+                const int i = tid + u * NT_LA, r = i >> 7, c = i & 127;
+                uint16_t uu = fu[u];
+                if (KDA) uu = f_to_f16(f16_to_f(uu) * expf(pcf[u]));
+                s.Uoh[r * HS + c] = uu;
+                s.Qoh[r * HS + c] = fq[u];
+                s.UoT[c * 8 + r] = uu;
+                s.QoT[c * 8 + r] = fq[u];
+            }
+            LQ_FSTAMP(1);
+            // window rows as stored (bf16), 16 bytes at a time into the padded tiles; rows L .. Lp-1 are zero
+#pragma unroll
+            for (int u = 0; u < NTC; ++u) {
+                const int i = tid + u * NT_LA;
+                if (i < Lp * 16) {
+                    const int j = i >> 4, c8 = i & 15;
+                    *reinterpret_cast<uint4*>(s.Kt + j * TS + c8 * 8) = tk[u];
+                    *reinterpret_cast<uint4*>(s.Ut + j * TS + c8 * 8) = tu[u];
+                }
             }
         }
         __syncthreads();
@@ -392,9 +422,6 @@ flush_kernel(lq_dims d, char* __restrict__ ssm, const uint16_t* __restrict__ Kbu
         }
         __syncthreads();                                        // the window tiles are dead: the region may be reused
         LQ_FSTAMP(3);
-        for (int i = tid; i < 128 * R; i += NT_LA) s.Qh[(i % R) * HS + i / R] = f_to_f16(Q0[i]);
-        __syncthreads();
-
         LQ_FSTAMP(4);
         // ---- stage C: subspace iteration on T = B + p Q_old U_old^T ----
         const int m0w = warp * 16;
@@ -407,10 +434,14 @@ flush_kernel(lq_dims d, char* __restrict__ ssm, const uint16_t* __restrict__ Kbu
                 s.Ph[(2 * tig + 1) * HS + m0w + gid + 8] = f_to_f16(dd[3]);
             }
         };
-        tall_product<R, true>(s.Bh, s.Qh, s.Qoh, s.UoT, p, warp, lane, dd);         // P = T^T Q
+        tall_product<R, true>(s.Bh, s.Q0h, s.Qoh, s.UoT, p, warp, lane, dd);        // P = T^T Q0
         store_p();
         __syncthreads();
         LQ_FSTAMP(5);
+        if (iters == 0) {                                       // no round: the stored Q is the start itself
+            for (int i = tid; i < R * HS; i += NT_LA) s.Qh[i] = s.Q0h[i];
+            __syncthreads();
+        }
         for (int it = 0; it < iters; ++it) {
             tall_product<R, false>(s.Bh, s.Ph, s.Uoh, s.QoT, p, warp, lane, dd);    // Q = T P
             if (2 * tig < R) {
