@@ -395,7 +395,7 @@ def run_b200(args, wl):
                            "timing": "one window of %d steps captured in a CUDA graph, replayed" % L},
                 "e2e": {"value": e2e_value, "unit": "head-steps/s", "h2d_bytes_per_step": layer.h2d_bytes(),
                         "d2h_bytes_per_step": layer.d2h_bytes(), "steps": e2e_steps},
-                "gpu_launches": 2 * done,
+                "gpu_launches": (1 if layer.st.fused else 2) * done,
                 "roofline": {"bound": "hbm", "kernel": "step_pipelined_kernel", "achieved": achieved, "peak": peak,
                              "unit": "GB/s", "frac": achieved / peak, "frac_of_8tbs": achieved / 8000.0,
                              "traffic": (traffic * alg_launch) if traffic else None, "alg_bytes_per_launch": alg_launch,

@@ -61,7 +61,9 @@ int lq_device_status(int* status);
 
 /* Tuning / debugging switch, process-wide; no reference counterpart.  "step_impl": 0 = persistent CTAs fed by bulk
  * asynchronous copies (default), 1 = one CTA per (row, head) with plain loads and the same arithmetic, 2 = one warp per
- * (row, head) in registers (GDN only; KDA keeps the default).  1 and 2 exist for debugging and comparison. */
+ * (row, head) in registers (GDN only; KDA keeps the default).  1 and 2 exist for debugging and comparison.
+ * "pdl": 1 (default) launches the step and flush kernels with programmatic stream serialisation, so that the launch and
+ * set-up of one overlap the tail of its predecessor on the stream; 0 = plain launches. */
 int lq_set_option(const char* name, int32_t value);
 
 /* GDN decode step.  Replaces the kernel built by make_gdn_step (reference leapquant/kernels.py:27-692, launch
@@ -89,6 +91,20 @@ int lq_kda_step(const lq_dims* d, void* ssm, void* Kbuf, void* Ubuf, float* Wbuf
  * the launch shape does not depend on how many are due.  kda != 0 selects the per-channel-gate variant (Gbuf used). */
 int lq_flush(const lq_dims* d, void* ssm, void* Kbuf, void* Ubuf, float* Wbuf, float* Pbuf, void* Gbuf,
              int32_t* hcnt, const float* Q0, const int32_t* idx, int32_t N, int32_t kda, int32_t iters, void* stream);
+
+/* Fused decode: lq_gdn_step / lq_kda_step followed by lq_flush on the same rows, in ONE launch.  Replaces the two
+ * launches of LeapQuantState.decode (reference leapquant/state.py:99-116): the persistent CTA that fills a head's window
+ * flushes that head itself after its last program, so the flush needs no due scan, no second launch and finds the
+ * head's window rows in cache.  Same arguments as the step plus the flush's Q0 and iters; same results as the two calls.
+ * Where the fused form is not available (a debug step driver is selected, or the flush working set does not fit beside
+ * nothing in shared memory) the two kernels are launched one after the other. */
+int lq_gdn_decode(const lq_dims* d, void* ssm, void* Kbuf, void* Ubuf, float* Wbuf, float* Pbuf, int32_t* hcnt,
+                  const void* mixed, const void* a, const void* b, const float* A_log, const float* dt_bias,
+                  const int32_t* idx, void* o, int32_t N, float scale, const float* Q0, int32_t iters, void* stream);
+int lq_kda_decode(const lq_dims* d, void* ssm, void* Kbuf, void* Ubuf, float* Wbuf, float* Pbuf, void* Gbuf,
+                  int32_t* hcnt, const void* mixed, const void* a, const void* b, const float* A_log,
+                  const float* dt_bias, const int32_t* idx, void* o, int32_t N, float scale, float gate_lower_bound,
+                  const float* Q0, int32_t iters, void* stream);
 
 /* Standalone quantize.  Replaces the kernel built by make_quantize (reference leapquant/kernels.py:2126-2242);
  * with kda != 0 it also stands in for LeapQuantState._kda_checkpoint (reference leapquant/state.py:130-142, which

@@ -13,7 +13,7 @@ _HERE = os.path.dirname(os.path.abspath(__file__))
 LIB_PATH = os.environ.get("LEAPQUANT_B200_LIB") or os.path.join(_HERE, "libleapquant_b200.so")
 
 EXPORTS = ("lq_version", "lq_strerror", "lq_last_cuda_error", "lq_device_status", "lq_set_option", "lq_gdn_step", "lq_kda_step",
-           "lq_flush", "lq_quantize", "lq_dequant", "lq_lowrank")
+           "lq_flush", "lq_gdn_decode", "lq_kda_decode", "lq_quantize", "lq_dequant", "lq_lowrank")
 
 _P = ctypes.c_void_p
 _I = ctypes.c_int32
@@ -51,6 +51,8 @@ def lib():
         L.lq_gdn_step.argtypes = [D, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _I, _F, _P]
         L.lq_kda_step.argtypes = [D, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _I, _F, _F, _P]
         L.lq_flush.argtypes = [D, _P, _P, _P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _P]
+        L.lq_gdn_decode.argtypes = [D, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _I, _F, _P, _I, _P]
+        L.lq_kda_decode.argtypes = [D, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _I, _F, _F, _P, _I, _P]
         L.lq_quantize.argtypes = [D, _P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _P]
         L.lq_dequant.argtypes = [D, _P, _P, _P, _P, _P, _P, _P, _P, _I, _I, _P]
         L.lq_lowrank.argtypes = [_P, _P, _P, _P, _I, _I, _I, _I, _I, _P]

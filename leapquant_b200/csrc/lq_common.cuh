@@ -126,6 +126,28 @@ int device_sm_count();
 int ensure_smem(const void* func, size_t bytes);
 int check_dims(const lq_dims* d);
 void set_last_cuda_error(cudaError_t e);
+
+// Programmatic dependent launch.  The decode path is a chain of short kernels on one stream (step, flush, step, ...); a
+// kernel launched with this attribute may be scheduled while its predecessor is still draining, runs its set-up
+// (shared-memory carve, barrier initialisation) and then blocks in pdl_wait() until the predecessor has completed and its
+// writes are visible.  Every kernel launched this way calls pdl_trigger() and pdl_wait() before it touches global memory.
+static int g_pdl = 1;
+__device__ __forceinline__ void pdl_trigger() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+template <typename... KArgs, typename... Args>
+inline cudaError_t launch_dependent(void (*kern)(KArgs...), unsigned grid, unsigned block, size_t smem, cudaStream_t st, Args... args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(grid);
+    cfg.blockDim = dim3(block);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = st;
+    cudaLaunchAttribute at[1];
+    at[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    at[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = at;
+    cfg.numAttrs = g_pdl ? 1 : 0;
+    return cudaLaunchKernelEx(&cfg, kern, KArgs(args)...);
+}
 inline int finish_launch() {
     cudaError_t e = cudaGetLastError();
     if (e != cudaSuccess) {

@@ -198,8 +198,8 @@ __device__ __forceinline__ void cholqr_pass_regs(float (&x)[4][R]) {
 }
 
 // CholeskyQR2 on X [128][R] by warp 0; the result is rounded to fp16 values (it becomes the stored Q factor).
-template <int R>
-__device__ __forceinline__ void cholqr2_f16(float* __restrict__ X, int tid) {
+template <int R, typename Sync>
+__device__ __forceinline__ void cholqr2_f16(float* __restrict__ X, int tid, Sync sync) {
     if (tid < 32) {
         float x[4][R];
 #pragma unroll
@@ -213,7 +213,11 @@ __device__ __forceinline__ void cholqr2_f16(float* __restrict__ X, int tid) {
 #pragma unroll
             for (int r = 0; r < R; ++r) X[(tid + 32 * i) * R + r] = round_f16(x[i][r]);
     }
-    __syncthreads();
+    sync();
+}
+template <int R>
+__device__ __forceinline__ void cholqr2_f16(float* __restrict__ X, int tid) {
+    cholqr2_f16<R>(X, tid, [] { __syncthreads(); });
 }
 
 }  // namespace lq

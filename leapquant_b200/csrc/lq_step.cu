@@ -713,6 +713,14 @@ __device__ __forceinline__ bool group_all(int bar, int nthreads, bool pred) {
 // [ND stage row counts].
 // Program i (CTA-local sequence number) uses descriptor i % ND: three mbarriers and the offset of its stage in the ring.
 // Stages are carved from the ring in order, each sized for its program's live window rows, and reclaimed in order.
+// Tail of the fused decode kernel: after its last program a CTA flushes the heads whose window it has just filled.
+struct FuseTail {
+    const float* Q0;
+    int iters;
+    int teams;                                      // teams of 256 threads that fit in the ring side by side (1 or 2)
+    int team_bytes;                                 // shared memory of one team
+};
+
 #ifndef LQ_REGC
 #define LQ_REGC 0
 #endif
@@ -725,8 +733,8 @@ constexpr bool REGC = LQ_REGC != 0;             // int8 tile through registers (
 constexpr int SKIP = REGC ? CK_SK : 0;          // stage bytes not held in the ring; `st` is a virtual origin SKIP bytes below
 constexpr int ND = 16;                         // descriptors = most programs resident in the ring at once
 
-template <int R, bool KDA, int NG>
-__global__ void __launch_bounds__(UT + NG * GT, 1) step_pipelined_kernel(StepParams P, int ring_bytes) {
+template <int R, bool KDA, int NG, bool FUSE>
+__global__ void __launch_bounds__(UT + NG * GT, 1) step_pipelined_kernel(StepParams P, int ring_bytes, FuseTail ft) {
     extern __shared__ __align__(128) char stage_smem[];
     char* scratch0 = stage_smem + ring_bytes;
     uint64_t* full = reinterpret_cast<uint64_t*>(scratch0 + NG * SCRATCH_BYTES);
@@ -736,6 +744,9 @@ __global__ void __launch_bounds__(UT + NG * GT, 1) step_pipelined_kernel(StepPar
     volatile int* doff = reinterpret_cast<volatile int*>(ready + ND);
     volatile int* gflag0 = doff + ND;
     ProgScalars* pbatch = reinterpret_cast<ProgScalars*>(const_cast<int*>(doff) + 2 * ND + NG + 2);      // [32], 8-byte aligned
+    int* dl_n = reinterpret_cast<int*>(pbatch + 32);             // fused flush: number of due heads, abort flag, the heads
+    volatile int* abortf = dl_n + 1;
+    int* dl = dl_n + 4;
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int HV = P.d.HV, H = P.d.H, L = P.d.L;
     const int nprog = P.N * HV;
@@ -743,6 +754,8 @@ __global__ void __launch_bounds__(UT + NG * GT, 1) step_pipelined_kernel(StepPar
     const int nit = (nprog - bid + grid - 1) / grid;
 
     if (tid == 0) {
+        *dl_n = 0;
+        *abortf = 0;
         for (int s = 0; s < ND; ++s) {
             mbar_init(full + s, 1);
             mbar_init(normed + s, 32);
@@ -753,7 +766,10 @@ __global__ void __launch_bounds__(UT + NG * GT, 1) step_pipelined_kernel(StepPar
         fence_async_smem();
     }
     __syncthreads();
+    pdl_trigger();
+    pdl_wait();                                                  // everything below reads what earlier kernels of the stream wrote
 
+    auto run_roles = [&]() {
     if (warp == 0) {
         // ================= producer: scalars of 32 programs per batch, then one stage placement per program =================
         ProgScalars cur, nxt;
@@ -803,7 +819,7 @@ __global__ void __launch_bounds__(UT + NG * GT, 1) step_pipelined_kernel(StepPar
                     ++tail;
                 }
                 if (!ok) {
-                    if (lane == 0) atomicOr(&g_status, ST_PRODUCER_TIMEOUT);
+                    if (lane == 0) { atomicOr(&g_status, ST_PRODUCER_TIMEOUT); *abortf = 1; }
                     break;
                 }
                 LQ_QSTAMP(2);
@@ -869,7 +885,7 @@ __global__ void __launch_bounds__(UT + NG * GT, 1) step_pipelined_kernel(StepPar
         for (int i = 0; i < nit; ++i) {
             const int dsc = i % ND;
             if (!warp_wait_bounded(ready + dsc, uint32_t(i / ND) & 1u, lane)) {
-                if (lane == 0) atomicOr(&g_status, ST_PRODUCER_TIMEOUT);
+                if (lane == 0) { atomicOr(&g_status, ST_PRODUCER_TIMEOUT); *abortf = 1; }
                 return;
             }
             char* st = stage_smem + doff[dsc] - SKIP;
@@ -900,7 +916,7 @@ __global__ void __launch_bounds__(UT + NG * GT, 1) step_pipelined_kernel(StepPar
             if (i < 256 && blockIdx.x < 160 && lane == 0) g_ntrace[(blockIdx.x * 256 + i) * 8 + 7] = clock64();
 #endif
             if (!warp_wait_bounded(full + dsc, uint32_t(i / ND) & 1u, lane)) {
-                if (lane == 0) atomicOr(&g_status, ST_PROLOGUE_TIMEOUT);
+                if (lane == 0) { atomicOr(&g_status, ST_PROLOGUE_TIMEOUT); *abortf = 1; }
                 return;
             }
             char* st = stage_smem + doff[dsc] - SKIP;
@@ -964,7 +980,7 @@ __global__ void __launch_bounds__(UT + NG * GT, 1) step_pipelined_kernel(StepPar
         }
         named_bar(bar, GT);
         if (*gflag == 0) {                              // uniform decision: nobody enters the body unless the data is there
-            if (t == 0) atomicOr(&g_status, ST_CONSUMER_TIMEOUT);
+            if (t == 0) { atomicOr(&g_status, ST_CONSUMER_TIMEOUT); *abortf = 1; }
             return;
         }
         char* st = stage_smem + doff[dsc] - SKIP;
@@ -983,7 +999,9 @@ __global__ void __launch_bounds__(UT + NG * GT, 1) step_pipelined_kernel(StepPar
         if (prog_live(sc, L)) {
 #endif
             step_body<R, KDA, REGC>(P, sc, st, lay, gs, t, bar, release, ac, refill, i);
+            if (FUSE && t == 0 && sc.h + 1 == L) dl[atomicAdd(dl_n, 1)] = sc.slot * HV + sc.hv;      // window just filled
         } else {
+            if (FUSE && t == 0 && sc.slot > 0 && sc.h == L) dl[atomicAdd(dl_n, 1)] = sc.slot * HV + sc.hv;   // was full already
             refill();
             release();
 #ifdef LQ_NOBODY
@@ -994,14 +1012,37 @@ __global__ void __launch_bounds__(UT + NG * GT, 1) step_pipelined_kernel(StepPar
         }
         if (t == 0) LQ_STAMP(i, 3);
     }
+    };
+    run_roles();
+
+    // ================= fused flush: the heads whose window this CTA just filled, two teams of 256 threads =================
+    if constexpr (FUSE) {
+        __syncthreads();                                         // every role is done; the ring is dead, this CTA's global writes are visible
+        if (*abortf) return;
+        const int ndl = *dl_n;
+        const int team = tid >> 8, ttid = tid & 255;
+        if (ndl == 0 || team >= ft.teams) return;
+        const FlushSmem fs = flush_carve<R>(stage_smem + team * ft.team_bytes, L, KDA);
+        flush_init<R>(fs, ft.Q0, ttid);
+        FlushArgs A;
+        A.d = P.d; A.ssm = P.ssm; A.Kbuf = P.Kbuf; A.Ubuf = P.Ubuf; A.Wbuf = P.Wbuf; A.Pbuf = P.Pbuf; A.Gbuf = P.Gbuf;
+        A.hcnt = P.hcnt; A.Q0 = ft.Q0; A.iters = ft.iters;
+        auto tsync = [&] { named_bar(8 + team, 256); };
+        long long facc[16] = {0}, flast = 0;
+        for (int k = team; k < ndl; k += ft.teams) flush_head<R, KDA>(fs, A, dl[k], ttid, tsync, facc, flast);
+    }
 }
 
 // 0 = pipelined, 1 = direct, 2 = one warp per program (GDN; KDA falls back to the pipelined driver)
 static int g_step_impl = 0;
 
+// fuse != nullptr: the pipelined driver also flushes, in the same launch, the heads whose window it fills (Q0, iters from
+// *fuse).  Returns LQ_ERR_UNSUPPORTED when the fused form is not available for the configuration (debug drivers, a flush
+// team that does not fit in the ring): the caller then launches the two kernels separately.
 template <int R, bool KDA>
-static int launch_step(const StepParams& P, cudaStream_t st) {
+static int launch_step(const StepParams& P, cudaStream_t st, const FuseTail* fuse) {
     const StageLayout lay = stage_layout(P.d.L, P.d.L, R, KDA);
+    if (g_step_impl != 0 && fuse && !(g_step_impl == 2 && KDA)) return LQ_ERR_UNSUPPORTED;
     if (g_step_impl == 1) {
         const size_t smem = size_t(lay.bytes) + SCRATCH_BYTES;
         int rc = ensure_smem((const void*)step_direct_kernel<R, KDA>, smem);
@@ -1017,23 +1058,39 @@ static int launch_step(const StepParams& P, cudaStream_t st) {
         return finish_launch();
     }
     constexpr int NG = LQ_NG;
-    const size_t budget = 227 * 1024;
-    const size_t fixed = size_t(NG) * SCRATCH_BYTES + 4 * ND * sizeof(uint64_t) + (2 * ND + NG + 4) * sizeof(int) + 32 * sizeof(ProgScalars);
-    const int ring_bytes = int((budget - fixed) & ~size_t(127));
-    if (ring_bytes < stage_layout(P.d.L, P.d.L, R, KDA).bytes) return LQ_ERR_UNSUPPORTED;
-    const size_t smem = size_t(ring_bytes) + fixed;
-    int rc = ensure_smem((const void*)step_pipelined_kernel<R, KDA, NG>, smem);
-    if (rc) return rc;
     const int nprog = P.N * P.d.HV;
     const int grid = nprog < device_sm_count() ? nprog : device_sm_count();
-    step_pipelined_kernel<R, KDA, NG><<<grid, UT + NG * GT, smem, st>>>(P, ring_bytes);
+    const int nit_max = (nprog + grid - 1) / grid;
+    const size_t budget = 227 * 1024;
+    const size_t fixed = size_t(NG) * SCRATCH_BYTES + 4 * ND * sizeof(uint64_t) + (2 * ND + NG + 4) * sizeof(int) + 32 * sizeof(ProgScalars) +
+                         (4 + size_t(nit_max)) * sizeof(int);
+    if (fixed + size_t(lay.bytes) > budget) return LQ_ERR_UNSUPPORTED;
+    const int ring_bytes = int((budget - fixed) & ~size_t(127));
+    if (ring_bytes < lay.bytes) return LQ_ERR_UNSUPPORTED;
+    const size_t smem = size_t(ring_bytes) + fixed;
+    FuseTail ft = {nullptr, 0, 0, 0};
+    cudaError_t le;
+    if (fuse) {
+        ft = *fuse;
+        ft.team_bytes = int((flush_smem_bytes<R>(P.d.L, 0, KDA) + 127) & ~size_t(127));
+        ft.teams = (2 * ft.team_bytes <= ring_bytes) ? 2 : (ft.team_bytes <= ring_bytes ? 1 : 0);
+        if (ft.teams == 0) return LQ_ERR_UNSUPPORTED;
+        int rc = ensure_smem((const void*)step_pipelined_kernel<R, KDA, NG, true>, smem);
+        if (rc) return rc;
+        le = launch_dependent(step_pipelined_kernel<R, KDA, NG, true>, unsigned(grid), unsigned(UT + NG * GT), smem, st, P, ring_bytes, ft);
+    } else {
+        int rc = ensure_smem((const void*)step_pipelined_kernel<R, KDA, NG, false>, smem);
+        if (rc) return rc;
+        le = launch_dependent(step_pipelined_kernel<R, KDA, NG, false>, unsigned(grid), unsigned(UT + NG * GT), smem, st, P, ring_bytes, ft);
+    }
+    if (le != cudaSuccess) { set_last_cuda_error(le); return LQ_ERR_LAUNCH; }
     return finish_launch();
 }
 
 static int step_common(const lq_dims* d, void* ssm, void* Kbuf, void* Ubuf, float* Wbuf, float* Pbuf, void* Gbuf,
                        int32_t* hcnt, const void* mixed, const void* a, const void* b, const float* A_log,
                        const float* dt_bias, const int32_t* idx, void* o, int32_t N, float scale, float glb, bool kda,
-                       void* stream) {
+                       void* stream, const FuseTail* fuse = nullptr) {
     int rc = check_dims(d);
     if (rc) return rc;
     if (!ssm || !Kbuf || !Ubuf || !Wbuf || !Pbuf || !hcnt || !A_log || !dt_bias || (kda && !Gbuf)) return LQ_ERR_NULL;
@@ -1052,8 +1109,8 @@ static int step_common(const lq_dims* d, void* ssm, void* Kbuf, void* Ubuf, floa
     P.scale = scale > 0.f ? scale : 1.0f / sqrtf(float(d->K));
     P.glb = glb;
     cudaStream_t s = static_cast<cudaStream_t>(stream);
-    if (kda) return d->R == 4 ? launch_step<4, true>(P, s) : launch_step<8, true>(P, s);
-    return d->R == 4 ? launch_step<4, false>(P, s) : launch_step<8, false>(P, s);
+    if (kda) return d->R == 4 ? launch_step<4, true>(P, s, fuse) : launch_step<8, true>(P, s, fuse);
+    return d->R == 4 ? launch_step<4, false>(P, s, fuse) : launch_step<8, false>(P, s, fuse);
 }
 
 }  // namespace lq
@@ -1080,6 +1137,10 @@ extern "C" int lq_set_option(const char* name, int32_t value) {
         lq::g_step_impl = value;
         return LQ_OK;
     }
+    if (strcmp(name, "pdl") == 0) {
+        lq::g_pdl = value != 0;
+        return LQ_OK;
+    }
     return LQ_ERR_UNSUPPORTED;
 }
 
@@ -1096,4 +1157,36 @@ extern "C" int lq_kda_step(const lq_dims* d, void* ssm, void* Kbuf, void* Ubuf, 
                            float gate_lower_bound, void* stream) {
     return lq::step_common(d, ssm, Kbuf, Ubuf, Wbuf, Pbuf, Gbuf, hcnt, mixed, a, b, A_log, dt_bias, idx, o, N, scale,
                            gate_lower_bound, true, stream);
+}
+
+// Fused decode = step + flush of the heads that fill up, one launch; falls back to the two launches where the fused form
+// is not available.  Same results as lq_*_step followed by lq_flush on the same rows.
+static int decode_common(const lq_dims* d, void* ssm, void* Kbuf, void* Ubuf, float* Wbuf, float* Pbuf, void* Gbuf, int32_t* hcnt,
+                         const void* mixed, const void* a, const void* b, const float* A_log, const float* dt_bias,
+                         const int32_t* idx, void* o, int32_t N, float scale, float glb, bool kda, const float* Q0, int32_t iters,
+                         void* stream) {
+    if (!Q0) return LQ_ERR_NULL;
+    if (iters < 0) return LQ_ERR_RANGE;
+    lq::FuseTail ft = {Q0, iters, 0, 0};
+    int rc = lq::step_common(d, ssm, Kbuf, Ubuf, Wbuf, Pbuf, Gbuf, hcnt, mixed, a, b, A_log, dt_bias, idx, o, N, scale, glb, kda,
+                             stream, &ft);
+    if (rc != LQ_ERR_UNSUPPORTED) return rc;
+    rc = lq::step_common(d, ssm, Kbuf, Ubuf, Wbuf, Pbuf, Gbuf, hcnt, mixed, a, b, A_log, dt_bias, idx, o, N, scale, glb, kda, stream);
+    if (rc) return rc;
+    return lq_flush(d, ssm, Kbuf, Ubuf, Wbuf, Pbuf, Gbuf, hcnt, Q0, idx, N, kda ? 1 : 0, iters, stream);
+}
+
+extern "C" int lq_gdn_decode(const lq_dims* d, void* ssm, void* Kbuf, void* Ubuf, float* Wbuf, float* Pbuf, int32_t* hcnt,
+                             const void* mixed, const void* a, const void* b, const float* A_log, const float* dt_bias,
+                             const int32_t* idx, void* o, int32_t N, float scale, const float* Q0, int32_t iters, void* stream) {
+    return decode_common(d, ssm, Kbuf, Ubuf, Wbuf, Pbuf, nullptr, hcnt, mixed, a, b, A_log, dt_bias, idx, o, N, scale, 0.f, false, Q0,
+                         iters, stream);
+}
+
+extern "C" int lq_kda_decode(const lq_dims* d, void* ssm, void* Kbuf, void* Ubuf, float* Wbuf, float* Pbuf, void* Gbuf,
+                             int32_t* hcnt, const void* mixed, const void* a, const void* b, const float* A_log,
+                             const float* dt_bias, const int32_t* idx, void* o, int32_t N, float scale, float glb, const float* Q0,
+                             int32_t iters, void* stream) {
+    return decode_common(d, ssm, Kbuf, Ubuf, Wbuf, Pbuf, Gbuf, hcnt, mixed, a, b, A_log, dt_bias, idx, o, N, scale, glb, true, Q0,
+                         iters, stream);
 }

@@ -70,6 +70,32 @@ def make_kda_step(NS, HV, H, K, V, L, SS, R=4, SMS=148, NSTAGE=6, NSTAGEQ=4, NCG
     return step
 
 
+def make_decode(NS, HV, H, K, V, L, SS, R=4, ITERS=1, KDA=False, GLB=0.0, scale=None):
+    """Step and flush in one launch (no counterpart factory in the reference, whose LeapQuantState.decode launches the two
+    kernels one after the other, leapquant/state.py:99-116).  Returns, for GDN,
+    decode(Sq, Kbuf, Ubuf, Wbuf, Pbuf, hcnt, mixed, a, b, A_log, dt_bias, Q0, idx, o) and for KDA the same with Gbuf
+    after Pbuf; results equal those of the step followed by the flush."""
+    _need_128(K, V, "make_decode")
+    d = _lib.dims(NS, HV, H, K, V, L, R, SS)
+    sc = float(K ** -0.5 if scale is None else scale)
+    iters, glb = int(ITERS), float(GLB)
+    p = _lib.ptr
+    if KDA:
+        fn = _lib.lib().lq_kda_decode
+
+        def decode(Sq, Kbuf, Ubuf, Wbuf, Pbuf, Gbuf, hcnt, mixed, a, b, A_log, dt_bias, Q0, idx, o):
+            _launch(fn, "lq_kda_decode", Sq, d, p(Sq), p(Kbuf), p(Ubuf), p(Wbuf), p(Pbuf), p(Gbuf), p(hcnt), p(mixed), p(a), p(b),
+                    p(A_log), p(dt_bias), p(idx), p(o), int(mixed.shape[0]), sc, glb, p(Q0), iters)
+    else:
+        fn = _lib.lib().lq_gdn_decode
+
+        def decode(Sq, Kbuf, Ubuf, Wbuf, Pbuf, hcnt, mixed, a, b, A_log, dt_bias, Q0, idx, o):
+            _launch(fn, "lq_gdn_decode", Sq, d, p(Sq), p(Kbuf), p(Ubuf), p(Wbuf), p(Pbuf), p(hcnt), p(mixed), p(a), p(b),
+                    p(A_log), p(dt_bias), p(idx), p(o), int(mixed.shape[0]), sc, p(Q0), iters)
+
+    return decode
+
+
 def make_flush(NS, HV, K, V, L, SS, R=4, ITERS=1, SMS=148, NCG=3, MAXIT=128, PAD=8, KDA=False, MMT="bf16", PNMIN=1e-20,
                NMAX=0, NTP=0, RSG=None):
     """End-of-window flush of every head of the rows idx whose window is full.  Returns

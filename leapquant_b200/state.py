@@ -87,6 +87,9 @@ class LeapQuantState:
         else:
             self.kstep = KN.make_gdn_step(NS, HV, H, K, V, L, SS, R=R)
         self.kflush = KN.make_flush(NS, HV, K, V, L, SS, R=R, ITERS=1, KDA=kda, NMAX=nmax)
+        self.kdecode = KN.make_decode(NS, HV, H, K, V, L, SS, R=R, ITERS=1, KDA=kda, GLB=float(gate_lower_bound),
+                                      scale=(128 ** -0.5 if kda else None))
+        self.fused = True                                     # decode() = one fused launch; False = step then flush
         self.kdeq = KN.make_dequant(NS, HV, K, V, L, SS, buf_dtype=KN.BF16, R=R, kda=kda)
         self.kquant = KN.make_quantize(NS, HV, K, V, L, SS, R=R, ITERS=3 if kda else 1, kda=kda)
         self._vkey = None
@@ -118,6 +121,14 @@ class LeapQuantState:
         dt_bias = dt_bias.reshape(self.HV, KA).contiguous()
         idx = idx if idx.dtype == torch.int32 else idx.to(torch.int32)
         v = self.views(ssm)
+        if self.fused:
+            if self.kda:
+                self.kdecode(v["q32"], self.Kbuf, self.Ubuf, self.Wbuf, self.Pbuf, self.Gbuf, self.hcnt, mixed, a, b, A_log,
+                             dt_bias, self.Q0, idx, out)
+            else:
+                self.kdecode(v["q32"], self.Kbuf, self.Ubuf, self.Wbuf, self.Pbuf, self.hcnt, mixed, a, b, A_log, dt_bias,
+                             self.Q0, idx, out)
+            return
         if self.kda:
             self.kstep(v["q32"], v["Sk"], v["Sv"], v["skv"], self.Kbuf, self.Ubuf, self.Wbuf, self.Pbuf, self.Gbuf,
                        self.hcnt, mixed, a, b, A_log, dt_bias, v["uq"], idx, out)

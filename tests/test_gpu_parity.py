@@ -468,6 +468,35 @@ def test_sharded_equals_unsharded():
     assert torch.equal(bits(gpu_all.ssm[1:5]), bits(gpu_a.ssm[1:5])) and torch.equal(bits(gpu_all.ssm[5:9]), bits(gpu_b.ssm[5:9]))
 
 
+@pytest.mark.parametrize("kda,L,R,H,HV", [(False, 16, 4, 2, 4), (False, 64, 4, 1, 2), (True, 16, 4, 2, 2), (True, 32, 8, 2, 2)])
+def test_fused_decode_equals_step_then_flush(kda, L, R, H, HV):
+    """One fused launch per token gives bit-identical outputs, window buffers and packed state to the step kernel followed
+    by the flush kernel, over more than two windows and with rows whose windows fill at different steps."""
+    NS, N, T = 12, 10, 2 * L + 7
+    cpu, gpu_f = make_pair(NS, HV, H, L, R, kda=kda, seed=8)
+    gpu_s = GpuSide(cpu)
+    gpu_s.st.fused = False
+    assert gpu_f.st.fused
+    idx = torch.tensor([3, 1, 0, 7, 2, 9, 5, -1, 11, 4], dtype=torch.int32).cuda()
+    mixed, a, b_, A_log, dtb = step_inputs(N, H, HV, T, 9, kda, gate_shift=2.0)
+    o_f = torch.zeros(N, HV, V, dtype=torch.bfloat16, device="cuda")
+    o_s = torch.zeros_like(o_f)
+    bits = lambda x: x.view(torch.int32) if x.dtype == torch.float32 else x.view(torch.int16) if x.element_size() == 2 else x
+    for t in range(T):
+        rows = idx if t % 3 else idx[: N // 2]               # half of the rows skip every third step: windows drift apart
+        n = rows.numel()
+        for g, o in ((gpu_f, o_f), (gpu_s, o_s)):
+            g.st.decode(g.ssm, mixed[t][:n].cuda(), a[t][:n].cuda(), b_[t][:n].cuda(), A_log.cuda(), dtb.cuda(), rows, o[:n])
+        assert torch.equal(bits(o_f[:n]), bits(o_s[:n])), t
+        assert torch.equal(gpu_f.st.hcnt, gpu_s.st.hcnt), t
+    for name in ("Kbuf", "Ubuf", "Wbuf", "Pbuf") + (("Gbuf",) if kda else ()):
+        assert torch.equal(bits(getattr(gpu_f.st, name)), bits(getattr(gpu_s.st, name))), name
+    assert torch.equal(bits(gpu_f.ssm), bits(gpu_s.ssm))
+    from leapquant_b200 import _lib
+    torch.cuda.synchronize()
+    assert _lib.device_status() == 0
+
+
 def test_host_staged_decode_equals_direct():
     """Steps fed from pinned host memory through the double-buffered staging give bit-identical outputs and state."""
     from leapquant_b200.host_io import HostStagedDecoder
