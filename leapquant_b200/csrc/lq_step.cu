@@ -442,7 +442,7 @@ __device__ __forceinline__ void step_body(const StepParams& P, const ProgScalars
     // ---- window dots dk_j = K_j . k_hat, dq_j = K_j . q_hat: four rows per warp pass, passes dealt round-robin to the warps ----
     const int nch = (h + 3) >> 2;
 #ifndef LQ_DP
-#define LQ_DP 2
+#define LQ_DP 1
 #endif
     constexpr int DP = LQ_DP;                                 // passes in flight per warp (window rows 4*GW*DP per trip)
     for (int ch = w; ch < nch; ch += DP * GW) {
@@ -1020,8 +1020,12 @@ __global__ void __launch_bounds__(UT + NG * GT, 1) step_pipelined_kernel(StepPar
         __syncthreads();                                         // every role is done; the ring is dead, this CTA's global writes are visible
         if (*abortf) return;
         const int ndl = *dl_n;
+        // a team is exactly 256 threads (its named barrier counts them): threads beyond the last whole team leave
+        constexpr int MAX_TEAMS = (UT + NG * GT) / 256;
+        static_assert(MAX_TEAMS >= 1, "the fused flush needs at least 256 threads");
+        const int nteams = ft.teams < MAX_TEAMS ? ft.teams : MAX_TEAMS;
         const int team = tid >> 8, ttid = tid & 255;
-        if (ndl == 0 || team >= ft.teams) return;
+        if (ndl == 0 || team >= nteams) return;
         const FlushSmem fs = flush_carve<R>(stage_smem + team * ft.team_bytes, L, KDA);
         flush_init<R>(fs, ft.Q0, ttid);
         FlushArgs A;
@@ -1029,7 +1033,7 @@ __global__ void __launch_bounds__(UT + NG * GT, 1) step_pipelined_kernel(StepPar
         A.hcnt = P.hcnt; A.Q0 = ft.Q0; A.iters = ft.iters;
         auto tsync = [&] { named_bar(8 + team, 256); };
         long long facc[16] = {0}, flast = 0;
-        for (int k = team; k < ndl; k += ft.teams) flush_head<R, KDA>(fs, A, dl[k], ttid, tsync, facc, flast);
+        for (int k = team; k < ndl; k += nteams) flush_head<R, KDA>(fs, A, dl[k], ttid, tsync, facc, flast);
     }
 }
 
