@@ -33,7 +33,7 @@ static_assert(GW == 4 || GW == 8, "the reductions below are written for 4 or 8 w
 //      is ONE contiguous copy.  The pipelined driver sizes every stage for the program's live rows (rows = h), so that a
 //      ring of 220 KB holds ~6 average programs instead of 4 worst-case ones. ----
 struct StageLayout {
-    int kb, ub, w, q, k, v, gb, pb, a, dtb, nrm, bop, sc, bytes;
+    int kb, ub, w, q, k, v, gb, pb, a, dtb, nrm, bop, bdk, sc, bytes;
 };
 __host__ __device__ inline StageLayout stage_layout(int rows, int L, int R, bool kda) {
     StageLayout s;
@@ -53,6 +53,7 @@ __host__ __device__ inline StageLayout stage_layout(int rows, int L, int R, bool
     }
     s.nrm = o; o += (kda ? 4 : 2) * 512;    // prologue output: k_hat, q_hat, then KDA: pc, en  (f32[128] each)
     s.bop = o; o += 4 * 256;                // prologue output: matvec operands as f16[128] x {k hi, k lo, q hi, q lo}
+    s.bdk = o; o += 4 * 256;                // prologue output: k_hat, q_hat as bf16[128] x {k head, k remainder, q head, q remainder}
     s.sc = o; o += 64;                      // ProgScalars (producer) + k_hat . q_hat and the operand unscale (prologue)
     s.bytes = (o + 127) & ~127;
     return s;
@@ -191,6 +192,13 @@ __device__ __forceinline__ void s8x4_to_h2x2(uint32_t w, uint32_t& lo, uint32_t&
     lo = *reinterpret_cast<const uint32_t*>(&r0);
     hi = *reinterpret_cast<const uint32_t*>(&r1);
 }
+// D += A B for one m16n8k16 tile, bf16 operands, f32 accumulator (warp-wide)
+__device__ __forceinline__ void mma_bf16_16816(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0,
+                                               uint32_t b1) {
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+                 : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+                 : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
 // D += A B for one m16n8k16 tile, f16 operands, f32 accumulator (warp-wide)
 __device__ __forceinline__ void mma_f16_16816(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0,
                                               uint32_t b1) {
@@ -287,6 +295,19 @@ __device__ __forceinline__ void step_prologue(const StepParams& P, const ProgSca
         }
 #pragma unroll
         for (int n = 0; n < 4; ++n) reinterpret_cast<uint2*>(st + lay.bop + n * 256)[lane] = make_uint2(hw[n][0], hw[n][1]);
+    }
+    {   // k_hat, q_hat as bf16 head + remainder (16 mantissa bits): the B operand of the window dots on the tensor cores
+        float kh[4], kl[4], qh[4], ql[4];
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            kh[i] = round_bf16(k[i]); kl[i] = k[i] - kh[i];
+            qh[i] = round_bf16(q[i]); ql[i] = q[i] - qh[i];
+        }
+        uint2* bd = reinterpret_cast<uint2*>(st + lay.bdk);
+        bd[lane] = make_uint2(f2_to_bf16x2(kh[0], kh[1]), f2_to_bf16x2(kh[2], kh[3]));
+        bd[32 + lane] = make_uint2(f2_to_bf16x2(kl[0], kl[1]), f2_to_bf16x2(kl[2], kl[3]));
+        bd[64 + lane] = make_uint2(f2_to_bf16x2(qh[0], qh[1]), f2_to_bf16x2(qh[2], qh[3]));
+        bd[96 + lane] = make_uint2(f2_to_bf16x2(ql[0], ql[1]), f2_to_bf16x2(ql[2], ql[3]));
     }
     float4* nrm = reinterpret_cast<float4*>(st + lay.nrm);
     const int sl = nrm_chunk(lane);                       // swizzled 16-byte chunk of this lane's four channels
@@ -439,56 +460,54 @@ __device__ __forceinline__ void step_body(const StepParams& P, const ProgScalars
         }
     }
 
-    // ---- window dots dk_j = K_j . k_hat, dq_j = K_j . q_hat: four rows per warp pass, passes dealt round-robin to the warps ----
-    const int nch = (h + 3) >> 2;
-#ifndef LQ_DP
-#define LQ_DP 1
-#endif
-    constexpr int DP = LQ_DP;                                 // passes in flight per warp (window rows 4*GW*DP per trip)
-    for (int ch = w; ch < nch; ch += DP * GW) {
-        uint4 r0[DP], r1[DP];
-        int jrow[DP];
+    // ---- window dots dk_j = K_j . k_hat, dq_j = K_j . q_hat on the tensor cores: D[j][n] = sum_c K_j[c] B[c][n] with
+    //      n = {k head, k remainder, q head, q remainder} (bf16, fp32 accumulate).  Sixteen rows per m16 tile, tiles dealt
+    //      round-robin to the warps; lane (gid, tig) reads rows gid and gid + 8 as four 16-byte chunks at 64 c + 16 tig, so
+    //      the k index of the instruction is again a permutation of the columns that the B fragments follow. ----
+    {
+        const int gid = lane >> 2, tig = lane & 3;
+        const int nmt = (h + 15) >> 4;
+        if (w < nmt) {
+            uint32_t bfr[16];
+            {
+                uint4 x[4] = {make_uint4(0, 0, 0, 0), make_uint4(0, 0, 0, 0), make_uint4(0, 0, 0, 0), make_uint4(0, 0, 0, 0)};
+                if (gid < 4) {
+                    const uint4* bp = reinterpret_cast<const uint4*>(st + lay.bdk + gid * 256 + tig * 16);
+                    x[0] = bp[0]; x[1] = bp[4]; x[2] = bp[8]; x[3] = bp[12];
+                }
 #pragma unroll
-        for (int u = 0; u < DP; ++u) {
-            jrow[u] = 4 * (ch + u * GW) + g;
-            const char* rp = st + lay.kb + (jrow[u] < h ? jrow[u] : 0) * 256;
-            r0[u] = reinterpret_cast<const uint4*>(rp)[l8 * 2];
-            r1[u] = reinterpret_cast<const uint4*>(rp)[l8 * 2 + 1];
-        }
-        float dk[DP], dq[DP];
-#pragma unroll
-        for (int u = 0; u < DP; ++u) {
-            const uint32_t ww[8] = {r0[u].x, r0[u].y, r0[u].z, r0[u].w, r1[u].x, r1[u].y, r1[u].z, r1[u].w};
-            float2 ak = make_float2(0.f, 0.f), aq = ak;
-#pragma unroll
-            for (int i = 0; i < 8; ++i) {
-                const float2 x = bf16x2_to_f2(ww[i]);
-                ak = __ffma2_rn(x, kn[i], ak);
-                aq = __ffma2_rn(x, qn[i], aq);
+                for (int i = 0; i < 4; ++i) { bfr[4 * i] = x[i].x; bfr[4 * i + 1] = x[i].y; bfr[4 * i + 2] = x[i].z; bfr[4 * i + 3] = x[i].w; }
             }
-            dk[u] = ak.x + ak.y;
-            dq[u] = aq.x + aq.y;
-        }
-#pragma unroll
-        for (int o = 1; o <= 4; o <<= 1) {
-#pragma unroll
-            for (int u = 0; u < DP; ++u) {
-                dk[u] += __shfl_xor_sync(0xffffffffu, dk[u], o);
-                dq[u] += __shfl_xor_sync(0xffffffffu, dq[u], o);
-            }
-        }
-        if (l8 == 0) {
             const float* ws = reinterpret_cast<const float*>(st + lay.w);        // GDN: already decayed by the prologue
+            float* wdf = reinterpret_cast<float*>(gs.wd);
+            for (int mt = w; mt < nmt; mt += GW) {
+                const int j0 = 16 * mt + gid, j1 = j0 + 8;
+                const char* p0 = st + lay.kb + (j0 < h ? j0 : h - 1) * 256 + tig * 16;      // rows past h repeat the last row
+                const char* p1 = st + lay.kb + (j1 < h ? j1 : h - 1) * 256 + tig * 16;
+                uint4 x0[4], x1[4];
 #pragma unroll
-            for (int u = 0; u < DP; ++u)
-                if (jrow[u] < h) { const float wj = ws[jrow[u]]; gs.wd[jrow[u]] = make_float2(wj * dk[u], wj * dq[u]); }
+                for (int c = 0; c < 4; ++c) {
+                    x0[c] = *reinterpret_cast<const uint4*>(p0 + 64 * c);
+                    x1[c] = *reinterpret_cast<const uint4*>(p1 + 64 * c);
+                }
+                float d[4] = {0.f, 0.f, 0.f, 0.f}, e[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+                for (int c = 0; c < 4; ++c) {
+                    mma_bf16_16816(d, x0[c].x, x1[c].x, x0[c].y, x1[c].y, bfr[4 * c], bfr[4 * c + 1]);
+                    mma_bf16_16816(e, x0[c].z, x1[c].z, x0[c].w, x1[c].w, bfr[4 * c + 2], bfr[4 * c + 3]);
+                }
+                if (tig < 2) {                               // tig 0 holds (k head, k remainder), tig 1 holds (q head, q remainder)
+                    if (j0 < h) wdf[2 * j0 + tig] = ws[j0] * ((d[0] + e[0]) + (d[1] + e[1]));
+                    if (j1 < h) wdf[2 * j1 + tig] = ws[j1] * ((d[2] + e[2]) + (d[3] + e[3]));
+                }
+            }
         }
     }
     LQ_PSTAMP(2);
     // ---- factor dots dU_r . k_hat, dU_r . q_hat (KDA: U_r[c] pc[c]) ----
 #pragma unroll
     for (int cr = 0; cr < R / 4; ++cr) {
-        if (((nch + cr) % GW) == w) {
+        if (((((h + 15) >> 4) + cr) % GW) == w) {
             const int r = 4 * cr + g;
             const uint4 r0 = reinterpret_cast<const uint4*>(st + CK_UQ + r * 512)[l8 * 2];
             const uint4 r1 = reinterpret_cast<const uint4*>(st + CK_UQ + r * 512)[l8 * 2 + 1];
