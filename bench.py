@@ -372,10 +372,8 @@ def run_b200(args, wl):
     achieved = alg_launch / (step_ms * 1e-3) / 1e9
     traffic = NCU_TRAFFIC_RATIO["kda" if kda else "gdn"]
 
-    if world > 1:
-        tt = torch.tensor([dt, dt_e2e], device=device, dtype=torch.float64)
-        dist.all_reduce(tt, op=dist.ReduceOp.MAX)
-        dt, dt_e2e = float(tt[0]), float(tt[1])
+    from leapquant_b200.sharding import job_times
+    dt, dt_e2e = job_times([dt, dt_e2e], device)               # max over ranks
     done = nwin * L + rem
     units = world * B * HV * done
     value = units / dt

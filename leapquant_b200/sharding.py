@@ -35,3 +35,17 @@ def slice_mixed_heads(mixed, H, HV, K, V, world, rank):
     k = mixed[:, H * K + k0 * K:H * K + k1 * K]
     v = mixed[:, 2 * H * K + v0 * V:2 * H * K + v1 * V]
     return torch.cat([q, k, v], dim=1).contiguous()
+
+
+def job_times(local_seconds, device=None):
+    """Whole-job time of a weakly scaled run: the MAXIMUM over the ranks of each entry of `local_seconds` (a list of floats
+    timed on this rank's device).  The only communication of the multi-GPU path: one all-reduce of a few doubles after the
+    timed region (NCCL on GPUs, gloo in the CPU tests).  Without an initialised process group it returns the input."""
+    import torch
+    import torch.distributed as dist
+    vals = [float(x) for x in local_seconds]
+    if not (dist.is_available() and dist.is_initialized()) or dist.get_world_size() == 1:
+        return vals
+    t = torch.tensor(vals, dtype=torch.float64, device=device if device is not None else "cpu")
+    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    return [float(x) for x in t]
