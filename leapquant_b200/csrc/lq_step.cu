@@ -35,15 +35,18 @@ static_assert(GW == 4 || GW == 8, "the reductions below are written for 4 or 8 w
 struct StageLayout {
     int kb, ub, w, q, k, v, gb, pb, a, dtb, nrm, bop, bdk, sc, bytes;
 };
-__host__ __device__ inline StageLayout stage_layout(int rows, int L, int R, bool kda) {
+__host__ __device__ inline StageLayout stage_layout(int rows, int L, int R, bool kda, bool qkv = true) {
     StageLayout s;
     int o = ck_bytes(R);
     s.kb = o; o += rows * 256;
     s.ub = o; o += rows * 256;
     s.w = o; o += L * 4;
-    s.q = o; o += 256;
-    s.k = o; o += 256;
-    s.v = o; o += 256;
+    s.q = s.k = s.v = 0;
+    if (qkv) {                               // the pipelined driver reads q, k, v straight from global memory into registers
+        s.q = o; o += 256;
+        s.k = o; o += 256;
+        s.v = o; o += 256;
+    }
     s.gb = s.pb = s.a = s.dtb = 0;
     if (kda) {
         s.gb = o; o += rows * 256;
@@ -213,12 +216,13 @@ __device__ __forceinline__ void mma_f16_16816(float (&d)[4], uint32_t a0, uint32
 // `signal()` is called after the last shared-memory write and BEFORE the global stores (see step_body's `release`).
 template <bool KDA, typename Signal>
 __device__ __forceinline__ void step_prologue(const StepParams& P, const ProgScalars& sc, char* st, const StageLayout& lay,
-                                              int lane, Signal signal, int pi = -1) {
+                                              int lane, Signal signal, int pi = -1, bool qk_regs = false,
+                                              uint2 q_in = make_uint2(0u, 0u), uint2 k_in = make_uint2(0u, 0u)) {
     const int L = P.d.L, h = sc.h;
     LQ_NSTAMP(0);
     const int64_t sh = int64_t(sc.slot) * P.d.HV + sc.hv;
-    const uint2 qw = reinterpret_cast<const uint2*>(st + lay.q)[lane];
-    const uint2 kw = reinterpret_cast<const uint2*>(st + lay.k)[lane];
+    const uint2 qw = qk_regs ? q_in : reinterpret_cast<const uint2*>(st + lay.q)[lane];      // this lane's four channels of q
+    const uint2 kw = qk_regs ? k_in : reinterpret_cast<const uint2*>(st + lay.k)[lane];
     float q[4], k[4];
     q[0] = bf16lo(qw.x); q[1] = bf16hi(qw.x); q[2] = bf16lo(qw.y); q[3] = bf16hi(qw.y);
     k[0] = bf16lo(kw.x); k[1] = bf16hi(kw.x); k[2] = bf16lo(kw.y); k[3] = bf16hi(kw.y);
@@ -379,6 +383,9 @@ __device__ __forceinline__ void step_body(const StepParams& P, const ProgScalars
     const int64_t sh = int64_t(sc.slot) * P.d.HV + sc.hv;
     LQ_PSTAMP(0);
     const float* nrm = reinterpret_cast<const float*>(st + lay.nrm);
+    // this lane's two values of the token's v, straight from global memory: issued now, used in the last phase
+    const uint32_t vraw = __ldg(reinterpret_cast<const uint32_t*>(
+        P.mixed + int64_t(sc.n) * (2 * P.d.H * KD + P.d.HV * VD) + 2 * P.d.H * KD + sc.hv * VD) + (64 / GW) * w + ((t & 31) % (64 / GW)));
 
     // ---- KDA: decayed window keys K_j D_j (bf16, in place), D_j = en prod_{j<i<h} e_i; thread per key channel ----
     if (KDA) {
@@ -565,7 +572,7 @@ __device__ __forceinline__ void step_body(const StepParams& P, const ProgScalars
     float u0 = 0.f, u1 = 0.f, y0 = 0.f, y1 = 0.f, pn = 0.f;
     if (jh == 0) {
         const float2 m0 = gs.mqy[2 * vp], m1 = gs.mqy[2 * vp + 1];
-        const float2 vv = bf16x2_to_f2(reinterpret_cast<const uint32_t*>(st + lay.v)[vp]);
+        const float2 vv = bf16x2_to_f2(vraw);
         const float beta = sc.beta;
         const float kq = *reinterpret_cast<const float*>(st + lay.sc + 32);
         if (KDA) {
@@ -824,7 +831,7 @@ __global__ void __launch_bounds__(UT + NG * GT, 1) step_pipelined_kernel(StepPar
                 const ProgScalars sc = *const_cast<const ProgScalars*>(&pbatch[j]);      // broadcast read
                 const bool live = prog_live(sc, L);
                 const int rows = live ? sc.h : 0;
-                const StageLayout lay = stage_layout(rows, L, R, KDA);
+                const StageLayout lay = stage_layout(rows, L, R, KDA, false);
                 const int size = lay.bytes - SKIP;
                 int off = head;
                 uint32_t v0 = vhead;
@@ -852,7 +859,7 @@ __global__ void __launch_bounds__(UT + NG * GT, 1) step_pipelined_kernel(StepPar
                     doff[ND + NG + dsc] = rows;
                     *reinterpret_cast<ProgScalars*>(st + lay.sc) = sc;
                     if (live) {
-                        uint32_t bytes = uint32_t(ck_bytes(R) - SKIP) + 2u * uint32_t(sc.h) * 256u + uint32_t(L) * 4u + 3u * 256u;
+                        uint32_t bytes = uint32_t(ck_bytes(R) - SKIP) + 2u * uint32_t(sc.h) * 256u + uint32_t(L) * 4u;
                         if (KDA) bytes += uint32_t(sc.h) * 256u + 512u + 256u + 512u;
                         mbar_arrive_expect_tx(full + dsc, bytes);
                     } else {
@@ -869,7 +876,6 @@ __global__ void __launch_bounds__(UT + NG * GT, 1) step_pipelined_kernel(StepPar
 
     if (warp == 1) {
         // ================= copy issue: one bulk asynchronous copy per lane and program =================
-        const int MIX = 2 * H * KD + HV * VD;
         const int gqa = HV / H;
         // Per-lane copy descriptor, fixed for the whole kernel: lane k < ncopy issues copy k of every program from
         //   src = base + slot * c_slot + hv * c_hv + n * c_n + hk * c_hk,   bytes = b_fix + h * b_h,
@@ -878,16 +884,13 @@ __global__ void __launch_bounds__(UT + NG * GT, 1) step_pipelined_kernel(StepPar
         uint32_t c_slot = 0, c_hv = 0, c_n = 0, c_hk = 0, b_fix = 0, b_h = 0, o_fix = 0, o_h = 0;
         {
             const uint32_t rowb = uint32_t(L) * 256u;                    // one head's window rows (bf16 / f16) in bytes
-            const StageLayout l0 = stage_layout(0, L, R, KDA), l1 = stage_layout(1, L, R, KDA);
+            const StageLayout l0 = stage_layout(0, L, R, KDA, false), l1 = stage_layout(1, L, R, KDA, false);
             int which = -1;                                              // member of the layout this lane copies into
             switch (lane) {
                 case 0: c_base = P.ssm + SKIP; c_slot = uint32_t(P.d.SS) * 4u; c_hv = VD * KD * 4u; b_fix = ck_bytes(R) - SKIP; o_fix = SKIP; break;
                 case 1: c_base = reinterpret_cast<const char*>(P.Kbuf); c_slot = uint32_t(HV) * rowb; c_hv = rowb; b_h = 256u; which = 0; break;
                 case 2: c_base = reinterpret_cast<const char*>(P.Ubuf); c_slot = uint32_t(HV) * rowb; c_hv = rowb; b_h = 256u; which = 1; break;
                 case 3: c_base = reinterpret_cast<const char*>(P.Wbuf); c_slot = uint32_t(HV * L) * 4u; c_hv = uint32_t(L) * 4u; b_fix = uint32_t(L) * 4u; which = 2; break;
-                case 4: c_base = reinterpret_cast<const char*>(P.mixed); c_n = uint32_t(MIX) * 2u; c_hk = 256u; b_fix = 256u; which = 3; break;
-                case 5: c_base = reinterpret_cast<const char*>(P.mixed) + H * 256; c_n = uint32_t(MIX) * 2u; c_hk = 256u; b_fix = 256u; which = 4; break;
-                case 6: c_base = reinterpret_cast<const char*>(P.mixed) + 2 * H * 256; c_n = uint32_t(MIX) * 2u; c_hv = 256u; b_fix = 256u; which = 5; break;
                 case 7: if (KDA) { c_base = reinterpret_cast<const char*>(P.Gbuf); c_slot = uint32_t(HV) * rowb; c_hv = rowb; b_h = 256u; which = 6; } break;
                 case 8: if (KDA) { c_base = reinterpret_cast<const char*>(P.Pbuf); c_slot = uint32_t(HV) * 512u; c_hv = 512u; b_fix = 512u; which = 7; } break;
                 case 9: if (KDA) { c_base = reinterpret_cast<const char*>(P.a); c_n = uint32_t(HV) * 256u; c_hv = 256u; b_fix = 256u; which = 8; } break;
@@ -909,7 +912,7 @@ __global__ void __launch_bounds__(UT + NG * GT, 1) step_pipelined_kernel(StepPar
             }
             char* st = stage_smem + doff[dsc] - SKIP;
             const int rows = doff[ND + NG + dsc];
-            const ProgScalars sc = *reinterpret_cast<const ProgScalars*>(st + stage_layout(rows, L, R, KDA).sc);
+            const ProgScalars sc = *reinterpret_cast<const ProgScalars*>(st + stage_layout(rows, L, R, KDA, false).sc);
             if (prog_live(sc, L)) {
                 LQ_QSTAMP(4);
                 // The ring bytes under this stage were read and written through the generic proxy by the previous tenants'
@@ -929,8 +932,23 @@ __global__ void __launch_bounds__(UT + NG * GT, 1) step_pipelined_kernel(StepPar
 
     if (warp < 2 + NPW) {
         // ================= prologue warps: programs dealt round-robin, each warp in fill order =================
+        // q and k of a program come straight from global memory into this warp's registers (lane = four channels), fetched
+        // one program of this warp ahead: row and key head follow from the program index alone
+        const int MIXq = 2 * H * KD + HV * VD, gqaq = HV / H;
+        uint2 q_nx = make_uint2(0u, 0u), k_nx = make_uint2(0u, 0u);
+        auto qk_fetch = [&](int i2) {
+            if (i2 >= nit) return;
+            const int p2 = bid + i2 * grid;
+            const int n2 = p2 / HV, hk2 = (p2 - n2 * HV) / gqaq;
+            const uint2* mrow = reinterpret_cast<const uint2*>(P.mixed + int64_t(n2) * MIXq);
+            q_nx = __ldg(mrow + hk2 * 32 + lane);
+            k_nx = __ldg(mrow + (H + hk2) * 32 + lane);
+        };
+        qk_fetch(warp - 2);
         for (int i = warp - 2; i < nit; i += NPW) {
             const int dsc = i % ND;
+            const uint2 q_cur = q_nx, k_cur = k_nx;
+            qk_fetch(i + NPW);
 #ifdef LQ_TRACE
             if (i < 256 && blockIdx.x < 160 && lane == 0) g_ntrace[(blockIdx.x * 256 + i) * 8 + 7] = clock64();
 #endif
@@ -940,11 +958,11 @@ __global__ void __launch_bounds__(UT + NG * GT, 1) step_pipelined_kernel(StepPar
             }
             char* st = stage_smem + doff[dsc] - SKIP;
             const int rows = doff[ND + NG + dsc];                  // rows the stage was sized for (h, or 0 for a dead program)
-            const ProgScalars sc = *reinterpret_cast<const ProgScalars*>(st + stage_layout(rows, L, R, KDA).sc);
+            const ProgScalars sc = *reinterpret_cast<const ProgScalars*>(st + stage_layout(rows, L, R, KDA, false).sc);
             if (lane == 0) LQ_STAMP(i, 1);
             if (prog_live(sc, L)) {
-                const StageLayout lay = stage_layout(sc.h, L, R, KDA);
-                step_prologue<KDA>(P, sc, st, lay, lane, [&] { mbar_arrive(normed + dsc); }, i);
+                const StageLayout lay = stage_layout(sc.h, L, R, KDA, false);
+                step_prologue<KDA>(P, sc, st, lay, lane, [&] { mbar_arrive(normed + dsc); }, i, true, q_cur, k_cur);
             } else {
                 mbar_arrive(normed + dsc);
             }
@@ -1004,7 +1022,7 @@ __global__ void __launch_bounds__(UT + NG * GT, 1) step_pipelined_kernel(StepPar
         }
         char* st = stage_smem + doff[dsc] - SKIP;
         const int rows = doff[ND + NG + dsc];
-        const StageLayout lay = stage_layout(rows, L, R, KDA);
+        const StageLayout lay = stage_layout(rows, L, R, KDA, false);
         const ProgScalars sc = *reinterpret_cast<const ProgScalars*>(st + lay.sc);
         if (t == 0) LQ_STAMP(i, 2);
 #ifdef LQ_FENCE_CONSUMER
@@ -1087,9 +1105,10 @@ static int launch_step(const StepParams& P, cudaStream_t st, const FuseTail* fus
     const size_t budget = 227 * 1024;
     const size_t fixed = size_t(NG) * SCRATCH_BYTES + 4 * ND * sizeof(uint64_t) + (2 * ND + NG + 4) * sizeof(int) + 32 * sizeof(ProgScalars) +
                          (4 + size_t(nit_max)) * sizeof(int);
-    if (fixed + size_t(lay.bytes) > budget) return LQ_ERR_UNSUPPORTED;
+    const int lay_p = stage_layout(P.d.L, P.d.L, R, KDA, false).bytes;
+    if (fixed + size_t(lay_p) > budget) return LQ_ERR_UNSUPPORTED;
     const int ring_bytes = int((budget - fixed) & ~size_t(127));
-    if (ring_bytes < lay.bytes) return LQ_ERR_UNSUPPORTED;
+    if (ring_bytes < lay_p) return LQ_ERR_UNSUPPORTED;
     const size_t smem = size_t(ring_bytes) + fixed;
     FuseTail ft = {nullptr, 0, 0, 0};
     cudaError_t le;
