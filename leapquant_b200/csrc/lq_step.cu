@@ -26,7 +26,6 @@ namespace lq {
 
 constexpr int GW = LQ_GW;                 // warps of one consumer group (a group executes one program at a time)
 constexpr int GT = 32 * GW;               // its threads
-constexpr int NPASS = 32 / GW;            // tile passes per warp (four 128-byte rows per pass)
 static_assert(GW == 4 || GW == 8, "the reductions below are written for 4 or 8 warps per group");
 
 // ---- stage layout (bytes) of a program with `rows` window rows; the checkpoint part mirrors the packed slot so that it
@@ -393,7 +392,22 @@ __device__ __forceinline__ void step_body(const StepParams& P, const ProgScalars
             uint16_t* kb = reinterpret_cast<uint16_t*>(st + lay.kb);
             const uint16_t* gb = reinterpret_cast<const uint16_t*>(st + lay.gb);
             float dcur = nrm[384 + 4 * nrm_chunk(t >> 2) + (t & 3)];
-            for (int j = h - 1; j >= 0; --j) {
+            // eight rows per trip: their loads are issued together, only the running product is a serial chain
+            int j = h - 1;
+            for (; j >= 7; j -= 8) {
+                float kv[8], gv[8];
+#pragma unroll
+                for (int u = 0; u < 8; ++u) {
+                    kv[u] = bf16_to_f(kb[(j - u) * KD + t]);
+                    gv[u] = f16_to_f(gb[(j - u) * KD + t]);
+                }
+#pragma unroll
+                for (int u = 0; u < 8; ++u) {
+                    kb[(j - u) * KD + t] = f_to_bf16(kv[u] * dcur);
+                    dcur *= gv[u];
+                }
+            }
+            for (; j >= 0; --j) {
                 kb[j * KD + t] = f_to_bf16(bf16_to_f(kb[j * KD + t]) * dcur);
                 dcur *= f16_to_f(gb[j * KD + t]);
             }
@@ -717,21 +731,6 @@ __device__ __forceinline__ void bulk_g2s(void* dst, const void* src, uint32_t by
                  : "memory");
 }
 __device__ __forceinline__ void fence_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
-// group-wide AND of a predicate over a named barrier (also a barrier)
-__device__ __forceinline__ bool group_all(int bar, int nthreads, bool pred) {
-    uint32_t r;
-    asm volatile(
-        "{\n"
-        ".reg .pred p, q;\n"
-        "setp.ne.u32 q, %3, 0;\n"
-        "barrier.cta.red.and.pred p, %1, %2, q;\n"
-        "selp.u32 %0, 1, 0, p;\n"
-        "}\n"
-        : "=r"(r)
-        : "r"(bar), "r"(nthreads), "r"(uint32_t(pred))
-        : "memory");
-    return r != 0;
-}
 
 // warp 0: producer (places stages, publishes scalars), warp 1: copy issue, warp 2: prologue, warps 3 ..: NG consumer groups
 // of GW warps.
@@ -1025,25 +1024,14 @@ __global__ void __launch_bounds__(UT + NG * GT, 1) step_pipelined_kernel(StepPar
         const StageLayout lay = stage_layout(rows, L, R, KDA, false);
         const ProgScalars sc = *reinterpret_cast<const ProgScalars*>(st + lay.sc);
         if (t == 0) LQ_STAMP(i, 2);
-#ifdef LQ_FENCE_CONSUMER
-        auto release = [&] { fence_async_smem(); mbar_arrive(empty + dsc); };
-#else
         auto release = [&] { mbar_arrive(empty + dsc); };
-#endif
-#ifdef LQ_NOBODY
-        if (false) {
-#else
         if (prog_live(sc, L)) {
-#endif
             step_body<R, KDA, REGC>(P, sc, st, lay, gs, t, bar, release, ac, refill, i);
             if (FUSE && t == 0 && sc.h + 1 == L) dl[atomicAdd(dl_n, 1)] = sc.slot * HV + sc.hv;      // window just filled
         } else {
             if (FUSE && t == 0 && sc.slot > 0 && sc.h == L) dl[atomicAdd(dl_n, 1)] = sc.slot * HV + sc.hv;   // was full already
             refill();
             release();
-#ifdef LQ_NOBODY
-            if (t == 0 && prog_live(sc, L)) P.hcnt[int64_t(sc.slot) * P.d.HV + sc.hv] = sc.h + 1;
-#endif
             const int p = bid + i * grid;
             if (t < 64) reinterpret_cast<uint32_t*>(P.o)[int64_t(p) * 64 + t] = 0u;
         }
