@@ -102,25 +102,48 @@ __device__ __forceinline__ GroupScratch carve_scratch(char* p) {
     return g;
 }
 
-__device__ __forceinline__ ProgScalars load_scalars(const StepParams& P, int n, int hv, bool kda) {
+// The scalars of a program come from two levels of dependent global loads (row -> slot -> counters and gates).  They are
+// split so that a caller can keep both levels of several programs in flight: load_raw() only issues loads (no branch, no
+// arithmetic on what it loaded; a null row reads slot 0, which exists and is never used), finish_scalars() does the math.
+struct RawScalars {
+    int slot, h, n, hv;
+    float alog, pold, dtb;
+    uint16_t a, b;
+};
+__device__ __forceinline__ RawScalars load_raw(const StepParams& P, int n, int hv, int slot, bool kda) {
+    RawScalars r;
+    r.n = n; r.hv = hv;
+    r.slot = (slot > 0 && slot < P.d.NS) ? slot : 0;
+    const int64_t sh = int64_t(r.slot) * P.d.HV + hv;
+    r.h = P.hcnt[sh];
+    r.alog = P.A_log[hv];
+    r.b = P.b[int64_t(n) * P.d.HV + hv];
+    r.a = 0; r.dtb = 0.f; r.pold = 1.f;
+    if (!kda) {
+        r.a = P.a[int64_t(n) * P.d.HV + hv];
+        r.dtb = P.dt_bias[hv];
+        r.pold = P.Pbuf[sh];
+    }
+    return r;
+}
+__device__ __forceinline__ ProgScalars finish_scalars(const RawScalars& r, bool kda) {
     ProgScalars s;
-    s.n = n; s.hv = hv;
-    s.slot = P.idx[n];
+    s.n = r.n; s.hv = r.hv; s.slot = r.slot;
     s.h = 0; s.alpha = 1.f; s.beta = 0.f; s.pold = 1.f; s.ea = 1.f;
-    if (s.slot > 0 && s.slot < P.d.NS) {
-        const int64_t sh = int64_t(s.slot) * P.d.HV + hv;
-        s.h = P.hcnt[sh];
-        s.ea = expf(P.A_log[hv]);
-        s.beta = round_bf16(sigmoidf_(bf16_to_f(P.b[int64_t(n) * P.d.HV + hv])));
+    if (r.slot > 0) {
+        s.h = r.h;
+        s.ea = expf(r.alog);
+        s.beta = round_bf16(sigmoidf_(bf16_to_f(r.b)));
         if (!kda) {
-            const float xg = bf16_to_f(P.a[int64_t(n) * P.d.HV + hv]) + P.dt_bias[hv];
+            const float xg = bf16_to_f(r.a) + r.dtb;
             s.alpha = expf(-s.ea * softplus_thr(xg));
-            s.pold = P.Pbuf[sh];
+            s.pold = r.pold;
         }
-    } else {
-        s.slot = 0;
     }
     return s;
+}
+__device__ __forceinline__ ProgScalars load_scalars(const StepParams& P, int n, int hv, bool kda) {
+    return finish_scalars(load_raw(P, n, hv, P.idx[n], kda), kda);
 }
 __device__ __forceinline__ bool prog_live(const ProgScalars& s, int L) { return s.slot > 0 && s.h >= 0 && s.h < L; }
 
@@ -779,6 +802,7 @@ __global__ void __launch_bounds__(UT + NG * GT, 1) step_pipelined_kernel(StepPar
     const int nit = (nprog - bid + grid - 1) / grid;
 
     if (tid == 0) {
+        LQ_STAMP(TRACE_PROGS - 1, 0);                            // (trace builds) kernel entry
         *dl_n = 0;
         *abortf = 0;
         for (int s = 0; s < ND; ++s) {
@@ -793,22 +817,27 @@ __global__ void __launch_bounds__(UT + NG * GT, 1) step_pipelined_kernel(StepPar
     __syncthreads();
     pdl_trigger();
     pdl_wait();                                                  // everything below reads what earlier kernels of the stream wrote
+    if (tid == 0) LQ_STAMP(TRACE_PROGS - 1, 1);                  // (trace builds) set-up done, predecessor complete
 
     auto run_roles = [&]() {
     if (warp == 0) {
         // ================= producer: scalars of 32 programs per batch, then one stage placement per program =================
-        ProgScalars cur, nxt;
-        auto fetch = [&](int i) {
-            ProgScalars r;
-            r.slot = 0; r.h = 0; r.n = 0; r.hv = 0; r.alpha = 1.f; r.beta = 0.f; r.pold = 1.f; r.ea = 1.f;
-            if (i < nit) {
-                const int p = bid + i * grid;
-                const int n = p / HV;
-                r = load_scalars(P, n, p - n * HV, KDA);
-            }
-            return r;
+        // Scalars of 32 programs per batch, one program per lane, fetched two levels ahead: while batch b is placed, the
+        // counters and gates of batch b + 1 and the slots of batch b + 2 are in flight.
+        ProgScalars cur;
+        auto slot_of = [&](int i) -> int { return i < nit ? P.idx[(bid + i * grid) / HV] : 0; };
+        auto raw_of = [&](int i, int slot) {
+            const int p = i < nit ? bid + i * grid : bid;
+            const int n = p / HV;
+            return load_raw(P, n, p - n * HV, i < nit ? slot : 0, KDA);
         };
-        nxt = fetch(lane);
+        int slot_b;
+        RawScalars rnx;
+        {
+            const int s0 = slot_of(lane);
+            slot_b = slot_of(32 + lane);
+            rnx = raw_of(lane, s0);
+        }
         // The ring is a FIFO: stages are placed in program order and reclaimed in program order.  Space is accounted in
         // virtual bytes: a stage that does not fit before the end of the ring starts at 0 and the skipped tail counts as
         // allocated, so the virtual position modulo the ring size is always the physical offset and the live programs
@@ -817,11 +846,12 @@ __global__ void __launch_bounds__(UT + NG * GT, 1) step_pipelined_kernel(StepPar
         uint32_t vhead = 0, r_vs = 0;                            // virtual head; lane (i % ND) keeps the virtual start of program i
         bool ok = true;
         for (int base = 0; base < nit && ok; base += 32) {
-            cur = nxt;
+            cur = finish_scalars(rnx, KDA);
             __syncwarp();
             pbatch[lane] = cur;                                  // the batch's scalars, one entry per lane
             __syncwarp();
-            nxt = fetch(base + 32 + lane);
+            rnx = raw_of(base + 32 + lane, slot_b);
+            slot_b = slot_of(base + 64 + lane);
             const int cnt = min(32, nit - base);
             for (int j = 0; j < cnt; ++j) {
                 const int i = base + j;
@@ -1039,6 +1069,7 @@ __global__ void __launch_bounds__(UT + NG * GT, 1) step_pipelined_kernel(StepPar
     }
     };
     run_roles();
+    if (tid == UT) LQ_STAMP(TRACE_PROGS - 1, 2);                 // (trace builds) first consumer group done
 
     // ================= fused flush: the heads whose window this CTA just filled, two teams of 256 threads =================
     if constexpr (FUSE) {
