@@ -211,12 +211,16 @@ class Layer:
         self.st.quantize(self.ssm, self.idx)
         self.period = L
         mixed, a, b, A_log, dtb = synth_inputs(B, H, HV, self.period, seed + 1, kda)
-        self.h_mixed, self.h_a, self.h_b = mixed.pin_memory(), a.contiguous().pin_memory(), b.pin_memory()
+        # pinned host copies of the inputs, the three tensors of a step back to back so that one copy moves them
+        from leapquant_b200.host_io import HostStagedDecoder
+        self.h_slab, hv = HostStagedDecoder.host_slab(mixed[0], a[0].contiguous(), b[0], steps=self.period)
+        for i in range(self.period):
+            hv[i][0].copy_(mixed[i]); hv[i][1].copy_(a[i]); hv[i][2].copy_(b[i])
+        self.h_mixed, self.h_a, self.h_b = [v[0] for v in hv], [v[1] for v in hv], [v[2] for v in hv]
         self.mixed, self.a, self.b = mixed.to(device), a.contiguous().to(device), b.to(device)
         self.A_log, self.dtb = A_log.to(device), dtb.to(device)
         self.out = torch.zeros(B, HV, V, dtype=torch.bfloat16, device=device)
         self.h_out = torch.zeros(B, HV, V, dtype=torch.bfloat16).pin_memory()
-        from leapquant_b200.host_io import HostStagedDecoder
         self.staged = HostStagedDecoder(self.st, self.ssm, self.A_log, self.dtb, self.idx, self.h_mixed[0], self.h_a[0],
                                         self.h_b[0], self.h_out)
 
@@ -247,7 +251,7 @@ class Layer:
                   st.hcnt, v["sq16"], v["uq"], st.Q0, self.idx)
 
     def h2d_bytes(self):
-        return sum(t[0].numel() * t.element_size() for t in (self.h_mixed, self.h_a, self.h_b))
+        return sum(t[0].numel() * t[0].element_size() for t in (self.h_mixed, self.h_a, self.h_b))
 
     def d2h_bytes(self):
         return self.h_out.numel() * self.h_out.element_size()

@@ -508,8 +508,17 @@ def test_host_staged_decode_equals_direct():
     hm, ha, hb = mixed.pin_memory(), a.contiguous().pin_memory(), b_.pin_memory()
     h_out = torch.zeros(T, N, HV, V, dtype=torch.bfloat16).pin_memory()
     dec = HostStagedDecoder(gpu_h.st, gpu_h.ssm, A_log, dtb, idx, hm[0], ha[0], hb[0], h_out[0])
+    # the first half of the steps from separate pinned tensors (three copies per step), the second half from a slab that
+    # holds a step's inputs back to back (one copy per step)
+    slab, views = HostStagedDecoder.host_slab(hm[0], ha[0], hb[0], steps=T)
     for t in range(T):
-        dec.submit(hm[t], ha[t], hb[t], h_out[t])
+        views[t][0].copy_(hm[t]); views[t][1].copy_(ha[t]); views[t][2].copy_(hb[t])
+    for t in range(T):
+        if t < T // 2:
+            dec.submit(hm[t], ha[t], hb[t], h_out[t])
+        else:
+            assert dec._slab_of(*views[t]) is not None
+            dec.submit(views[t][0], views[t][1], views[t][2], h_out[t])
     dec.drain()
     o = torch.zeros(N, HV, V, dtype=torch.bfloat16, device="cuda")
     for t in range(T):
