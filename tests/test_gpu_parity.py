@@ -449,6 +449,51 @@ def test_decode_free_running(kda, L, R, steps, step_impl):
     assert float((full - S).abs().max() / S.abs().max()) < 3e-2
 
 
+def test_config0_prefill_then_512_decode_steps():
+    """BASELINE's CPU-runnable configuration: one sequence, 16 key = 16 value heads, L = 64, R = 4.  1 024 tokens through the
+    fp32 delta rule build the state, it is quantised, then 512 decode steps run on the 8-bit state: outputs against the
+    oracle (same arithmetic) and against the unquantised fp32 recurrence (the accuracy the method claims)."""
+    NS, HV, H, L, R, N, PRE, T = 3, 16, 16, 64, 4, 1, 1024, 512
+    mixed, a, b_, A_log, dtb = step_inputs(N, H, HV, PRE + T, 31, False)
+    S = torch.zeros(N, HV, V, K)
+
+    def fp32_step(t):
+        m = mixed[t].float()
+        q = m[:, :H * K].view(N, H, K)
+        k = m[:, H * K:2 * H * K].view(N, H, K)
+        vv = m[:, 2 * H * K:].view(N, HV, V)
+        beta = torch.sigmoid(b_[t].float()).bfloat16().float()
+        alpha = torch.exp(-torch.nn.functional.softplus(a[t].float()))
+        return O.fp32_gdn_recurrence(S, q, k, vv, alpha, beta)
+
+    for t in range(PRE):
+        fp32_step(t)
+    cpu = CpuSide(NS, HV, H, K, V, L, R)
+    cpu.ssm[1].copy_(S[0])
+    idx = torch.tensor([1], dtype=torch.int32)
+    cpu.quantize(idx)
+    gpu = GpuSide(cpu)
+    o_c = torch.zeros(N, HV, V, dtype=torch.bfloat16)
+    o_g = torch.zeros(N, HV, V, dtype=torch.bfloat16, device="cuda")
+    A_g, d_g, i_g = A_log.cuda(), dtb.cuda(), idx.cuda()
+    worst_oracle, worst_fp32, sq_err, sq_ref = 0.0, 0.0, 0.0, 0.0
+    for t in range(PRE, PRE + T):
+        cpu.decode(mixed[t], a[t], b_[t], A_log, dtb, idx, o_c)
+        gpu.st.decode(gpu.ssm, mixed[t].cuda(), a[t].cuda(), b_[t].cuda(), A_g, d_g, i_g, o_g)
+        ref = fp32_step(t)
+        scale = float(ref.abs().max())
+        og = o_g.cpu().float()
+        worst_oracle = max(worst_oracle, float((og - o_c.float()).abs().max()) / scale)
+        worst_fp32 = max(worst_fp32, float((og - ref).abs().max()) / scale)
+        sq_err += float(((og - ref) ** 2).sum()); sq_ref += float((ref ** 2).sum())
+    assert torch.equal(gpu.st.hcnt.cpu(), cpu.bufs.hcnt) and int(gpu.st.hcnt[1, 0]) == T % L
+    assert worst_oracle < 2e-2, worst_oracle
+    assert worst_fp32 < 3e-2, worst_fp32
+    assert (sq_err / sq_ref) ** 0.5 < 1e-2, (sq_err / sq_ref) ** 0.5         # relative RMS error of the outputs over the run
+    full = gpu.full_state(idx)
+    assert float((full - S).abs().max() / S.abs().max()) < 3e-2
+
+
 def test_sharded_equals_unsharded():
     """Sequences split over two state objects (as over two GPUs) give bit-identical results to one object."""
     NS, HV, H, L, R, N = 9, 4, 2, 16, 4, 8
