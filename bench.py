@@ -366,6 +366,12 @@ def run_b200(args, wl):
             layer.flush_only()
 
     flush_idle_ms = 1e3 * timed(body_f, torch.cuda.current_stream()) / 20
+    # ---- the prefill round trip: dequantize every slot to fp32, quantize it again (65 536 B fp32 + the checkpoint per head) ----
+    layer.st.dequantize(layer.ssm, layer.idx)
+    layer.st.quantize(layer.ssm, layer.idx)
+    deq_ms = 1e3 * timed(lambda: layer.st.dequantize(layer.ssm, layer.idx), torch.cuda.current_stream())
+    quant_ms = 1e3 * timed(lambda: layer.st.quantize(layer.ssm, layer.idx), torch.cuda.current_stream())
+    rt_bytes = B * HV * (4 * V * K + K * V + 4 * (K + V) + 2 * R * (K + V))
     alg_launch = B * HV * sum(step_bytes(h, L, R, gqa, kda) for h in range(L)) / L
     peaks = {}
     try:
@@ -404,6 +410,9 @@ def run_b200(args, wl):
                              "ms_per_launch": step_ms, "peak_source": "MEASURED_PEAKS.json" if peaks else "fallback"},
                 "flush": {"all_due_ms": flush_all_ms, "none_due_ms": flush_idle_ms,
                           "all_due_gbs": B * HV * flush_bytes(L, R, kda) / (flush_all_ms * 1e-3) / 1e9},
+                "prefill_round_trip": {"dequantize_ms": deq_ms, "quantize_ms": quant_ms,
+                                       "dequantize_gbs": rt_bytes / (deq_ms * 1e-3) / 1e9,
+                                       "quantize_gbs": rt_bytes / (quant_ms * 1e-3) / 1e9},
                 "clocks": clocks}
         if cpu_rate is not None:
             line["cpu_baseline"] = {"value": cpu_rate, "unit": "head-steps/s", "cores": os.cpu_count() or 1, "kind": "port",
