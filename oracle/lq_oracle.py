@@ -630,7 +630,7 @@ def fp32_kda_recurrence(S, q, k, v, alpha, beta, scale=None):
 
 
 # --------------------------------------------------------------------------------------------------------------
-# synthetic workloads (the seeded distributions BASELINE.json's configs name)
+# synthetic workloads (the seeded distributions of the benchmark configurations)
 # --------------------------------------------------------------------------------------------------------------
 def synth_inputs(N, H, HV, K, V, steps, seed, kda=False, dtype=torch.bfloat16):
     """q, k ~ N(0,1) l2-normalised per head, v ~ N(0,1), b ~ N(0,1) (beta = sigmoid b), a ~ N(0,1) with A_log = 0 and

@@ -24,7 +24,7 @@ def make_pair(NS, HV, H, L, R, kda=False, glb=0.0, seed=0, scale=0.1, slot_pad=0
 
 
 def step_inputs(N, H, HV, steps, seed, kda, gate_shift=0.0):
-    """BASELINE's seeded distributions; gate_shift > 0 moves the raw gate down so that the per-step decay is mild
+    """The benchmark's seeded distributions; gate_shift > 0 moves the raw gate down so that the per-step decay is mild
     (alpha close to 1) and the state keeps a well-conditioned spectrum over a whole window."""
     mixed, a, b, A_log, dtb = O.synth_inputs(N, H, HV, K, V, steps, seed, kda=kda)
     if gate_shift:
@@ -366,7 +366,7 @@ def check_flush(cpu, gpu, idx, slots, what, code_tol=5e-3, code_frac=0.002, stri
 @pytest.mark.parametrize("gate_shift", [4.0, 0.0], ids=["mild_decay", "baseline_decay"])
 def test_flush_against_oracle(kda, L, R, gate_shift):
     """gate_shift = 4: alpha ~ 0.98 per step, the state stays full rank and the factors are well defined -> strict factor
-    parity.  gate_shift = 0 is BASELINE's distribution (alpha ~ 0.5 per step): after a window the state is the last few
+    parity.  gate_shift = 0 is the benchmark's distribution (alpha ~ 0.5 per step): after a window the state is the last few
     tokens only, numerically rank deficient, and only the fit quality, the stage-wise codes and the state are compared."""
     NS, HV, H = 5, 4, 2
     cpu, gpu = make_pair(NS, HV, H, L, R, kda=kda, seed=2)
@@ -450,7 +450,7 @@ def test_decode_free_running(kda, L, R, steps, step_impl):
 
 
 def test_config0_prefill_then_512_decode_steps():
-    """BASELINE's CPU-runnable configuration: one sequence, 16 key = 16 value heads, L = 64, R = 4.  1 024 tokens through the
+    """The benchmark's CPU-runnable configuration: one sequence, 16 key = 16 value heads, L = 64, R = 4.  1 024 tokens through the
     fp32 delta rule build the state, it is quantised, then 512 decode steps run on the 8-bit state: outputs against the
     oracle (same arithmetic) and against the unquantised fp32 recurrence (the accuracy the method claims)."""
     NS, HV, H, L, R, N, PRE, T = 3, 16, 16, 64, 4, 1, 1024, 512
