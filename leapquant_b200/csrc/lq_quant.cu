@@ -154,6 +154,8 @@ dequant_kernel(lq_dims d, char* __restrict__ ssm, const uint16_t* __restrict__ K
     float* Qo = Uo + R * 128;                             // [R][128]
     float* Kf = Qo + R * 128;                             // [L][128] keys (KDA: decayed)
     float* Uf = Kf + d.L * 128;                           // [L][128] w_j u_j
+    float* lut = Uf + d.L * 128;                          // [256] code / 127, indexed by code + 128: the IEEE division the
+                                                          // reference's expression asks for, done 256 times per CTA instead of 16 384
     const int tid = threadIdx.x;
     const int n = blockIdx.x / d.HV, hv = blockIdx.x % d.HV;
     const int slot = idx[n];
@@ -165,6 +167,7 @@ dequant_kernel(lq_dims d, char* __restrict__ ssm, const uint16_t* __restrict__ K
 
     for (int i = tid; i < 4096 / 4; i += NT_LA)
         reinterpret_cast<uint4*>(cw)[i] = reinterpret_cast<const uint4*>(base + CK_CODES)[i];
+    lut[tid] = float(tid - 128) / QMAX;
     if (tid < 128) {
         sk[tid] = reinterpret_cast<const float*>(base + CK_SK)[tid];
         sv[tid] = reinterpret_cast<const float*>(base + CK_SV)[tid];
@@ -206,11 +209,11 @@ dequant_kernel(lq_dims d, char* __restrict__ ssm, const uint16_t* __restrict__ K
 #pragma unroll
         for (int i = 0; i < 8; ++i) {
             const float svv = sv[v0 + i];
-            float f[8];
-            s8x4_to_f4(cw[(v0 + i) * 32 + tx], f[0], f[1], f[2], f[3]);
-            s8x4_to_f4(cw[(v0 + i) * 32 + 16 + tx], f[4], f[5], f[6], f[7]);
+            const uint32_t wa = cw[(v0 + i) * 32 + tx] ^ 0x80808080u, wb = cw[(v0 + i) * 32 + 16 + tx] ^ 0x80808080u;
+            const float f[8] = {lut[wa & 255u], lut[(wa >> 8) & 255u], lut[(wa >> 16) & 255u], lut[wa >> 24],
+                                lut[wb & 255u], lut[(wb >> 8) & 255u], lut[(wb >> 16) & 255u], lut[wb >> 24]};
 #pragma unroll
-            for (int k = 0; k < 8; ++k) acc[i][k] = (f[k] / QMAX) * skl[k] * svv;
+            for (int k = 0; k < 8; ++k) acc[i][k] = f[k] * skl[k] * svv;
         }
 #pragma unroll
         for (int r = 0; r < R; ++r) {
@@ -332,7 +335,7 @@ extern "C" int lq_dequant(const lq_dims* d, void* ssm, const void* Kbuf, const v
     if (!ssm || !Kbuf || !Ubuf || !Wbuf || !Pbuf || !hcnt || (N > 0 && !idx) || (kda && !Gbuf)) return LQ_ERR_NULL;
     if (N < 0) return LQ_ERR_RANGE;
     if (N == 0) return LQ_OK;
-    const size_t smem = sizeof(float) * (4096 + 3 * 128 + 2 * d->R * 128 + 2 * d->L * 128);
+    const size_t smem = sizeof(float) * (4096 + 3 * 128 + 2 * d->R * 128 + 2 * d->L * 128 + 256);
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     dim3 grid(unsigned(N) * d->HV), block(NT_LA);
     if (d->R == 4) {
