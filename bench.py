@@ -35,7 +35,7 @@ WORKLOADS = {
 # DRAM bytes (read + write) of the step kernel relative to its algorithmic bytes, from the ncu capture summarised in
 # profiles/step_pipelined_gdn_B128_ncu.md (150.05 MB + 5.40 MB for 4 096 programs at h = 33 vs 37 928 B algorithmic per
 # program).  `roofline.traffic` scales the live algorithmic bytes per launch by this ratio.  None = not captured.
-NCU_TRAFFIC_RATIO = {"gdn": 1.018, "kda": None}
+NCU_TRAFFIC_RATIO = {"gdn": 1.01, "kda": None}
 
 
 def step_bytes(h, L, R, gqa, kda):
