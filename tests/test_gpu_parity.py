@@ -514,7 +514,8 @@ def test_sharded_equals_unsharded():
     assert torch.equal(bits(gpu_all.ssm[1:5]), bits(gpu_a.ssm[1:5])) and torch.equal(bits(gpu_all.ssm[5:9]), bits(gpu_b.ssm[5:9]))
 
 
-@pytest.mark.parametrize("kda,L,R,H,HV", [(False, 16, 4, 2, 4), (False, 64, 4, 1, 2), (True, 16, 4, 2, 2), (True, 32, 8, 2, 2)])
+@pytest.mark.parametrize("kda,L,R,H,HV", [(False, 16, 4, 2, 4), (False, 64, 4, 1, 2), (True, 16, 4, 2, 2), (True, 32, 8, 2, 2),
+                                          (False, 64, 8, 1, 2), (True, 64, 8, 2, 2)])     # the last one has room for one flush team only
 def test_fused_decode_equals_step_then_flush(kda, L, R, H, HV):
     """One fused launch per token gives bit-identical outputs, window buffers and packed state to the step kernel followed
     by the flush kernel, over more than two windows and with rows whose windows fill at different steps."""
