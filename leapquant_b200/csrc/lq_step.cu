@@ -491,19 +491,6 @@ __device__ __forceinline__ void step_body(const StepParams& P, const ProgScalars
     refill();
     LQ_PSTAMP(1);
 
-    // ---- k_hat, q_hat of this lane's 16 columns ----
-    float2 kn[8], qn[8];
-    {
-        const float4* kp = reinterpret_cast<const float4*>(nrm);
-        const float4* qp = reinterpret_cast<const float4*>(nrm + 128);
-#pragma unroll
-        for (int i = 0; i < 4; ++i) {
-            const float4 a = kp[nrm_chunk(l8 * 4 + i)], b = qp[nrm_chunk(l8 * 4 + i)];
-            kn[2 * i] = make_float2(a.x, a.y); kn[2 * i + 1] = make_float2(a.z, a.w);
-            qn[2 * i] = make_float2(b.x, b.y); qn[2 * i + 1] = make_float2(b.z, b.w);
-        }
-    }
-
     // ---- window dots dk_j = K_j . k_hat, dq_j = K_j . q_hat on the tensor cores: D[j][n] = sum_c K_j[c] B[c][n] with
     //      n = {k head, k remainder, q head, q remainder} (bf16, fp32 accumulate).  Sixteen rows per m16 tile, tiles dealt
     //      round-robin to the warps; lane (gid, tig) reads rows gid and gid + 8 as four 16-byte chunks at 64 c + 16 tig, so
@@ -552,6 +539,18 @@ __device__ __forceinline__ void step_body(const StepParams& P, const ProgScalars
 #pragma unroll
     for (int cr = 0; cr < R / 4; ++cr) {
         if (((((h + 15) >> 4) + cr) % GW) == w) {
+            // k_hat, q_hat (fp32) of this lane's 16 columns: only the warp that takes this chunk of factor rows reads them
+            float2 kn[8], qn[8];
+            {
+                const float4* kp = reinterpret_cast<const float4*>(nrm);
+                const float4* qp = reinterpret_cast<const float4*>(nrm + 128);
+#pragma unroll
+                for (int i = 0; i < 4; ++i) {
+                    const float4 a = kp[nrm_chunk(l8 * 4 + i)], b = qp[nrm_chunk(l8 * 4 + i)];
+                    kn[2 * i] = make_float2(a.x, a.y); kn[2 * i + 1] = make_float2(a.z, a.w);
+                    qn[2 * i] = make_float2(b.x, b.y); qn[2 * i + 1] = make_float2(b.z, b.w);
+                }
+            }
             const int r = 4 * cr + g;
             const uint4 r0 = reinterpret_cast<const uint4*>(st + CK_UQ + r * 512)[l8 * 2];
             const uint4 r1 = reinterpret_cast<const uint4*>(st + CK_UQ + r * 512)[l8 * 2 + 1];
