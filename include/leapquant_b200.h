@@ -59,7 +59,9 @@ int lq_last_cuda_error(void);
  * the device: debugging / tests only.  No reference counterpart. */
 int lq_device_status(int* status);
 
-/* Tuning / debugging switch, process-wide; no reference counterpart.  "step_impl": 0 = persistent CTAs fed by bulk
+/* Tuning / debugging switch; no reference counterpart.  The setting is process-wide (it applies to every layer and every
+ * later call in the process, not to one call), stored atomically, and read once per launch: it may be set from any
+ * thread, but calls already in progress on other threads may still use the previous value.  "step_impl": 0 = persistent CTAs fed by bulk
  * asynchronous copies (default), 1 = one CTA per (row, head) with plain loads and the same arithmetic, 2 = one warp per
  * (row, head) in registers (GDN only; KDA keeps the default).  1 and 2 exist for debugging and comparison.
  * "pdl": 1 (default) launches the step and flush kernels with programmatic stream serialisation, so that the launch and
@@ -88,7 +90,8 @@ int lq_kda_step(const lq_dims* d, void* ssm, void* Kbuf, void* Ubuf, float* Wbuf
  * signature :1139-1148).  For every (idx[n] > 0, hv) with hcnt == L: rebuilds the state from checkpoint + window,
  * extracts R new Compensator Tokens by `iters` rounds of subspace iteration from Q0 (f32 [V,R]) with CholeskyQR2,
  * recomputes Sk / Sv, requantises the residual to INT8 and resets the window.  Due heads are found on the device;
- * the launch shape does not depend on how many are due.  kda != 0 selects the per-channel-gate variant (Gbuf used). */
+ * the launch shape does not depend on how many are due.  (Row n, head hv) is handled by CTA (n * HV + hv) % grid, which
+ * reads that head's counter once: no CTA depends on what another one reads or resets, nor on all CTAs being resident.  kda != 0 selects the per-channel-gate variant (Gbuf used). */
 int lq_flush(const lq_dims* d, void* ssm, void* Kbuf, void* Ubuf, float* Wbuf, float* Pbuf, void* Gbuf,
              int32_t* hcnt, const float* Q0, const int32_t* idx, int32_t N, int32_t kda, int32_t iters, void* stream);
 
@@ -96,8 +99,8 @@ int lq_flush(const lq_dims* d, void* ssm, void* Kbuf, void* Ubuf, float* Wbuf, f
  * launches of LeapQuantState.decode (reference leapquant/state.py:99-116): the persistent CTA that fills a head's window
  * flushes that head itself after its last program, so the flush needs no due scan, no second launch and finds the
  * head's window rows in cache.  Same arguments as the step plus the flush's Q0 and iters; same results as the two calls.
- * Where the fused form is not available (a debug step driver is selected, or the flush working set does not fit beside
- * nothing in shared memory) the two kernels are launched one after the other. */
+ * Where the fused form is not available (a debug step driver is selected, or the working set of one flush team does not
+ * fit in the shared memory the step pipeline leaves behind) the two kernels are launched one after the other. */
 int lq_gdn_decode(const lq_dims* d, void* ssm, void* Kbuf, void* Ubuf, float* Wbuf, float* Pbuf, int32_t* hcnt,
                   const void* mixed, const void* a, const void* b, const float* A_log, const float* dt_bias,
                   const int32_t* idx, void* o, int32_t N, float scale, const float* Q0, int32_t iters, void* stream);

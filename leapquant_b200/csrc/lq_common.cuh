@@ -5,6 +5,9 @@
 #include <cuda_fp16.h>
 #include <stdint.h>
 
+#include <atomic>
+#include <initializer_list>
+
 #include "../../include/leapquant_b200.h"
 
 namespace lq {
@@ -125,13 +128,19 @@ __device__ __forceinline__ uint4 ldg_stream(const void* p) {
 int device_sm_count();
 int ensure_smem(const void* func, size_t bytes);
 int check_dims(const lq_dims* d);
+// true if any of the (non-null) pointers is not 16-byte aligned: the kernels read and write them with 128-bit accesses
+inline bool misaligned16(std::initializer_list<const void*> ptrs) {
+    uintptr_t acc = 0;
+    for (const void* p : ptrs) acc |= reinterpret_cast<uintptr_t>(p);
+    return (acc & 15) != 0;
+}
 void set_last_cuda_error(cudaError_t e);
 
 // Programmatic dependent launch.  The decode path is a chain of short kernels on one stream (step, flush, step, ...); a
 // kernel launched with this attribute may be scheduled while its predecessor is still draining, runs its set-up
 // (shared-memory carve, barrier initialisation) and then blocks in pdl_wait() until the predecessor has completed and its
 // writes are visible.  Every kernel launched this way calls pdl_trigger() and pdl_wait() before it touches global memory.
-static int g_pdl = 1;
+static std::atomic<int> g_pdl{1};       // set by lq_set_option from any thread, read by every launch
 __device__ __forceinline__ void pdl_trigger() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
 __device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
 template <typename... KArgs, typename... Args>
@@ -145,7 +154,7 @@ inline cudaError_t launch_dependent(void (*kern)(KArgs...), unsigned grid, unsig
     at[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
     at[0].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = at;
-    cfg.numAttrs = g_pdl ? 1 : 0;
+    cfg.numAttrs = g_pdl.load(std::memory_order_relaxed) ? 1 : 0;
     return cudaLaunchKernelEx(&cfg, kern, KArgs(args)...);
 }
 inline int finish_launch() {

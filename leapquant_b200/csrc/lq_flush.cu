@@ -1,8 +1,8 @@
 // Window-flush kernel (sm_100a): rebuild -> rank-R subspace iteration -> residual -> smoothing scales -> INT8.
 //
-// Persistent CTAs of 256 threads, two per SM.  Every CTA scans the due flags of all (row, head) programs of the call,
-// ranks the due ones in a fixed order and keeps the ranks congruent to its block index, so the work is balanced to +-1
-// head per CTA whatever the pattern of full windows, and the launch shape never depends on device data.
+// Persistent CTAs of 256 threads, two per SM.  Program p = row * HV + head belongs to CTA p % grid; a CTA tests the window
+// counters of its own programs and flushes the due ones, so the launch shape never depends on device data and no CTA
+// relies on what another one reads or resets.
 //
 // All matrix products of a head run on the tensor cores (mma.sync m16n8k16, fp32 accumulate): the window product that
 // rebuilds the state B (bf16 operands, the scaled one as head + remainder), the tall-skinny products of the subspace
@@ -195,16 +195,9 @@ __device__ __forceinline__ void flush_init(const FlushSmem& s, const float* Q0, 
     for (int i = tid; i < 128 * R; i += NT_LA) s.Q0h[(i % R) * HS + i / R] = f_to_f16(Q0[i]);
 }
 
-#ifdef LQ_TRACE
-#define LQ_FSTAMP(k) do { if (tid == 0) { const long long tn = clock64(); facc[k] += tn - flast; flast = tn; } } while (0)
-#else
-#define LQ_FSTAMP(k) do { } while (0)
-#endif
-
 // The flush of head q = slot * HV + hv by a team of 256 threads (tid 0 .. 255); sync() is the team's barrier.
 template <int R, bool KDA, typename Sync>
-__device__ __forceinline__ void flush_head(const FlushSmem& s, const FlushArgs& A, int q, int tid, Sync sync, long long* facc,
-                                           long long& flast) {
+__device__ __forceinline__ void flush_head(const FlushSmem& s, const FlushArgs& A, int q, int tid, Sync sync) {
     constexpr int KC = FlushK<R>::KC, KS = FlushK<R>::KS;
     const lq_dims& d = A.d;
     char* ssm = A.ssm;
@@ -217,7 +210,6 @@ __device__ __forceinline__ void flush_head(const FlushSmem& s, const FlushArgs& 
     const int iters = A.iters;
     const int L = d.L, HV = d.HV, Lp = flush_lp(d.L);
     const int warp = tid >> 5, lane = tid & 31, gid = lane >> 2, tig = lane & 3;
-    LQ_FSTAMP(0);
     const int slot = q / HV, hv = q - slot * HV;
     const int64_t sh = q;
     char* base = head_base(ssm, d.SS, slot, hv);
@@ -273,7 +265,6 @@ __device__ __forceinline__ void flush_head(const FlushSmem& s, const FlushArgs& 
             s.UoT[c * 8 + r] = uu;
             s.QoT[c * 8 + r] = fq[u];
         }
-        LQ_FSTAMP(1);
         // window rows as stored (bf16), 16 bytes at a time into the padded tiles; rows L .. Lp-1 are zero
 #pragma unroll
         for (int u = 0; u < NTC; ++u) {
@@ -297,7 +288,6 @@ __device__ __forceinline__ void flush_head(const FlushSmem& s, const FlushArgs& 
     }
     if (KDA) sync();
 
-    LQ_FSTAMP(2);
     // ---- stage B: B = deq(checkpoint) * decay + sum_j (w_j u_j) k_j^T on the tensor cores (mma.sync bf16, fp32 accumulate).
     //      The operand that carries an fp32 scale (GDN: w_j u_j[v]; KDA: w_j D_j[c] k_j[c]) is the A operand, built in
     //      registers as two bf16 pieces (hi + lo, 16 mantissa bits); the other one is bf16 as stored and comes
@@ -329,7 +319,6 @@ __device__ __forceinline__ void flush_head(const FlushSmem& s, const FlushArgs& 
             }
             cpre[nt] = pk;
         }
-        LQ_FSTAMP(14);
         for (int ks = 0; ks < Lp; ks += 16) {
             uint32_t ah[4], al[4];
 #pragma unroll
@@ -362,7 +351,6 @@ __device__ __forceinline__ void flush_head(const FlushSmem& s, const FlushArgs& 
                 mma_bf16_16816(acc[2 * np + 1], al, bf[2], bf[3]);
             }
         }
-        LQ_FSTAMP(13);
         // add the dequantised checkpoint and store B[v][c] as f16; accumulator (e, nt): row m0 + r + 8 (e >> 1), col 8 nt + q2 + (e & 1)
         const float pq = KDA ? (1.0f / QMAX) : (p / QMAX);
 #pragma unroll
@@ -386,8 +374,6 @@ __device__ __forceinline__ void flush_head(const FlushSmem& s, const FlushArgs& 
         }
     }
     sync();                                        // the window tiles are dead: the region may be reused
-    LQ_FSTAMP(3);
-    LQ_FSTAMP(4);
     // ---- stage C: subspace iteration on T = B + p Q_old U_old^T ----
     const int m0w = warp * 16;
     float dd[4] = {0.f, 0.f, 0.f, 0.f};
@@ -402,7 +388,6 @@ __device__ __forceinline__ void flush_head(const FlushSmem& s, const FlushArgs& 
     tall_product<R, true>(s.Bh, s.Q0h, s.Qoh, s.UoT, p, warp, lane, dd);        // P = T^T Q0
     store_p();
     sync();
-    LQ_FSTAMP(5);
     if (iters == 0) {                                       // no round: the stored Q is the start itself
         for (int i = tid; i < R * HS; i += NT_LA) s.Qh[i] = s.Q0h[i];
         sync();
@@ -414,17 +399,14 @@ __device__ __forceinline__ void flush_head(const FlushSmem& s, const FlushArgs& 
             *reinterpret_cast<float2*>(s.Qn + (m0w + gid + 8) * R + 2 * tig) = make_float2(dd[2], dd[3]);
         }
         sync();
-        LQ_FSTAMP(6);
         cholqr2_f16<R>(s.Qn, tid, sync);
         for (int i = tid; i < 128 * R; i += NT_LA) s.Qh[(i % R) * HS + i / R] = f_to_f16(s.Qn[i]);
         sync();
-        LQ_FSTAMP(7);
         tall_product<R, true>(s.Bh, s.Qh, s.Qoh, s.UoT, p, warp, lane, dd);     // P = T^T Q
         store_p();
         sync();
     }
 
-    LQ_FSTAMP(8);
     // ---- stage D: new factors to the checkpoint (16-byte copies of the f16 rows); operands of the residual ----
     if (tid < R * 32) {
         const int r = tid >> 5, j = tid & 31;
@@ -456,7 +438,6 @@ __device__ __forceinline__ void flush_head(const FlushSmem& s, const FlushArgs& 
     }
     sync();
 
-    LQ_FSTAMP(9);
     // ---- stage E: residual E = B + p Q_old U_old^T - Q U^T on the tensor cores, fp32 in registers: warp w owns rows
     //      16 w .. 16 w + 15, lane (gid, tig) holds rows gid, gid + 8 at columns 8 nt + 2 tig, + 1 ----
     float e[16][4];
@@ -511,7 +492,6 @@ __device__ __forceinline__ void flush_head(const FlushSmem& s, const FlushArgs& 
     }
     sync();
 
-    LQ_FSTAMP(10);
     // ---- stage F: row scales and INT8 codes, staged in the warp's own rows of the (dead) state tile ----
     {
         float r0 = 0.f, r1 = 0.f;
@@ -546,7 +526,6 @@ __device__ __forceinline__ void flush_head(const FlushSmem& s, const FlushArgs& 
 #pragma unroll
         for (int i = 0; i < 4; ++i) dst[i] = src[i];
     }
-    LQ_FSTAMP(11);
     // ---- stage G: window reset ----
     if (tid < L) Wbuf[sh * L + tid] = 0.f;
     if (KDA) {
@@ -558,12 +537,7 @@ __device__ __forceinline__ void flush_head(const FlushSmem& s, const FlushArgs& 
     }
     if (tid == 0) hcnt[sh] = 0;
     sync();
-    LQ_FSTAMP(12);
 }
-
-#ifdef LQ_TRACE
-static __device__ long long g_ftrace[320 * 16];
-#endif
 
 template <int R, bool KDA>
 __global__ void __launch_bounds__(NT_LA, 2)
@@ -577,75 +551,43 @@ flush_kernel(lq_dims d, char* ssm, const uint16_t* Kbuf, const uint16_t* Ubuf, f
     pdl_trigger();
     pdl_wait();                                                  // the scan reads the counters the step kernel just wrote
 
-    // ---------------- balanced compaction of the due programs ----------------
+    // ---------------- the due programs of this CTA ----------------
+    // Program p = n * HV + hv belongs to CTA p % G, whatever the state of the windows: a CTA tests only its own programs and
+    // reads each counter once, so the assignment does not depend on counters that other CTAs reset while they work, nor
+    // on all CTAs being resident at the same time.  Warp 0 compacts the due ones in program order.
     const int total = N * HV;
-    const int per_warp = ((total + 7) / 8 + 31) & ~31;
-    const int wbeg = warp * per_warp, wend = min(wbeg + per_warp, total);
-    auto due_at = [&](int i, int& q) -> bool {
-        if (i >= wend) return false;
-        const int n = i / HV, hv = i - n * HV;
-        const int slot = idx[n];
-        if (slot <= 0 || slot >= d.NS) return false;
-        q = slot * HV + hv;
-        return hcnt[q] == L;
-    };
-    // counting pass, 16 flags per lane in flight: all slot loads, then all counter loads, then the ballots
-    // (a loop of dependent load pairs made a launch that finds nothing due cost ~10 us)
-    int cnt = 0;
-    constexpr int UN = 16;
-    for (int b0 = wbeg; b0 < wend; b0 += 32 * UN) {
-        int sl[UN], hc[UN];
-#pragma unroll
-        for (int u = 0; u < UN; ++u) {
-            const int i = b0 + 32 * u + lane;
-            sl[u] = (i < wend) ? idx[i / HV] : 0;
-        }
-#pragma unroll
-        for (int u = 0; u < UN; ++u) {
-            const int i = b0 + 32 * u + lane;
-            const bool ok = sl[u] > 0 && sl[u] < d.NS;
-            hc[u] = ok ? hcnt[sl[u] * HV + (i % HV)] : -1;
-        }
-#pragma unroll
-        for (int u = 0; u < UN; ++u) cnt += __popc(__ballot_sync(0xffffffffu, hc[u] == L));
-    }
-    if (lane == 0) s.wcnt[warp] = cnt;
-    __syncthreads();
-    int rank = 0, ndue = 0;
-#pragma unroll
-    for (int w2 = 0; w2 < 8; ++w2) {
-        const int c2 = s.wcnt[w2];
-        rank += (w2 < warp) ? c2 : 0;
-        ndue += c2;
-    }
-    if (ndue == 0) return;
-    if (cnt > 0) {
+    const int nmine = (total > bid) ? (total - bid + G - 1) / G : 0;
+    if (warp == 0) {
+        int base = 0;
         const uint32_t lt = (1u << lane) - 1u;
-        for (int b0 = wbeg; b0 < wend; b0 += 32) {
+        for (int b0 = 0; b0 < nmine; b0 += 32) {
+            const int i = b0 + lane;
             int q = 0;
-            const bool f = due_at(b0 + lane, q);
+            bool f = false;
+            if (i < nmine) {
+                const int pgm = bid + i * G;
+                const int n = pgm / HV, hv = pgm - n * HV;
+                const int slot = idx[n];
+                if (slot > 0 && slot < d.NS) {
+                    q = slot * HV + hv;
+                    f = hcnt[q] == L;
+                }
+            }
             const uint32_t m = __ballot_sync(0xffffffffu, f);
-            const int r = rank + __popc(m & lt);
-            if (f && (r % G) == bid && (r / G) < maxd) s.dlist[r / G] = q;
-            rank += __popc(m);
+            if (f) s.dlist[base + __popc(m & lt)] = q;
+            base += __popc(m);
         }
+        if (lane == 0) s.wcnt[0] = base;
     }
-    const int mine = (ndue > bid) ? min((ndue - bid + G - 1) / G, maxd) : 0;
     __syncthreads();
+    const int mine = min(s.wcnt[0], maxd);
+    if (mine == 0) return;
 
     flush_init<R>(s, Q0, tid);
     FlushArgs A;
     A.d = d; A.ssm = ssm; A.Kbuf = Kbuf; A.Ubuf = Ubuf; A.Wbuf = Wbuf; A.Pbuf = Pbuf; A.Gbuf = Gbuf; A.hcnt = hcnt; A.Q0 = Q0;
     A.iters = iters;
-    long long facc[16] = {0}, flast = 0;
-#ifdef LQ_TRACE
-    flast = clock64();
-#endif
-    for (int k = 0; k < mine; ++k) flush_head<R, KDA>(s, A, s.dlist[k], tid, [] { __syncthreads(); }, facc, flast);
-#ifdef LQ_TRACE
-    if (tid == 0 && blockIdx.x < 320) for (int i = 0; i < 16; ++i) g_ftrace[blockIdx.x * 16 + i] = facc[i];
-    if (tid == 0 && blockIdx.x < 320) g_ftrace[blockIdx.x * 16 + 15] = mine;
-#endif
+    for (int k = 0; k < mine; ++k) flush_head<R, KDA>(s, A, s.dlist[k], tid, [] { __syncthreads(); });
 }
 
 template <int R, bool KDA>
@@ -676,12 +618,6 @@ static int launch_flush(const lq_dims* d, void* ssm, void* Kbuf, void* Ubuf, flo
 
 using namespace lq;
 
-#ifdef LQ_TRACE
-extern "C" int lq_debug_read_ftrace(long long* out, int n) {
-    return cudaMemcpyFromSymbol(out, lq::g_ftrace, sizeof(long long) * n) == cudaSuccess ? 0 : -5;
-}
-#endif
-
 extern "C" int lq_flush(const lq_dims* d, void* ssm, void* Kbuf, void* Ubuf, float* Wbuf, float* Pbuf, void* Gbuf,
                         int32_t* hcnt, const float* Q0, const int32_t* idx, int32_t N, int32_t kda, int32_t iters,
                         void* stream) {
@@ -689,6 +625,7 @@ extern "C" int lq_flush(const lq_dims* d, void* ssm, void* Kbuf, void* Ubuf, flo
     if (rc) return rc;
     if (!ssm || !Kbuf || !Ubuf || !Wbuf || !Pbuf || !hcnt || !Q0 || (N > 0 && !idx) || (kda && !Gbuf)) return LQ_ERR_NULL;
     if (N < 0 || iters < 0) return LQ_ERR_RANGE;
+    if (misaligned16({ssm, Kbuf, Ubuf, Wbuf}) || (kda && misaligned16({Gbuf, Pbuf}))) return LQ_ERR_ALIGN;
     if (N == 0) return LQ_OK;
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     if (d->R == 4)

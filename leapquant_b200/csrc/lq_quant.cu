@@ -314,6 +314,7 @@ extern "C" int lq_quantize(const lq_dims* d, void* ssm, float* Wbuf, float* Pbuf
     if (rc) return rc;
     if (!ssm || !Wbuf || !Pbuf || !hcnt || !Q0 || (N > 0 && !idx) || (kda && !Gbuf)) return LQ_ERR_NULL;
     if (N < 0 || iters < 0) return LQ_ERR_RANGE;
+    if (misaligned16({ssm}) || (kda && misaligned16({Gbuf}))) return LQ_ERR_ALIGN;
     if (N == 0) return LQ_OK;
     const size_t smem = sizeof(float) * (128 * LDB + 3 * 128 * d->R + 128 + 256);
     cudaStream_t st = static_cast<cudaStream_t>(stream);
@@ -334,6 +335,7 @@ extern "C" int lq_dequant(const lq_dims* d, void* ssm, const void* Kbuf, const v
     if (rc) return rc;
     if (!ssm || !Kbuf || !Ubuf || !Wbuf || !Pbuf || !hcnt || (N > 0 && !idx) || (kda && !Gbuf)) return LQ_ERR_NULL;
     if (N < 0) return LQ_ERR_RANGE;
+    if (misaligned16({ssm, Kbuf, Ubuf})) return LQ_ERR_ALIGN;
     if (N == 0) return LQ_OK;
     const size_t smem = sizeof(float) * (4096 + 3 * 128 + 2 * d->R * 128 + 2 * d->L * 128 + 256);
     cudaStream_t st = static_cast<cudaStream_t>(stream);

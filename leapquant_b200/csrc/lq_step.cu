@@ -190,18 +190,6 @@ __device__ __forceinline__ float pass_transpose_sum(const float (&x)[N], int l8)
     }
 }
 
-#ifdef LQ_TRACE
-static __device__ long long g_qtrace[160 * 256 * 8];
-#define LQ_QSTAMP(k) do { if (i < 256 && blockIdx.x < 160 && lane == 0) g_qtrace[(blockIdx.x * 256 + i) * 8 + (k)] = clock64(); } while (0)
-static __device__ long long g_ntrace[160 * 256 * 8];
-#define LQ_NSTAMP(k) do { if (pi >= 0 && pi < 256 && blockIdx.x < 160 && lane == 0) g_ntrace[(blockIdx.x * 256 + pi) * 8 + (k)] = clock64(); } while (0)
-#define LQ_NSTAMPD(k, dep) do { if (pi >= 0 && pi < 256 && blockIdx.x < 160 && lane == 0) g_ntrace[(blockIdx.x * 256 + pi) * 8 + (k)] = clock64() + (long long)(__float_as_uint(dep) & 0u); } while (0)
-#else
-#define LQ_NSTAMP(k) do { } while (0)
-#define LQ_QSTAMP(k) do { } while (0)
-#define LQ_NSTAMPD(k, dep) do { } while (0)
-#endif
-
 // The four f32[128] vectors the prologue leaves in the stage are read back by eight lanes at a time, lane l8 taking the
 // 64 bytes of its 16 channels as four 16-byte chunks.  Chunk c (0..31) is stored at c with its two low bits XORed by
 // bits 3..4 of c, which spreads the eight lanes of a quarter-warp over all eight 16-byte bank groups.
@@ -238,10 +226,9 @@ __device__ __forceinline__ void mma_f16_16816(float (&d)[4], uint32_t a0, uint32
 // `signal()` is called after the last shared-memory write and BEFORE the global stores (see step_body's `release`).
 template <bool KDA, typename Signal>
 __device__ __forceinline__ void step_prologue(const StepParams& P, const ProgScalars& sc, char* st, const StageLayout& lay,
-                                              int lane, Signal signal, int pi = -1, bool qk_regs = false,
+                                              int lane, Signal signal, bool qk_regs = false,
                                               uint2 q_in = make_uint2(0u, 0u), uint2 k_in = make_uint2(0u, 0u)) {
     const int L = P.d.L, h = sc.h;
-    LQ_NSTAMP(0);
     const int64_t sh = int64_t(sc.slot) * P.d.HV + sc.hv;
     const uint2 qw = qk_regs ? q_in : reinterpret_cast<const uint2*>(st + lay.q)[lane];      // this lane's four channels of q
     const uint2 kw = qk_regs ? k_in : reinterpret_cast<const uint2*>(st + lay.k)[lane];
@@ -283,7 +270,6 @@ __device__ __forceinline__ void step_prologue(const StepParams& P, const ProgSca
         mk = fmaxf(mk, fabsf(k[i] * s[i]));
         mq = fmaxf(mq, fabsf(q[i] * s[i]));
     }
-    LQ_NSTAMP(1);
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) {
         const float a0 = __shfl_xor_sync(0xffffffffu, sq, o), a1 = __shfl_xor_sync(0xffffffffu, sk, o);
@@ -291,7 +277,6 @@ __device__ __forceinline__ void step_prologue(const StepParams& P, const ProgSca
         const float a4 = __shfl_xor_sync(0xffffffffu, mq, o);
         sq += a0; sk += a1; skq += a2; mk = fmaxf(mk, a3); mq = fmaxf(mq, a4);
     }
-    LQ_NSTAMP(2);
     const float inq = rsqrtf(sq + 1e-6f) * P.scale, ink = rsqrtf(sk + 1e-6f);
 #pragma unroll
     for (int i = 0; i < 4; ++i) {
@@ -343,7 +328,6 @@ __device__ __forceinline__ void step_prologue(const StepParams& P, const ProgSca
         *reinterpret_cast<float*>(st + lay.sc + 32) = skq * inq * ink;
         *reinterpret_cast<uint32_t*>(st + lay.sc + 36) = (254u << 23) - sbits;       // 1 / oscale
     }
-    LQ_NSTAMP(3);
     const uint2 kapp = make_uint2(f2_to_bf16x2(k[0], k[1]), f2_to_bf16x2(k[2], k[3]));      // k_hat (bf16) for the window
     if (KDA) {
         nrm[64 + sl] = make_float4(pc[0], pc[1], pc[2], pc[3]);
@@ -366,44 +350,28 @@ __device__ __forceinline__ void step_prologue(const StepParams& P, const ProgSca
                 ws[j] = wj[i];
             }
         }
-        LQ_NSTAMP(4);
         signal();
-        LQ_NSTAMP(5);
         reinterpret_cast<uint2*>(P.Kbuf + (sh * L + h) * KD)[lane] = kapp;
 #pragma unroll
         for (int i = 0; i < 2; ++i) {
             const int j = lane + 32 * i;
             if (j < h) P.Wbuf[sh * L + j] = wj[i];
         }
-        LQ_NSTAMP(6);
     }
 }
-
-#ifdef LQ_TRACE
-static __device__ long long g_ptrace[160 * 256 * 8];
-#define LQ_PSTAMP(k) do { if (pi >= 0 && pi < 256 && blockIdx.x < 160 && t == 0) g_ptrace[(blockIdx.x * 256 + pi) * 8 + (k)] = clock64(); } while (0)
-#else
-#define LQ_PSTAMP(k) do { } while (0)
-#endif
 
 // ------------------------------------------------------------------------------------------------------------------
 // body: GT threads, operands in the shared-memory stage `st` (prologue done)
 // ------------------------------------------------------------------------------------------------------------------
 // `release()` is called by every thread after its last read of the stage and BEFORE the program's global stores: the
 // stage hand-back is an mbarrier arrive with release semantics, which would otherwise wait for those stores to drain.
-//
-// The int8 tile comes either from the stage (REGC false: `st` holds the whole checkpoint) or from the registers `ac`, which
-// the caller filled with plain global loads issued one program ahead (REGC true: the stage then starts at Sk and `st` is a
-// virtual origin CK_SK bytes below it).  `refill()` is called once the tile phase has consumed `ac`.
 constexpr int MT = (VD / GW) / 16;                 // m16 tiles of tile rows per warp
-template <int R, bool KDA, bool REGC, typename Release, typename Refill>
+template <int R, bool KDA, typename Release>
 __device__ __forceinline__ void step_body(const StepParams& P, const ProgScalars& sc, char* st, const StageLayout& lay,
-                                          const GroupScratch& gs, int t, int bar, Release release, uint4 (&ac)[4 * MT],
-                                          Refill refill, int pi = -1) {
+                                          const GroupScratch& gs, int t, int bar, Release release) {
     const int w = t >> 5, lane = t & 31, l8 = lane & 7, g = lane >> 3;
     const int L = P.d.L, h = sc.h;
     const int64_t sh = int64_t(sc.slot) * P.d.HV + sc.hv;
-    LQ_PSTAMP(0);
     const float* nrm = reinterpret_cast<const float*>(st + lay.nrm);
     // this lane's two values of the token's v, straight from global memory: issued now, used in the last phase
     const uint32_t vraw = __ldg(reinterpret_cast<const uint32_t*>(
@@ -455,7 +423,8 @@ __device__ __forceinline__ void step_body(const StepParams& P, const ProgScalars
             for (int i = 0; i < 4; ++i) { bfr[4 * i] = x[i].x; bfr[4 * i + 1] = x[i].y; bfr[4 * i + 2] = x[i].z; bfr[4 * i + 3] = x[i].w; }
         }
         const float unscale = *reinterpret_cast<const float*>(st + lay.sc + 36);
-        if (!REGC) {
+        uint4 ac[4 * MT];
+        {
             const uint4* tile = reinterpret_cast<const uint4*>(st + CK_CODES);
 #pragma unroll
             for (int mt = 0; mt < MT; ++mt) {
@@ -488,8 +457,6 @@ __device__ __forceinline__ void step_body(const StepParams& P, const ProgScalars
             }
         }
     }
-    refill();
-    LQ_PSTAMP(1);
 
     // ---- window dots dk_j = K_j . k_hat, dq_j = K_j . q_hat on the tensor cores: D[j][n] = sum_c K_j[c] B[c][n] with
     //      n = {k head, k remainder, q head, q remainder} (bf16, fp32 accumulate).  Sixteen rows per m16 tile, tiles dealt
@@ -534,7 +501,6 @@ __device__ __forceinline__ void step_body(const StepParams& P, const ProgScalars
             }
         }
     }
-    LQ_PSTAMP(2);
     // ---- factor dots dU_r . k_hat, dU_r . q_hat (KDA: U_r[c] pc[c]) ----
 #pragma unroll
     for (int cr = 0; cr < R / 4; ++cr) {
@@ -568,10 +534,7 @@ __device__ __forceinline__ void step_body(const StepParams& P, const ProgScalars
         }
     }
 
-    LQ_PSTAMP(3);
-    LQ_PSTAMP(4);
     named_bar(bar, GT);
-    LQ_PSTAMP(5);
 
     // ---- contribution of the window and of the rank-R part.  A warp owns VPW = 64 / GW value pairs; lane % VPW picks the
     //      pair and lane / VPW the phase of j; the phases are combined with shuffles. ----
@@ -604,7 +567,6 @@ __device__ __forceinline__ void step_body(const StepParams& P, const ProgScalars
         rk.x += __shfl_xor_sync(0xffffffffu, rk.x, o); rk.y += __shfl_xor_sync(0xffffffffu, rk.y, o);
         rq.x += __shfl_xor_sync(0xffffffffu, rq.x, o); rq.y += __shfl_xor_sync(0xffffffffu, rq.y, o);
     }
-    LQ_PSTAMP(6);
     float u0 = 0.f, u1 = 0.f, y0 = 0.f, y1 = 0.f, pn = 0.f;
     if (jh == 0) {
         const float2 m0 = gs.mqy[2 * vp], m1 = gs.mqy[2 * vp + 1];
@@ -691,8 +653,7 @@ __global__ void __launch_bounds__(GT, 2) step_direct_kernel(StepParams P) {
     if (t < 32) step_prologue<KDA>(P, sc, st, lay, t, [] {});
     __syncthreads();
     const GroupScratch gs = carve_scratch(stage_smem + stage_layout(P.d.L, P.d.L, R, KDA).bytes);
-    uint4 ac[4 * MT];
-    step_body<R, KDA, false>(P, sc, st, lay, gs, t, 1, [] {}, ac, [] {});
+    step_body<R, KDA>(P, sc, st, lay, gs, t, 1, [] {});
 }
 
 #include "lq_step_warp.cuh"
@@ -700,14 +661,6 @@ __global__ void __launch_bounds__(GT, 2) step_direct_kernel(StepParams P) {
 // ------------------------------------------------------------------------------------------------------------------
 // driver 2: persistent CTAs, producer warp + bulk asynchronous copies into a ring of stages
 // ------------------------------------------------------------------------------------------------------------------
-#ifdef LQ_TRACE
-// Debug build only: per (CTA, program) cycle stamps -- stage free / data landed / prologue done / program done.
-constexpr int TRACE_PROGS = 256;
-static __device__ long long g_trace[160 * TRACE_PROGS * 4];
-#define LQ_STAMP(i, k) do { if ((i) < TRACE_PROGS && blockIdx.x < 160) g_trace[(blockIdx.x * TRACE_PROGS + (i)) * 4 + (k)] = clock64(); } while (0)
-#else
-#define LQ_STAMP(i, k) do { } while (0)
-#endif
 constexpr uint32_t WAIT_LIMIT = 1u << 22;      // bounded spin: ~seconds at worst, then the kernel records a status and leaves
 constexpr int ST_PRODUCER_TIMEOUT = 1, ST_CONSUMER_TIMEOUT = 2, ST_PROLOGUE_TIMEOUT = 4;
 
@@ -768,16 +721,11 @@ struct FuseTail {
     int team_bytes;                                 // shared memory of one team
 };
 
-#ifndef LQ_REGC
-#define LQ_REGC 0
-#endif
 #ifndef LQ_NPW
 #define LQ_NPW 2
 #endif
 constexpr int NPW = LQ_NPW;                     // prologue warps; warp 2 + k takes the programs i = k (mod NPW)
 constexpr int UT = 32 * (2 + NPW);              // utility threads ahead of the consumer groups: producer, copy issue, prologues
-constexpr bool REGC = LQ_REGC != 0;             // int8 tile through registers (plain loads one program ahead), not the ring
-constexpr int SKIP = REGC ? CK_SK : 0;          // stage bytes not held in the ring; `st` is a virtual origin SKIP bytes below
 constexpr int ND = 16;                         // descriptors = most programs resident in the ring at once
 
 template <int R, bool KDA, int NG, bool FUSE>
@@ -801,7 +749,6 @@ __global__ void __launch_bounds__(UT + NG * GT, 1) step_pipelined_kernel(StepPar
     const int nit = (nprog - bid + grid - 1) / grid;
 
     if (tid == 0) {
-        LQ_STAMP(TRACE_PROGS - 1, 0);                            // (trace builds) kernel entry
         *dl_n = 0;
         *abortf = 0;
         for (int s = 0; s < ND; ++s) {
@@ -816,7 +763,6 @@ __global__ void __launch_bounds__(UT + NG * GT, 1) step_pipelined_kernel(StepPar
     __syncthreads();
     pdl_trigger();
     pdl_wait();                                                  // everything below reads what earlier kernels of the stream wrote
-    if (tid == 0) LQ_STAMP(TRACE_PROGS - 1, 1);                  // (trace builds) set-up done, predecessor complete
 
     auto run_roles = [&]() {
     if (warp == 0) {
@@ -855,17 +801,15 @@ __global__ void __launch_bounds__(UT + NG * GT, 1) step_pipelined_kernel(StepPar
             for (int j = 0; j < cnt; ++j) {
                 const int i = base + j;
                 const int dsc = i % ND;
-                LQ_QSTAMP(0);
                 const ProgScalars sc = *const_cast<const ProgScalars*>(&pbatch[j]);      // broadcast read
                 const bool live = prog_live(sc, L);
                 const int rows = live ? sc.h : 0;
                 const StageLayout lay = stage_layout(rows, L, R, KDA, false);
-                const int size = lay.bytes - SKIP;
+                const int size = lay.bytes;
                 int off = head;
                 uint32_t v0 = vhead;
                 if (head + size > ring_bytes) { v0 += uint32_t(ring_bytes - head); off = 0; }
                 const uint32_t v1 = v0 + uint32_t(size);
-                LQ_QSTAMP(1);
                 while (tail < i) {                               // reclaim in order until the stage and its descriptor are free
                     const uint32_t vt = __shfl_sync(0xffffffffu, r_vs, tail % ND);
                     if (v1 - vt <= uint32_t(ring_bytes) && i - tail < ND) break;
@@ -876,26 +820,21 @@ __global__ void __launch_bounds__(UT + NG * GT, 1) step_pipelined_kernel(StepPar
                     if (lane == 0) { atomicOr(&g_status, ST_PRODUCER_TIMEOUT); *abortf = 1; }
                     break;
                 }
-                LQ_QSTAMP(2);
                 if (lane == dsc) r_vs = v0;
                 head = off + size;
                 vhead = v1;
-                char* st = stage_smem + off - SKIP;
+                char* st = stage_smem + off;
                 if (lane == 0) {
-                    LQ_STAMP(i, 0);
                     doff[dsc] = off;
                     doff[ND + NG + dsc] = rows;
                     *reinterpret_cast<ProgScalars*>(st + lay.sc) = sc;
                     if (live) {
-                        uint32_t bytes = uint32_t(ck_bytes(R) - SKIP) + 2u * uint32_t(sc.h) * 256u + uint32_t(L) * 4u;
+                        uint32_t bytes = uint32_t(ck_bytes(R)) + 2u * uint32_t(sc.h) * 256u + uint32_t(L) * 4u;
                         if (KDA) bytes += uint32_t(sc.h) * 256u + 512u + 256u + 512u;
                         mbar_arrive_expect_tx(full + dsc, bytes);
-                    } else {
-                        mbar_arrive(full + dsc);
-                    }
+                    }                                            // a dead program's `full` is completed by the copy-issue warp
                 }
                 __syncwarp();
-                LQ_QSTAMP(3);
                 if (lane == 0) mbar_arrive(ready + dsc);
             }
         }
@@ -915,7 +854,7 @@ __global__ void __launch_bounds__(UT + NG * GT, 1) step_pipelined_kernel(StepPar
             const StageLayout l0 = stage_layout(0, L, R, KDA, false), l1 = stage_layout(1, L, R, KDA, false);
             int which = -1;                                              // member of the layout this lane copies into
             switch (lane) {
-                case 0: c_base = P.ssm + SKIP; c_slot = uint32_t(P.d.SS) * 4u; c_hv = VD * KD * 4u; b_fix = ck_bytes(R) - SKIP; o_fix = SKIP; break;
+                case 0: c_base = P.ssm; c_slot = uint32_t(P.d.SS) * 4u; c_hv = VD * KD * 4u; b_fix = ck_bytes(R); break;
                 case 1: c_base = reinterpret_cast<const char*>(P.Kbuf); c_slot = uint32_t(HV) * rowb; c_hv = rowb; b_h = 256u; which = 0; break;
                 case 2: c_base = reinterpret_cast<const char*>(P.Ubuf); c_slot = uint32_t(HV) * rowb; c_hv = rowb; b_h = 256u; which = 1; break;
                 case 3: c_base = reinterpret_cast<const char*>(P.Wbuf); c_slot = uint32_t(HV * L) * 4u; c_hv = uint32_t(L) * 4u; b_fix = uint32_t(L) * 4u; which = 2; break;
@@ -938,11 +877,10 @@ __global__ void __launch_bounds__(UT + NG * GT, 1) step_pipelined_kernel(StepPar
                 if (lane == 0) { atomicOr(&g_status, ST_PRODUCER_TIMEOUT); *abortf = 1; }
                 return;
             }
-            char* st = stage_smem + doff[dsc] - SKIP;
+            char* st = stage_smem + doff[dsc];
             const int rows = doff[ND + NG + dsc];
             const ProgScalars sc = *reinterpret_cast<const ProgScalars*>(st + stage_layout(rows, L, R, KDA, false).sc);
             if (prog_live(sc, L)) {
-                LQ_QSTAMP(4);
                 // The ring bytes under this stage were read and written through the generic proxy by the previous tenants'
                 // prologue and consumers; their accesses are visible here through the empty -> ready barrier chain, and this
                 // fence orders them before the asynchronous-proxy writes issued below.
@@ -952,7 +890,11 @@ __global__ void __launch_bounds__(UT + NG * GT, 1) step_pipelined_kernel(StepPar
                                   uint64_t(uint32_t(sc.n)) * c_n + uint64_t(hk) * c_hk;
                 const uint32_t bytes = b_fix + uint32_t(sc.h) * b_h;
                 if (bytes) bulk_g2s(st + o_fix + uint32_t(sc.h) * o_h, src, bytes, full + dsc);
-                LQ_QSTAMP(5);
+            } else if (lane == 0) {
+                // nothing to copy (padding row, null slot or full window): this warp completes the phase itself.  Doing it here
+                // and not in the producer keeps this warp inside the full -> normed -> empty chain for every program, so the
+                // producer can never run a whole round of descriptors ahead of it, however long a run of dead programs is.
+                mbar_arrive(full + dsc);
             }
         }
         return;
@@ -977,20 +919,16 @@ __global__ void __launch_bounds__(UT + NG * GT, 1) step_pipelined_kernel(StepPar
             const int dsc = i % ND;
             const uint2 q_cur = q_nx, k_cur = k_nx;
             qk_fetch(i + NPW);
-#ifdef LQ_TRACE
-            if (i < 256 && blockIdx.x < 160 && lane == 0) g_ntrace[(blockIdx.x * 256 + i) * 8 + 7] = clock64();
-#endif
             if (!warp_wait_bounded(full + dsc, uint32_t(i / ND) & 1u, lane)) {
                 if (lane == 0) { atomicOr(&g_status, ST_PROLOGUE_TIMEOUT); *abortf = 1; }
                 return;
             }
-            char* st = stage_smem + doff[dsc] - SKIP;
+            char* st = stage_smem + doff[dsc];
             const int rows = doff[ND + NG + dsc];                  // rows the stage was sized for (h, or 0 for a dead program)
             const ProgScalars sc = *reinterpret_cast<const ProgScalars*>(st + stage_layout(rows, L, R, KDA, false).sc);
-            if (lane == 0) LQ_STAMP(i, 1);
             if (prog_live(sc, L)) {
                 const StageLayout lay = stage_layout(sc.h, L, R, KDA, false);
-                step_prologue<KDA>(P, sc, st, lay, lane, [&] { mbar_arrive(normed + dsc); }, i, true, q_cur, k_cur);
+                step_prologue<KDA>(P, sc, st, lay, lane, [&] { mbar_arrive(normed + dsc); }, true, q_cur, k_cur);
             } else {
                 mbar_arrive(normed + dsc);
             }
@@ -1004,39 +942,7 @@ __global__ void __launch_bounds__(UT + NG * GT, 1) step_pipelined_kernel(StepPar
     const int bar = 1 + g;
     const GroupScratch gs = carve_scratch(scratch0 + g * SCRATCH_BYTES);
     volatile int* gflag = gflag0 + g;
-    // Register path of the int8 tile: lane (gid, tig) of warp w keeps, for each of its m16 tiles, rows gid and gid + 8 at
-    // columns 16 tig and 64 + 16 tig (the fragment order of step_body).  The loads of program i + NG are issued when the
-    // tile phase of program i has consumed the registers; the slot of the program after that is fetched at the same time.
-    uint4 ac[4 * MT];
-    int slot_n = 0;                                              // slot of the next program of this group (<= 0: no loads)
-    auto slot_of = [&](int i2) -> int {
-        if (!REGC || i2 >= nit) return 0;
-        return P.idx[(bid + i2 * grid) / HV];
-    };
-    auto load_codes = [&](int i2, int slot) {
-        if (!REGC || i2 >= nit || slot <= 0) return;
-        const int p2 = bid + i2 * grid;
-        const int hv2 = p2 - (p2 / HV) * HV;
-        const int lane = t & 31, gid = lane >> 2, tig = lane & 3;
-        const char* base = P.ssm + (int64_t(slot) * P.d.SS + int64_t(hv2) * VD * KD) * 4 +
-                           ((VD / GW) * (t >> 5) + gid) * KD + tig * 16;
-#pragma unroll
-        for (int mt = 0; mt < MT; ++mt) {
-            ac[4 * mt] = ldg_stream(base + (16 * mt) * KD);
-            ac[4 * mt + 1] = ldg_stream(base + (16 * mt) * KD + 64);
-            ac[4 * mt + 2] = ldg_stream(base + (16 * mt + 8) * KD);
-            ac[4 * mt + 3] = ldg_stream(base + (16 * mt + 8) * KD + 64);
-        }
-    };
-    if (REGC) {
-        load_codes(g, slot_of(g));
-        slot_n = slot_of(g + NG);
-    }
     for (int i = g; i < nit; i += NG) {
-        auto refill = [&] {
-            load_codes(i + NG, slot_n);
-            slot_n = slot_of(i + 2 * NG);
-        };
         const int dsc = i % ND;
         // one warp polls and publishes the outcome; the other warps sleep at the group barrier
         if (t < 32) {
@@ -1048,27 +954,23 @@ __global__ void __launch_bounds__(UT + NG * GT, 1) step_pipelined_kernel(StepPar
             if (t == 0) { atomicOr(&g_status, ST_CONSUMER_TIMEOUT); *abortf = 1; }
             return;
         }
-        char* st = stage_smem + doff[dsc] - SKIP;
+        char* st = stage_smem + doff[dsc];
         const int rows = doff[ND + NG + dsc];
         const StageLayout lay = stage_layout(rows, L, R, KDA, false);
         const ProgScalars sc = *reinterpret_cast<const ProgScalars*>(st + lay.sc);
-        if (t == 0) LQ_STAMP(i, 2);
         auto release = [&] { mbar_arrive(empty + dsc); };
         if (prog_live(sc, L)) {
-            step_body<R, KDA, REGC>(P, sc, st, lay, gs, t, bar, release, ac, refill, i);
+            step_body<R, KDA>(P, sc, st, lay, gs, t, bar, release);
             if (FUSE && t == 0 && sc.h + 1 == L) dl[atomicAdd(dl_n, 1)] = sc.slot * HV + sc.hv;      // window just filled
         } else {
             if (FUSE && t == 0 && sc.slot > 0 && sc.h == L) dl[atomicAdd(dl_n, 1)] = sc.slot * HV + sc.hv;   // was full already
-            refill();
             release();
             const int p = bid + i * grid;
             if (t < 64) reinterpret_cast<uint32_t*>(P.o)[int64_t(p) * 64 + t] = 0u;
         }
-        if (t == 0) LQ_STAMP(i, 3);
     }
     };
     run_roles();
-    if (tid == UT) LQ_STAMP(TRACE_PROGS - 1, 2);                 // (trace builds) first consumer group done
 
     // ================= fused flush: the heads whose window this CTA just filled, two teams of 256 threads =================
     if constexpr (FUSE) {
@@ -1087,13 +989,12 @@ __global__ void __launch_bounds__(UT + NG * GT, 1) step_pipelined_kernel(StepPar
         A.d = P.d; A.ssm = P.ssm; A.Kbuf = P.Kbuf; A.Ubuf = P.Ubuf; A.Wbuf = P.Wbuf; A.Pbuf = P.Pbuf; A.Gbuf = P.Gbuf;
         A.hcnt = P.hcnt; A.Q0 = ft.Q0; A.iters = ft.iters;
         auto tsync = [&] { named_bar(8 + team, 256); };
-        long long facc[16] = {0}, flast = 0;
-        for (int k = team; k < ndl; k += nteams) flush_head<R, KDA>(fs, A, dl[k], ttid, tsync, facc, flast);
+        for (int k = team; k < ndl; k += nteams) flush_head<R, KDA>(fs, A, dl[k], ttid, tsync);
     }
 }
 
 // 0 = pipelined, 1 = direct, 2 = one warp per program (GDN; KDA falls back to the pipelined driver)
-static int g_step_impl = 0;
+static std::atomic<int> g_step_impl{0};
 
 // fuse != nullptr: the pipelined driver also flushes, in the same launch, the heads whose window it fills (Q0, iters from
 // *fuse).  Returns LQ_ERR_UNSUPPORTED when the fused form is not available for the configuration (debug drivers, a flush
@@ -1101,15 +1002,16 @@ static int g_step_impl = 0;
 template <int R, bool KDA>
 static int launch_step(const StepParams& P, cudaStream_t st, const FuseTail* fuse) {
     const StageLayout lay = stage_layout(P.d.L, P.d.L, R, KDA);
-    if (g_step_impl != 0 && fuse && !(g_step_impl == 2 && KDA)) return LQ_ERR_UNSUPPORTED;
-    if (g_step_impl == 1) {
+    const int impl = g_step_impl.load(std::memory_order_relaxed);      // read once: one call never mixes two drivers
+    if (impl != 0 && fuse && !(impl == 2 && KDA)) return LQ_ERR_UNSUPPORTED;
+    if (impl == 1) {
         const size_t smem = size_t(lay.bytes) + SCRATCH_BYTES;
         int rc = ensure_smem((const void*)step_direct_kernel<R, KDA>, smem);
         if (rc) return rc;
         step_direct_kernel<R, KDA><<<unsigned(P.N) * P.d.HV, GT, smem, st>>>(P);
         return finish_launch();
     }
-    if (g_step_impl == 2 && !KDA) {
+    if (impl == 2 && !KDA) {
         const int nprog = P.N * P.d.HV;
         const int want = (nprog + WK_WARPS - 1) / WK_WARPS;
         const int cap = device_sm_count() * 4;
@@ -1157,11 +1059,8 @@ static int step_common(const lq_dims* d, void* ssm, void* Kbuf, void* Ubuf, floa
     if (N < 0) return LQ_ERR_RANGE;
     if (N == 0) return LQ_OK;
     if (!mixed || !a || !b || !idx || !o) return LQ_ERR_NULL;
-    const uintptr_t al = reinterpret_cast<uintptr_t>(ssm) | reinterpret_cast<uintptr_t>(Kbuf) | reinterpret_cast<uintptr_t>(Ubuf) |
-                         reinterpret_cast<uintptr_t>(Wbuf) | reinterpret_cast<uintptr_t>(mixed) | reinterpret_cast<uintptr_t>(o) |
-                         (kda ? (reinterpret_cast<uintptr_t>(Gbuf) | reinterpret_cast<uintptr_t>(Pbuf) |
-                                 reinterpret_cast<uintptr_t>(a) | reinterpret_cast<uintptr_t>(dt_bias)) : 0);
-    if (al & 15) return LQ_ERR_ALIGN;
+    if (misaligned16({ssm, Kbuf, Ubuf, Wbuf, mixed, o})) return LQ_ERR_ALIGN;
+    if (kda && misaligned16({Gbuf, Pbuf, a, dt_bias})) return LQ_ERR_ALIGN;
     StepParams P;
     P.d = *d; P.ssm = (char*)ssm; P.Kbuf = (uint16_t*)Kbuf; P.Ubuf = (uint16_t*)Ubuf; P.Wbuf = Wbuf; P.Pbuf = Pbuf;
     P.Gbuf = (uint16_t*)Gbuf; P.hcnt = hcnt; P.mixed = (const uint16_t*)mixed; P.a = (const uint16_t*)a;
@@ -1175,30 +1074,15 @@ static int step_common(const lq_dims* d, void* ssm, void* Kbuf, void* Ubuf, floa
 
 }  // namespace lq
 
-#ifdef LQ_TRACE
-extern "C" int lq_debug_read_trace(long long* out, int n) {
-    return cudaMemcpyFromSymbol(out, lq::g_trace, sizeof(long long) * n) == cudaSuccess ? 0 : -5;
-}
-extern "C" int lq_debug_read_qtrace(long long* out, int n) {
-    return cudaMemcpyFromSymbol(out, lq::g_qtrace, sizeof(long long) * n) == cudaSuccess ? 0 : -5;
-}
-extern "C" int lq_debug_read_ntrace(long long* out, int n) {
-    return cudaMemcpyFromSymbol(out, lq::g_ntrace, sizeof(long long) * n) == cudaSuccess ? 0 : -5;
-}
-extern "C" int lq_debug_read_ptrace(long long* out, int n) {
-    return cudaMemcpyFromSymbol(out, lq::g_ptrace, sizeof(long long) * n) == cudaSuccess ? 0 : -5;
-}
-#endif
-
 extern "C" int lq_set_option(const char* name, int32_t value) {
     if (!name) return LQ_ERR_NULL;
     if (strcmp(name, "step_impl") == 0) {
         if (value < 0 || value > 2) return LQ_ERR_RANGE;
-        lq::g_step_impl = value;
+        lq::g_step_impl.store(value, std::memory_order_relaxed);
         return LQ_OK;
     }
     if (strcmp(name, "pdl") == 0) {
-        lq::g_pdl = value != 0;
+        lq::g_pdl.store(value != 0, std::memory_order_relaxed);
         return LQ_OK;
     }
     return LQ_ERR_UNSUPPORTED;
