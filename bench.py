@@ -1,21 +1,31 @@
 """Benchmark of the quantized-state decode path (step + window flush) on B200.
 
-    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl b200|reference] [--workload gdn|kda] [--batch B]
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl b200|reference] [--workload gdn|kda] [--batch B] [--only-main]
 
 Workload (default): the batched GDN decode of a Qwen3-Next-like layer -- 16 key / 32 value heads, d_k = d_v = 128,
 B = 256 independent sequences per GPU, window L = 64, R = 4 Compensator Tokens, bf16 q/k/v, INT8 state with fp32
-scales; every head flushes every 64 steps.  One bench "step" is one decode step of the whole batch (step kernel + flush
-kernel).  `--workload kda` runs the KDA layer (32 heads, B = 128, L = 32, R = 8).  Inputs are seeded synthetic tensors.
+scales.  One bench "step" is one decode step of the whole batch: ONE launch of the fused decode kernel (the step of every
+head plus the flush of the heads whose window fills).  Inputs are seeded synthetic tensors.
 
-Prints ONE JSON line.  `value` is the whole-job rate in (sequence, value-head) decode steps per second with inputs
-resident in HBM (one window of 64 steps captured in a CUDA graph and replayed); `e2e` is the same rate through
-LeapQuantState.decode with the step's inputs copied from pinned host memory and the output copied back inside the
-timed region; `roofline` times the step kernel alone over one window; `cpu_baseline` times the CPU oracle.
+Fill levels are STAGGERED, as on a serving engine whose sequences arrive at different times: sequence n starts with
+n mod L live window entries, so every step reads the window-average number of bytes and flushes B * HV / L heads, and any
+run of steps is representative whatever --steps is.  The timed region is a CUDA graph of L steps replayed until at least
+--steps steps and 0.5 s have been timed; `steps` in the output is the number actually timed.
+
+Prints ONE JSON line.  `value`: (sequence, value-head) decode steps per second, inputs resident in HBM.  `e2e`: the same
+through LeapQuantState.decode with each step's inputs copied from pinned host memory and the output copied back inside
+the timed region.  `roofline`: the decode kernel over the timed region (algorithmic bytes of the fill levels that were
+timed / CUDA-event time).  Further keys: `parity_check` (a decode step of the whole batch after the timed region against
+the CPU oracle), `step_kernel` and `flush` (the two halves alone, lock-step windows), `lockstep` (all heads flush on the
+same step), `prefill_round_trip`, `kda` (the KDA layer: 32 heads, B = 128, L = 32, R = 8, and the isolated quantize on
+outlier states), `batch_sweep` (B = 1 ... 256), `config3` (48 layers x 32 heads, 1 024 sequences split over the GPUs),
+`cpu_baseline` (the CPU oracle on the host cores).
 With N > 1 (torchrun) every rank runs its own B sequences on its own GPU (weak scaling, no communication on the state
 path) and the time is the maximum over ranks.
 """
 import argparse
 import json
+import math
 import os
 import statistics
 import sys
@@ -32,10 +42,11 @@ WORKLOADS = {
     "gdn": dict(name="gdn_decode_H16_HV32_d128_L64_R4", H=16, HV=32, L=64, R=4, B=256, kda=False),
     "kda": dict(name="kda_decode_H32_HV32_d128_L32_R8", H=32, HV=32, L=32, R=8, B=128, kda=True),
 }
-# DRAM bytes (read + write) of the step kernel relative to its algorithmic bytes, from the ncu capture summarised in
-# profiles/step_pipelined_gdn_B128_ncu.md (150.05 MB + 5.40 MB for 4 096 programs at h = 33 vs 37 928 B algorithmic per
-# program).  `roofline.traffic` scales the live algorithmic bytes per launch by this ratio.  None = not captured.
+# DRAM bytes (read + write) per algorithmic byte of the decode kernel, from the ncu captures summarised under profiles/
+# (decode_fused_gdn_B128_ncu.md: 150.1 MB + 4.7 MB for 4 096 programs at h = 32 against 153 MB algorithmic;
+# decode_fused_kda_B128_ncu.md).  `roofline.traffic` scales the live algorithmic bytes per launch by this ratio.
 NCU_TRAFFIC_RATIO = {"gdn": 1.01, "kda": None}
+MIN_TIMED_S = 0.5
 
 
 def step_bytes(h, L, R, gqa, kda):
@@ -58,7 +69,12 @@ def flush_bytes(L, R, kda):
 
 
 def window_bytes_per_head_step(L, R, gqa, kda):
+    """Mean over one window: the steps at h = 0 .. L-1 plus one flush, per step."""
     return (sum(step_bytes(h, L, R, gqa, kda) for h in range(L)) + flush_bytes(L, R, kda)) / L
+
+
+def roundtrip_bytes(R):
+    return 4 * V * K + K * V + 4 * (K + V) + 2 * R * (K + V)
 
 
 class ClockSampler(threading.Thread):
@@ -152,14 +168,16 @@ def cpu_oracle_rate(wl, steps, warmup, nseq=8):
     for t in range(warmup, warmup + steps):
         one(t)
     dt = time.perf_counter() - t0
-    return nseq * HV * steps / dt, dt, f"{nseq} sequences x {HV} heads, {steps} decode steps (step + flush), torch CPU oracle"
+    return nseq * HV * steps / dt, dt, (f"{nseq} sequences x {HV} heads, {steps} decode steps (step + flush, one whole window "
+                                        f"from empty), torch CPU oracle")
 
 
 def run_reference(args, wl):
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return
-    steps = max(1, min(args.steps, 2 * wl["L"]))
+    L = wl["L"]
+    steps = L * max(1, min(-(-args.steps // L), 2))            # whole windows, so that the flush is inside the sample
     warm = max(3, min(args.warmup, 8))
     rate, dt, sample = cpu_oracle_rate(wl, steps, warm)
     cores = os.cpu_count() or 1
@@ -167,7 +185,7 @@ def run_reference(args, wl):
             "n_gpus": args.gpus, "steps": steps, "warmup": warm, "ms_per_step": 1e3 * dt / steps, "higher_is_better": True,
             "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
             "config": {"workload": wl["name"], "note": "the reference has no CPU implementation of this path; this is the "
-                       "CPU restatement (oracle) of its kernel arithmetic on the host cores"},
+                       "CPU restatement (oracle) of its kernel arithmetic on the host cores, on a bounded sample"},
             "cpu_baseline": {"value": rate, "unit": "head-steps/s", "cores": cores, "kind": "port", "sample": sample},
             "e2e": {"value": rate, "unit": "head-steps/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
             "gpu_launches": 0}
@@ -193,40 +211,93 @@ def synth_inputs(N, H, HV, steps, seed, kda):
     return mixed, a, b, torch.zeros(HV), (torch.zeros(HV, K) if kda else torch.zeros(HV))
 
 
-class Layer:
-    """One layer's quantized state for B sequences on the current device, plus 64 steps of device-resident inputs."""
+def device_inputs(N, H, HV, steps, seed, kda, device):
+    """The same distributions generated on the device (for the large secondary workloads; values differ from the host
+    generator's, distributions do not)."""
+    g = torch.Generator(device=device).manual_seed(seed)
+    r = lambda *s: torch.randn(*s, generator=g, device=device)
+    q, k = r(steps, N, H, K), r(steps, N, H, K)
+    q = q / q.norm(dim=-1, keepdim=True)
+    k = k / k.norm(dim=-1, keepdim=True)
+    mixed = torch.cat([q.reshape(steps, N, -1), k.reshape(steps, N, -1), r(steps, N, HV * V)], -1).to(torch.bfloat16)
+    a = r(steps, N, HV, K).to(torch.bfloat16) if kda else r(steps, N, HV).to(torch.bfloat16)
+    b = r(steps, N, HV).to(torch.bfloat16)
+    z = lambda *s: torch.zeros(*s, device=device)
+    return mixed, a, b, z(HV), (z(HV, K) if kda else z(HV))
 
-    def __init__(self, wl, B, device, seed):
+
+class Layer:
+    """One layer's quantized state for B sequences on the current device, plus one window period (L steps) of inputs."""
+
+    def __init__(self, wl, B, device, seed, host_io=True, device_rng=False, inputs=None):
         from leapquant_b200.state import LeapQuantState
         self.wl, self.B, self.device = wl, B, device
         H, HV, L, R, kda = wl["H"], wl["HV"], wl["L"], wl["R"], wl["kda"]
         NS = B + 9
-        g = torch.Generator(device="cpu").manual_seed(seed)
         self.ssm = torch.empty(NS, HV, V, K, device=device)
-        for s0 in range(0, NS, 64):                             # seeded fp32 states, generated in chunks
-            n = min(64, NS - s0)
-            self.ssm[s0:s0 + n] = (torch.randn(n, HV, V, K, generator=g) * 0.1).to(device)
+        if device_rng:
+            gd = torch.Generator(device=device).manual_seed(seed)
+            for s0 in range(0, NS, 256):
+                n = min(256, NS - s0)
+                self.ssm[s0:s0 + n] = torch.randn(n, HV, V, K, generator=gd, device=device) * 0.1
+        else:
+            g = torch.Generator(device="cpu").manual_seed(seed)
+            for s0 in range(0, NS, 64):                         # seeded fp32 states, generated in chunks
+                n = min(64, NS - s0)
+                self.ssm[s0:s0 + n] = (torch.randn(n, HV, V, K, generator=g) * 0.1).to(device)
         self.st = LeapQuantState(self.ssm, H, kda=kda, L=L, R=R, nmax=B)
         self.idx = torch.arange(1, B + 1, dtype=torch.int32, device=device)
         self.st.quantize(self.ssm, self.idx)
         self.period = L
-        mixed, a, b, A_log, dtb = synth_inputs(B, H, HV, self.period, seed + 1, kda)
-        # pinned host copies of the inputs, the three tensors of a step back to back so that one copy moves them
-        from leapquant_b200.host_io import HostStagedDecoder
-        self.h_slab, hv = HostStagedDecoder.host_slab(mixed[0], a[0].contiguous(), b[0], steps=self.period)
-        for i in range(self.period):
-            hv[i][0].copy_(mixed[i]); hv[i][1].copy_(a[i]); hv[i][2].copy_(b[i])
-        self.h_mixed, self.h_a, self.h_b = [v[0] for v in hv], [v[1] for v in hv], [v[2] for v in hv]
-        self.mixed, self.a, self.b = mixed.to(device), a.contiguous().to(device), b.to(device)
-        self.A_log, self.dtb = A_log.to(device), dtb.to(device)
+        if inputs is not None:                                  # inputs shared with other layers of a model
+            self.mixed, self.a, self.b, self.A_log, self.dtb = inputs
+        elif device_rng:
+            self.mixed, self.a, self.b, self.A_log, self.dtb = device_inputs(B, H, HV, L, seed + 1, kda, device)
+        else:
+            mixed, a, b, A_log, dtb = synth_inputs(B, H, HV, L, seed + 1, kda)
+            self.mixed, self.a, self.b = mixed.to(device), a.contiguous().to(device), b.to(device)
+            self.A_log, self.dtb = A_log.to(device), dtb.to(device)
         self.out = torch.zeros(B, HV, V, dtype=torch.bfloat16, device=device)
-        self.h_out = torch.zeros(B, HV, V, dtype=torch.bfloat16).pin_memory()
-        self.staged = HostStagedDecoder(self.st, self.ssm, self.A_log, self.dtb, self.idx, self.h_mixed[0], self.h_a[0],
-                                        self.h_b[0], self.h_out)
+        self.graph = None
+        self.staged = None
+        if host_io:
+            # pinned host copies of the inputs, the three tensors of a step back to back so that one copy moves them
+            from leapquant_b200.host_io import HostStagedDecoder
+            self.h_slab, hv = HostStagedDecoder.host_slab(mixed[0], a[0].contiguous(), b[0], steps=L)
+            for i in range(L):
+                hv[i][0].copy_(mixed[i]); hv[i][1].copy_(a[i]); hv[i][2].copy_(b[i])
+            self.h_mixed, self.h_a, self.h_b = [x[0] for x in hv], [x[1] for x in hv], [x[2] for x in hv]
+            self.h_out = torch.zeros(B, HV, V, dtype=torch.bfloat16).pin_memory()
+            self.staged = HostStagedDecoder(self.st, self.ssm, self.A_log, self.dtb, self.idx, self.h_mixed[0], self.h_a[0],
+                                            self.h_b[0], self.h_out)
 
-    def decode_resident(self, t):
+    def decode_resident(self, t, idx=None):
         i = t % self.period
-        self.st.decode(self.ssm, self.mixed[i], self.a[i], self.b[i], self.A_log, self.dtb, self.idx, self.out)
+        self.st.decode(self.ssm, self.mixed[i], self.a[i], self.b[i], self.A_log, self.dtb, self.idx if idx is None else idx,
+                       self.out)
+
+    def stagger(self):
+        """From all windows empty to sequence n holding n mod L entries: L - 1 decode steps in which row n takes part only
+        while t < n mod L (the other rows are padding rows of the call)."""
+        L = self.period
+        phase = (torch.arange(self.B, device=self.device) % L).to(torch.int32)
+        for t in range(L - 1):
+            self.decode_resident(t, torch.where(phase > t, self.idx, torch.zeros_like(self.idx)))
+
+    def capture(self):
+        """One window period (L decode steps, one launch each) as a CUDA graph."""
+        torch.cuda.synchronize()
+        self.graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(self.graph):
+            for t in range(self.period):
+                self.decode_resident(t)
+        return self.graph
+
+    def to_lockstep(self):
+        """All windows empty again (the prefill round trip: dequantize to fp32, quantize back); returns the two times."""
+        deq = timed(lambda: self.st.dequantize(self.ssm, self.idx))
+        qnt = timed(lambda: self.st.quantize(self.ssm, self.idx))
+        return deq, qnt
 
     def decode_host(self, t):
         """One step with host-resident inputs and output: the three input tensors come from pinned host memory and the
@@ -257,7 +328,8 @@ class Layer:
         return self.h_out.numel() * self.h_out.element_size()
 
 
-def timed(fn, stream):
+def timed(fn, stream=None):
+    stream = stream or torch.cuda.current_stream()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     e0.record(stream)
     fn()
@@ -266,8 +338,205 @@ def timed(fn, stream):
     return e0.elapsed_time(e1) * 1e-3
 
 
+def replay_timed(graph, min_windows, min_seconds, barrier=None):
+    """Replays the window graph: a calibration replay, then `reps` replays timed as one region (>= min_windows, >= min_seconds)."""
+    graph.replay()
+    t1 = timed(graph.replay)
+    reps = max(min_windows, int(math.ceil(min_seconds / max(t1, 1e-6))))
+    if barrier:
+        barrier()
+
+    def body():
+        for _ in range(reps):
+            graph.replay()
+
+    return timed(body), reps
+
+
+def parity_check(layer, rows):
+    """One more decode step of the WHOLE batch (the launch shape that was timed) from the state the timed region left behind,
+    against the CPU oracle on a few rows whose device state is copied to the host bit for bit.  Returns (ok, detail)."""
+    from oracle import lq_oracle as O
+    st, wl = layer.st, layer.wl
+    H, HV, L, R, kda = wl["H"], wl["HV"], wl["L"], wl["R"], wl["kda"]
+    rows = [r for r in rows if r < layer.B]
+    slots = layer.idx[rows].long()
+    n = len(rows)
+    # oracle-side copies: slot i + 1 of a small state tensor holds the device's slot of row rows[i]
+    ssm_c = torch.zeros(n + 1, HV, V, K)
+    ssm_c[1:] = layer.ssm[slots].cpu()
+    bufs = O.Buffers(n + 1, HV, K, V, L, R, kda)
+    for name in ("Kbuf", "Ubuf", "Wbuf", "Pbuf", "hcnt") + (("Gbuf",) if kda else ()):
+        getattr(bufs, name)[1:] = getattr(st, name)[slots].cpu()
+    vc = O.state_views(ssm_c, R)
+    t = 7 % layer.period
+    idx_c = torch.arange(1, n + 1, dtype=torch.int32)
+    o_c = torch.zeros(n, HV, V, dtype=torch.bfloat16)
+    mixed, a, b = layer.mixed[t][rows].cpu(), layer.a[t][rows].cpu(), layer.b[t][rows].cpu()
+    A_log, dtb = layer.A_log.cpu(), layer.dtb.cpu()
+    h_before = bufs.hcnt[1:].clone()
+    if kda:
+        O.kda_step(vc["Sq"], vc["Sk"], vc["Sv"], bufs.Kbuf, bufs.Ubuf, bufs.Wbuf, bufs.Pbuf, bufs.Gbuf, bufs.hcnt, mixed, a, b,
+                   A_log, dtb, vc["uq"], idx_c, o_c, H)
+    else:
+        O.gdn_step(vc["Sq"], vc["Sk"], vc["Sv"], bufs.Kbuf, bufs.Ubuf, bufs.Wbuf, bufs.Pbuf, bufs.hcnt, mixed, a, b, A_log, dtb,
+                   vc["uq"], idx_c, o_c, H)
+    u_c = torch.stack([bufs.Ubuf[1 + i, torch.arange(HV), h_before[i].long().clamp(max=L - 1)] for i in range(n)]).float()
+    O.flush(vc["Sq"], vc["Sk"], vc["Sv"], bufs.Kbuf, bufs.Ubuf, bufs.Wbuf, bufs.Pbuf, bufs.Gbuf if kda else None, bufs.hcnt,
+            vc["uq"], bufs.Q0, idx_c, kda=kda)
+    layer.decode_resident(t)
+    torch.cuda.synchronize()
+    o_g = layer.out[rows].cpu().float()
+    u_g = torch.stack([st.Ubuf[slots[i], torch.arange(HV, device=layer.device), h_before[i].long().clamp(max=L - 1).to(layer.device)]
+                       for i in range(n)]).cpu().float()
+    oc = o_c.float()
+    scale = float(oc.abs().max())
+    err_o = float((o_g - oc).abs().max())
+    err_u = float((u_g - u_c).abs().max())
+    lim_o = 8e-3 * scale + 1e-4                                   # one bf16 ulp of the largest output
+    lim_u = 8e-3 * float(u_c.abs().max()) + 2e-4
+    hc_ok = bool(torch.equal(st.hcnt[slots].cpu(), bufs.hcnt[1:]))
+    ok = err_o <= lim_o and err_u <= lim_u and hc_ok
+    return ok, {"rows": rows, "heads_flushed_in_check": int((h_before == L - 1).sum()), "max_abs_err_out": err_o,
+                "limit_out": lim_o, "max_abs_err_appended_u": err_u, "limit_u": lim_u, "window_counters_equal": hc_ok}
+
+
+def measure_staggered(layer, steps, min_seconds, barrier=None):
+    """Staggered fill levels, graph of one window period replayed.  Returns (seconds, steps timed, reps)."""
+    L = layer.period
+    layer.stagger()
+    layer.capture()
+    nwin = max(1, -(-steps // L))
+    dt, reps = replay_timed(layer.graph, nwin, min_seconds, barrier)
+    return dt, reps * L, reps
+
+
+def secondary_layer_numbers(layer, peak, reps_step=3):
+    """The prefill round trip, the lock-step window, the step kernel alone and the flush alone, on a layer whose main
+    measurement is done.  Leaves every window empty."""
+    wl, B = layer.wl, layer.B
+    L, HV, R, kda = wl["L"], wl["HV"], wl["R"], wl["kda"]
+    gqa = HV // wl["H"]
+    st = layer.st
+    layer.to_lockstep()                                          # warm-up of the two kernels; windows empty
+    for t in range(3):
+        layer.decode_resident(t)                                 # a few live entries for the dequantize to fold in
+    deq_s, qnt_s = layer.to_lockstep()
+    rt = B * HV * roundtrip_bytes(R)
+    out = {"prefill_round_trip": {"dequantize_ms": 1e3 * deq_s, "quantize_ms": 1e3 * qnt_s,
+                                  "dequantize_gbs": rt / deq_s / 1e9, "quantize_gbs": rt / qnt_s / 1e9,
+                                  "dequantize_frac_of_measured_hbm": rt / deq_s / 1e9 / peak,
+                                  "quantize_frac_of_measured_hbm": rt / qnt_s / 1e9 / peak,
+                                  "bytes_per_head": roundtrip_bytes(R)}}
+    # lock-step: every head flushes on the same step (the graph is the one captured for the staggered run)
+    dt_l, reps_l = replay_timed(layer.graph, 1, 0.1)
+    amort = window_bytes_per_head_step(L, R, gqa, kda)
+    out["lockstep"] = {"ms_per_step": 1e3 * dt_l / (reps_l * L), "value": B * HV * reps_l * L / dt_l, "steps": reps_l * L,
+                       "frac_of_measured_hbm": B * HV * reps_l * L / dt_l * amort / 1e9 / peak,
+                       "note": "all windows in phase: every head flushes on the same step, once per window"}
+    # the step kernel alone over one lock-step window (h = 0 .. L-1), state restored between repetitions
+    bufs = (layer.ssm, st.Kbuf, st.Ubuf, st.Wbuf, st.Pbuf, st.hcnt) + ((st.Gbuf,) if kda else ())
+    snap = [t.clone() for t in bufs]
+    tk = 0.0
+    for r in range(reps_step + 1):
+        for dst, src in zip(bufs, snap):
+            dst.copy_(src)
+        torch.cuda.synchronize()
+
+        def body_k():
+            for t in range(L):
+                layer.step_only(t)
+
+        x = timed(body_k)
+        if r > 0:
+            tk += x
+    step_ms = 1e3 * tk / (reps_step * L)
+    alg_step = B * HV * sum(step_bytes(h, L, R, gqa, kda) for h in range(L)) / L
+    out["step_kernel"] = {"kernel": "step_pipelined_kernel (no flush tail)", "ms_per_launch": step_ms,
+                          "alg_bytes_per_launch": alg_step, "achieved": alg_step / (step_ms * 1e-3) / 1e9, "unit": "GB/s",
+                          "frac": alg_step / (step_ms * 1e-3) / 1e9 / peak, "frac_of_8tbs": alg_step / (step_ms * 1e-3) / 1e9 / 8000.0,
+                          "note": "one lock-step window h = 0 .. L-1, %d repetitions" % reps_step}
+    # the flush kernel alone: every head due (state left by the last pass above), then nothing due
+    flush_all_s = timed(layer.flush_only)
+    flush_idle_s = timed(lambda: [layer.flush_only() for _ in range(20)]) / 20
+    out["flush"] = {"all_due_ms": 1e3 * flush_all_s, "none_due_ms": 1e3 * flush_idle_s, "heads": B * HV,
+                    "all_due_gbs": B * HV * flush_bytes(L, R, kda) / flush_all_s / 1e9,
+                    "all_due_frac_of_measured_hbm": B * HV * flush_bytes(L, R, kda) / flush_all_s / 1e9 / peak}
+    for dst, src in zip(bufs, snap):
+        dst.copy_(src)
+    del snap
+    return out
+
+
+def outlier_quantize(layer, peak):
+    """The isolated quantize on fp32 states drawn as N(0,1) with 1 % of the rows and of the columns scaled by 50."""
+    wl, B = layer.wl, layer.B
+    HV, R = wl["HV"], wl["R"]
+    g = torch.Generator(device=layer.device).manual_seed(77)
+    S = layer.ssm
+    for s0 in range(0, S.shape[0], 64):
+        n = min(64, S.shape[0] - s0)
+        x = torch.randn(n, HV, V, K, generator=g, device=layer.device)
+        rsel = torch.rand(n, HV, V, 1, generator=g, device=layer.device) < 0.01
+        csel = torch.rand(n, HV, 1, K, generator=g, device=layer.device) < 0.01
+        S[s0:s0 + n] = x * torch.where(rsel, 50.0, 1.0) * torch.where(csel, 50.0, 1.0)
+    q_s = timed(lambda: layer.st.quantize(layer.ssm, layer.idx))
+    by = B * HV * roundtrip_bytes(R)
+    return {"heads": B * HV, "quantize_ms": 1e3 * q_s, "gbs": by / q_s / 1e9, "frac_of_measured_hbm": by / q_s / 1e9 / peak,
+            "states": "N(0,1), 1 % of rows and of columns x 50", "iters": 3 if wl["kda"] else 1}
+
+
+def run_config3(world, rank, device, peak, barrier):
+    """48 GDN layers x 32 value heads, 1 024 sequences split over the ranks (strong scaling), staggered fill levels, one
+    window period of decode steps per layer group.  On one GPU the 48 layer states (3.3 GB each at 1 024 sequences) do not
+    fit next to each other, so the layers are timed in groups and the group times are added."""
+    from leapquant_b200.sharding import job_times, shard_rows
+    wl = WORKLOADS["gdn"]
+    L, HV, R = wl["L"], wl["HV"], wl["R"]
+    NL, BT = 48, 1024
+    r0, r1 = shard_rows(BT, world, rank)
+    Bl = r1 - r0
+    # every layer has its own state; the per-step inputs (1 GB per window period at 1 024 sequences) come from four sets
+    # that the layers take in turn, so that consecutive layers never read the same rows
+    inputs = [device_inputs(Bl, wl["H"], HV, L, 900 + 13 * rank + i, False, device) for i in range(4)]
+    per_layer = (Bl + 9) * HV * (4 * V * K + L * (2 * K + 2 * V + 4) + 8)
+    free, _ = torch.cuda.mem_get_info(device)
+    ngroups = -(-NL // max(1, min(NL, int((free * 0.85) // per_layer))))
+    group = -(-NL // ngroups)
+    total_s = 0.0
+    done = 0
+    for gi in range(ngroups):
+        nl = min(group, NL - gi * group)
+        layers = [Layer(wl, Bl, device, seed=1000 + 97 * rank + gi * group + i, host_io=False, device_rng=True,
+                        inputs=inputs[(gi * group + i) % 4]) for i in range(nl)]
+        for ly in layers:
+            ly.stagger()
+        torch.cuda.synchronize()
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph):
+            for t in range(L):
+                for ly in layers:                                # a decode step of the model: every layer once
+                    ly.decode_resident(t)
+        graph.replay()
+        barrier()
+        dt = timed(graph.replay)
+        total_s += dt
+        done += nl
+        del graph, layers
+        torch.cuda.empty_cache()
+    total_s = job_times([total_s], device)[0]
+    amort = window_bytes_per_head_step(L, R, HV // wl["H"], False)
+    units = BT * HV * NL * L
+    return {"layers": NL, "sequences": BT, "sequences_per_gpu": Bl, "steps": L, "layer_groups": ngroups, "layers_per_group": group,
+            "ms_per_model_step": 1e3 * total_s / L, "value": units / total_s, "unit": "head-steps/s",
+            "model_decode_steps_per_s": L / total_s, "gbs_per_gpu": units / total_s * amort / 1e9 / world,
+            "frac_of_measured_hbm_per_gpu": units / total_s * amort / 1e9 / world / peak, "scaling": "strong",
+            "note": "all 48 layers per step; group times added when the states of all layers do not fit at once"}
+
+
 def run_b200(args, wl):
     import torch.distributed as dist
+    from leapquant_b200.sharding import job_times
     world = int(os.environ.get("WORLD_SIZE", "1"))
     rank = int(os.environ.get("RANK", "0"))
     local = int(os.environ.get("LOCAL_RANK", "0"))
@@ -281,8 +550,12 @@ def run_b200(args, wl):
     L, HV, R, kda = wl["L"], wl["HV"], wl["R"], wl["kda"]
     gqa = HV // wl["H"]
     steps, warm = args.steps, max(args.warmup, 3)
-    layer = Layer(wl, B, device, seed=100 + rank)
-    stream = torch.cuda.current_stream()
+    peaks = {}
+    try:
+        peaks = json.load(open(os.path.join(ROOT, "MEASURED_PEAKS.json")))
+    except Exception:
+        pass
+    peak = float(peaks.get("hbm_gbs", 6650.0))
 
     def barrier():
         torch.cuda.synchronize()
@@ -290,39 +563,27 @@ def run_b200(args, wl):
             dist.barrier()
         torch.cuda.synchronize()
 
-    # ---- warm-up (eager), then capture one window of L steps in a CUDA graph ----
-    for t in range(L):                                          # a whole window: every head flushes once, hcnt returns to 0
+    layer = Layer(wl, B, device, seed=100 + rank)
+    for t in range(max(warm, 3)):                               # eager warm-up steps (module load, first-launch set-up)
         layer.decode_resident(t)
-    torch.cuda.synchronize()
-    graph = torch.cuda.CUDAGraph()
-    with torch.cuda.graph(graph):
-        for t in range(L):
-            layer.decode_resident(t)
-    nwin_w, nwin = -(-warm // L), max(1, steps // L)
-    rem = steps - nwin * L if steps >= L else 0
-    if steps < L:                                               # fewer steps than a window: run them eagerly
-        nwin, rem = 0, steps
-    for _ in range(nwin_w):
-        graph.replay()
+    layer.to_lockstep()
     sampler = ClockSampler(visible_to_nvml_index(local)) if rank == 0 else None
-    barrier()
+    layer.stagger()
+    layer.capture()
+    nwin_w = max(1, -(-warm // L))
+    for _ in range(nwin_w):
+        layer.graph.replay()
     if sampler:
         sampler.start()
-
-    def body():
-        for _ in range(nwin):
-            graph.replay()
-        for t in range(rem):
-            layer.decode_resident(t)
-
-    dt = timed(body, torch.cuda.current_stream())
+    nwin = max(1, -(-steps // L))
+    dt, reps = replay_timed(layer.graph, nwin, MIN_TIMED_S, barrier)
+    done = reps * L
     barrier()
-    if rem:                                                     # finish the partial window so that hcnt returns to 0
-        for t in range(rem, L):
-            layer.decode_resident(t)
-    # ---- end to end through the public API with host buffers ----
-    e2e_steps = min(steps, 4 * L)
-    e2e_steps -= e2e_steps % L if e2e_steps >= L else 0
+    ok, pdetail = parity_check(layer, [0, 1, B // 2, B - 1])
+
+    # ---- end to end through the public API with host buffers (same staggered state) ----
+    per_e2e = max(dt / done, 1e-6) * 2.2                       # a host-fed step costs about twice a resident one
+    e2e_steps = L * max(1, int(math.ceil(0.3 / per_e2e / L)))
     for t in range(L):                                          # warm-up: one whole window through the host path
         layer.decode_host(t)
     layer.staged.drain()
@@ -333,87 +594,96 @@ def run_b200(args, wl):
             layer.decode_host(t)
         layer.staged.join()                                     # the timed stream waits for the last output copy
 
-    dt_e2e = timed(body_e2e, torch.cuda.current_stream())
+    dt_e2e = timed(body_e2e)
     barrier()
-    if e2e_steps % L:
-        for t in range(e2e_steps % L, L):
-            layer.decode_resident(t)
     clocks = sampler.finish() if sampler else None
-
-    # ---- the step kernel alone over one window (roofline) ----
-    snap = [t.clone() for t in (layer.ssm, layer.st.Kbuf, layer.st.Ubuf, layer.st.Wbuf, layer.st.Pbuf, layer.st.hcnt)]
-    reps, tk = 3, 0.0
-    for r in range(reps + 1):
-        for dst, src in zip((layer.ssm, layer.st.Kbuf, layer.st.Ubuf, layer.st.Wbuf, layer.st.Pbuf, layer.st.hcnt), snap):
-            dst.copy_(src)
-        if kda:
-            layer.st.Gbuf.fill_(1.0)
-        torch.cuda.synchronize()
-
-        def body_k():
-            for t in range(L):
-                layer.step_only(t)
-
-        x = timed(body_k, torch.cuda.current_stream())
-        if r > 0:
-            tk += x
-    step_ms = 1e3 * tk / (reps * L)
-    # ---- the flush kernel alone: every head due (state left by the last pass above), then nothing due ----
-    flush_all_ms = 1e3 * timed(lambda: layer.flush_only(), torch.cuda.current_stream())
-
-    def body_f():
-        for _ in range(20):
-            layer.flush_only()
-
-    flush_idle_ms = 1e3 * timed(body_f, torch.cuda.current_stream()) / 20
-    # ---- the prefill round trip: dequantize every slot to fp32, quantize it again (65 536 B fp32 + the checkpoint per head) ----
-    layer.st.dequantize(layer.ssm, layer.idx)
-    layer.st.quantize(layer.ssm, layer.idx)
-    deq_ms = 1e3 * timed(lambda: layer.st.dequantize(layer.ssm, layer.idx), torch.cuda.current_stream())
-    quant_ms = 1e3 * timed(lambda: layer.st.quantize(layer.ssm, layer.idx), torch.cuda.current_stream())
-    rt_bytes = B * HV * (4 * V * K + K * V + 4 * (K + V) + 2 * R * (K + V))
-    alg_launch = B * HV * sum(step_bytes(h, L, R, gqa, kda) for h in range(L)) / L
-    peaks = {}
-    try:
-        peaks = json.load(open(os.path.join(ROOT, "MEASURED_PEAKS.json")))
-    except Exception:
-        pass
-    peak = float(peaks.get("hbm_gbs", 6650.0))
-    achieved = alg_launch / (step_ms * 1e-3) / 1e9
-    traffic = NCU_TRAFFIC_RATIO["kda" if kda else "gdn"]
-
-    from leapquant_b200.sharding import job_times
     dt, dt_e2e = job_times([dt, dt_e2e], device)               # max over ranks
-    done = nwin * L + rem
     units = world * B * HV * done
     value = units / dt
-    e2e_value = world * B * HV * e2e_steps / dt_e2e if e2e_steps else None
+    e2e_value = world * B * HV * e2e_steps / dt_e2e
+
+    extras = {}
+    if not args.only_main:
+        extras.update(secondary_layer_numbers(layer, peak))
+        if world == 1 and not args.batch:
+            other = WORKLOADS["kda" if not kda else "gdn"]
+            key = "kda" if not kda else "gdn"
+            del layer.graph
+            ly2 = Layer(other, other["B"], device, seed=300, host_io=False)
+            for t in range(3):
+                ly2.decode_resident(t)
+            ly2.to_lockstep()
+            dt2, done2, reps2 = measure_staggered(ly2, other["L"], 0.25)
+            ok2, pd2 = parity_check(ly2, [0, other["B"] - 1])
+            am2 = window_bytes_per_head_step(other["L"], other["R"], other["HV"] // other["H"], other["kda"])
+            v2 = other["B"] * other["HV"] * done2 / dt2
+            sec2 = secondary_layer_numbers(ly2, peak)
+            extras[key] = {"workload": other["name"], "batch": other["B"], "value": v2, "unit": "head-steps/s", "steps": done2,
+                           "ms_per_step": 1e3 * dt2 / done2, "alg_bytes_per_head_step": am2,
+                           "roofline": {"bound": "hbm", "kernel": "step_pipelined_kernel<FUSE> (decode)", "achieved": v2 * am2 / 1e9,
+                                        "peak": peak, "unit": "GB/s", "frac": v2 * am2 / 1e9 / peak, "frac_of_8tbs": v2 * am2 / 1e9 / 8000.0,
+                                        "ms_per_launch": 1e3 * dt2 / done2},
+                           "parity_check": "ok" if ok2 else "fail", "parity_detail": pd2, **sec2,
+                           "isolated_quantize_outlier_states": outlier_quantize(ly2, peak)}
+            del ly2
+            torch.cuda.empty_cache()
+            sweep = []
+            for Bs in (1, 8, 32, 128, 256):
+                lys = Layer(wl, Bs, device, seed=400 + Bs, host_io=False)
+                for t in range(3):
+                    lys.decode_resident(t)
+                lys.to_lockstep()
+                dts, dones, _ = measure_staggered(lys, L, 0.1)
+                am = window_bytes_per_head_step(L, R, gqa, kda)
+                vs = Bs * HV * dones / dts
+                sweep.append({"batch": Bs, "ms_per_step": 1e3 * dts / dones, "value": vs, "decode_steps_per_s": dones / dts,
+                              "gbs": vs * am / 1e9, "frac_of_measured_hbm": vs * am / 1e9 / peak, "steps": dones})
+                del lys
+                torch.cuda.empty_cache()
+            extras["batch_sweep"] = sweep
+        if not args.batch:
+            del layer.graph
+            layer.graph = None
+            del layer
+            torch.cuda.empty_cache()
+            extras["config3"] = run_config3(world, rank, device, peak, barrier)
+
     if rank == 0:
-        cpu_rate, cpu_dt, cpu_sample = cpu_oracle_rate(wl, L, 3, nseq=8) if world == 1 else (None, None, None)
+        cpu_rate, cpu_dt, cpu_sample = cpu_oracle_rate(wl, L, 3, nseq=32) if world == 1 else (None, None, None)
         amort = window_bytes_per_head_step(L, R, gqa, kda)
+        alg_launch = B * HV * amort                              # every staggered step sees each fill level B * HV / L times
+        ms_step = 1e3 * dt / done
+        achieved = alg_launch / (ms_step * 1e-3) / 1e9
+        traffic = NCU_TRAFFIC_RATIO["kda" if kda else "gdn"]
+        h2d, d2h = layer_h2d_d2h(wl, B)
         line = {"metric": "int8_state_decode_head_steps_per_s", "value": value, "unit": "head-steps/s", "n_gpus": world,
-                "steps": done, "warmup": nwin_w * L, "ms_per_step": 1e3 * dt / done, "higher_is_better": True,
+                "steps": done, "warmup": nwin_w * L + max(warm, 3), "ms_per_step": ms_step, "higher_is_better": True,
                 "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
                 "config": {"workload": wl["name"], "batch_per_gpu": B, "value_heads": HV, "key_heads": wl["H"], "window": L,
                            "rank": R, "decode_steps_per_s_per_gpu": value / world / (B * HV),
+                           "fill_levels": "staggered: sequence n starts with n mod %d live entries, so every step reads the "
+                                          "window-average bytes and flushes %d heads" % (L, B * HV // L),
                            "alg_bytes_per_head_step": amort, "whole_path_gbs_per_gpu": value / world * amort / 1e9,
                            "whole_path_frac_of_measured_hbm": value / world * amort / 1e9 / peak,
                            "whole_path_frac_of_8tbs": value / world * amort / 1e9 / 8000.0,
                            "l2": "per-step working set %.0f MB exceeds the 126 MB L2" % (B * HV * amort / 1e6),
-                           "timing": "one window of %d steps captured in a CUDA graph, replayed" % L},
-                "e2e": {"value": e2e_value, "unit": "head-steps/s", "h2d_bytes_per_step": layer.h2d_bytes(),
-                        "d2h_bytes_per_step": layer.d2h_bytes(), "steps": e2e_steps},
-                "gpu_launches": (1 if layer.st.fused else 2) * done,
-                "roofline": {"bound": "hbm", "kernel": "step_pipelined_kernel", "achieved": achieved, "peak": peak,
-                             "unit": "GB/s", "frac": achieved / peak, "frac_of_8tbs": achieved / 8000.0,
-                             "traffic": (traffic * alg_launch) if traffic else None, "alg_bytes_per_launch": alg_launch,
-                             "ms_per_launch": step_ms, "peak_source": "MEASURED_PEAKS.json" if peaks else "fallback"},
-                "flush": {"all_due_ms": flush_all_ms, "none_due_ms": flush_idle_ms,
-                          "all_due_gbs": B * HV * flush_bytes(L, R, kda) / (flush_all_ms * 1e-3) / 1e9},
-                "prefill_round_trip": {"dequantize_ms": deq_ms, "quantize_ms": quant_ms,
-                                       "dequantize_gbs": rt_bytes / (deq_ms * 1e-3) / 1e9,
-                                       "quantize_gbs": rt_bytes / (quant_ms * 1e-3) / 1e9},
+                           "timing": "CUDA graph of %d decode steps (one launch each) replayed %d times as one timed region of "
+                                     "%.2f s; --steps %d rounded up to whole windows and to >= %.1f s" % (L, reps, dt, steps, MIN_TIMED_S),
+                           "reps": reps},
+                "e2e": {"value": e2e_value, "unit": "head-steps/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
+                        "steps": e2e_steps, "h2d_gbs_per_gpu": h2d * e2e_steps / dt_e2e / 1e9,
+                        "d2h_gbs_per_gpu": d2h * e2e_steps / dt_e2e / 1e9,
+                        "bound": "PCIe: every step moves its own inputs host->device and its output device->host; the "
+                                 "state stays on the device"},
+                "gpu_launches": done,
+                "roofline": {"bound": "hbm", "kernel": "step_pipelined_kernel<FUSE> (decode: step + flush tail, one launch per step)",
+                             "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
+                             "frac_of_8tbs": achieved / 8000.0, "traffic": (traffic * alg_launch) if traffic else None,
+                             "alg_bytes_per_launch": alg_launch, "ms_per_launch": ms_step,
+                             "peak_source": "MEASURED_PEAKS.json" if peaks else "fallback"},
+                "parity_check": "ok" if ok else "fail", "parity_detail": pdetail,
                 "clocks": clocks}
+        line.update(extras)
         if cpu_rate is not None:
             line["cpu_baseline"] = {"value": cpu_rate, "unit": "head-steps/s", "cores": os.cpu_count() or 1, "kind": "port",
                                     "sample": cpu_sample}
@@ -421,6 +691,14 @@ def run_b200(args, wl):
     if world > 1:
         dist.barrier()
         dist.destroy_process_group()
+
+
+def layer_h2d_d2h(wl, B):
+    H, HV, kda = wl["H"], wl["HV"], wl["kda"]
+    mixed = B * (2 * H * K + HV * V) * 2
+    a = B * HV * (K if kda else 1) * 2
+    b = B * HV * 2
+    return mixed + a + b, B * HV * V * 2
 
 
 def main():
@@ -431,13 +709,25 @@ def main():
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--workload", default="gdn", choices=sorted(WORKLOADS))
     ap.add_argument("--batch", type=int, default=0)
+    ap.add_argument("--only-main", action="store_true", help="skip the secondary keys (kda, batch_sweep, config3, ...)")
     ap.add_argument("--step-impl", type=int, default=-1, help="debug: step kernel driver (see lq_set_option)")
+    ap.add_argument("--profile-case", action="store_true",
+                    help="for a profiler: quantize, stagger the fill levels (L - 1 decode launches), 4 more decode launches, "
+                         "the prefill round trip once, exit; prints nothing")
     args = ap.parse_args()
     wl = WORKLOADS[args.workload]
     if args.step_impl >= 0:
         from leapquant_b200 import _lib
         _lib.set_option("step_impl", args.step_impl)
-    if args.impl == "reference":
+    if args.profile_case:
+        torch.cuda.set_device(0)
+        layer = Layer(wl, args.batch or wl["B"], torch.device("cuda", 0), seed=100, host_io=False)
+        layer.stagger()
+        for t in range(4):
+            layer.decode_resident(t)
+        layer.to_lockstep()
+        torch.cuda.synchronize()
+    elif args.impl == "reference":
         run_reference(args, wl)
     else:
         run_b200(args, wl)

@@ -47,6 +47,13 @@ def test_argument_errors_are_codes_not_crashes():
                       1, 0, 1, None) == -3                                                         # slot stride alignment
     mis = ctypes.c_void_p(260)
     assert L.lq_gdn_step(good, mis, one, one, one, one, one, one, one, one, one, one, one, one, 1, 0.0, None) == -3
+    # every entry point that moves the state with 128-bit accesses refuses a misaligned pointer before it launches
+    assert L.lq_quantize(good, mis, one, one, None, one, one, one, 1, 0, 1, None) == -3
+    assert L.lq_dequant(good, mis, one, one, one, one, None, one, one, 1, 0, None) == -3
+    assert L.lq_dequant(good, one, mis, one, one, one, None, one, one, 1, 0, None) == -3
+    assert L.lq_flush(good, mis, one, one, one, one, None, one, one, one, 1, 0, 1, None) == -3
+    assert L.lq_flush(good, one, one, mis, one, one, None, one, one, one, 1, 0, 1, None) == -3
+    assert L.lq_flush(good, one, one, one, one, one, mis, one, one, one, 1, 1, 1, None) == -3       # KDA: Gbuf
     # fused decode: the step's checks plus the flush's Q0 / iters
     dec = (good, one, one, one, one, one, one, one, one, one, one, one, one, one, 1, 0.0)
     assert L.lq_gdn_decode(*dec, None, 1, None) == -1                                                # NULL Q0

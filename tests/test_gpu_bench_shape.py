@@ -1,0 +1,154 @@
+"""GPU parity tests at the shape the benchmark runs: many programs per persistent CTA and many flushed heads per CTA.
+
+A B200 has 148 SMs and the step / decode kernels run one persistent CTA per SM, so a call with 1 280 (row, head) programs
+gives every CTA eight or nine programs: the byte ring wraps, the sixteen stage descriptors are reused with flipped
+parities, and -- when every window fills in the same call -- each CTA flushes eight or nine heads, four or five per team,
+in the shared memory the ring leaves behind.  The standalone flush with 1 280 due heads gives each of its 296 CTAs four or
+five heads.  The configurations are the benchmark's: GDN L = 64, R = 4, 16 key / 32 value heads and KDA L = 32, R = 8,
+32 heads.
+"""
+import pytest
+import torch
+
+from lq_testlib import CpuSide, GpuSide, assert_close, random_states
+from oracle import lq_oracle as O
+from test_gpu_parity import check_flush, compare_window, make_pair, step_inputs
+
+pytestmark = pytest.mark.gpu
+K = V = 128
+CONFIGS = [pytest.param(False, 64, 4, 16, 32, id="gdn_L64_R4_gqa2"), pytest.param(True, 32, 8, 32, 32, id="kda_L32_R8")]
+N_ROWS = 40                                   # 40 rows x 32 heads = 1 280 programs: 8.6 per CTA on 148 SMs
+
+
+def fill_windows(cpu, fill, seed):
+    """Plausible window contents with `fill[slot, head]` live entries per head (ragged or uniform)."""
+    b = cpu.bufs
+    NS, HV, L = cpu.NS, cpu.HV, cpu.L
+    g = torch.Generator().manual_seed(seed)
+    live = torch.arange(L)[None, None, :] < fill[..., None]
+    b.hcnt.copy_(fill.int())
+    b.Kbuf.copy_((torch.randn(NS, HV, L, K, generator=g) * 0.09).bfloat16())
+    b.Ubuf.copy_(torch.randn(NS, HV, L, V, generator=g).bfloat16())
+    b.Wbuf.copy_(torch.where(live, 0.2 + 0.8 * torch.rand(NS, HV, L, generator=g), torch.zeros(NS, HV, L)))
+    if cpu.kda:
+        b.Pbuf.copy_(-1.5 * torch.rand(NS, HV, K, generator=g))                             # cumulative log gate
+        e = (0.5 + 0.5 * torch.rand(NS, HV, L, K, generator=g)).half()                      # per-entry step factors
+        b.Gbuf.copy_(torch.where(live[..., None], e, torch.ones_like(e)))
+    else:
+        b.Pbuf.copy_(0.1 + 0.9 * torch.rand(NS, HV, 1, generator=g))
+
+
+def launch_step(gpu, kda, mixed, a, b_, A_log, dtb, idx, o):
+    st, vv = gpu.st, gpu.st.views(gpu.ssm)
+    N = mixed.shape[0]
+    args = (mixed.cuda(), a.reshape(N, st.HV, -1).contiguous().cuda(), b_.cuda(), A_log.cuda(),
+            dtb.reshape(st.HV, -1).contiguous().cuda(), vv["uq"], idx.cuda(), o)
+    if kda:
+        st.kstep(vv["q32"], vv["Sk"], vv["Sv"], vv["skv"], st.Kbuf, st.Ubuf, st.Wbuf, st.Pbuf, st.Gbuf, st.hcnt, *args)
+    else:
+        st.kstep(vv["q32"], vv["Sk"], vv["Sv"], vv["skv"], st.Kbuf, st.Ubuf, st.Wbuf, st.Pbuf, st.hcnt, *args)
+
+
+@pytest.mark.parametrize("kda,L,R,H,HV", CONFIGS)
+def test_step_ragged_fill_many_programs_per_cta(kda, L, R, H, HV):
+    """(i) One step of 1 280 programs at ragged fill levels (stages of 22 KB to 55 KB wrap the ring), null rows and full
+    windows in between, against the oracle from bit-identical inputs."""
+    N, NS = N_ROWS, N_ROWS + 2
+    cpu, gpu = make_pair(NS, HV, H, L, R, kda=kda, seed=11)
+    g = torch.Generator().manual_seed(1)
+    fill = torch.randint(0, L, (NS, HV), generator=g)
+    fill[5, 3] = L                                                         # a window that is already full: skipped, o = 0
+    fill_windows(cpu, fill, 2)
+    gpu.sync_from(cpu)
+    idx = torch.arange(1, N + 1, dtype=torch.int32)
+    idx[torch.randperm(N, generator=g)[:3]] = 0
+    mixed, a, b_, A_log, dtb = step_inputs(N, H, HV, 1, 5, kda)
+    A_log = A_log + 0.05 * torch.arange(HV)
+    o_c = torch.zeros(N, HV, V, dtype=torch.bfloat16)
+    o_g = torch.full((N, HV, V), 3.0, dtype=torch.bfloat16, device="cuda")
+    cpu.step(mixed[0], a[0], b_[0], A_log, dtb, idx, o_c)
+    launch_step(gpu, kda, mixed[0], a[0], b_[0], A_log, dtb, idx, o_g)
+    mag = float(o_c.float().abs().max())
+    assert_close(o_g.cpu(), o_c, 8e-3, 1e-4 + 1e-3 * mag, "outputs")
+    compare_window(cpu, gpu, list(range(NS)), "ragged batch")
+    from leapquant_b200 import _lib
+    torch.cuda.synchronize()
+    assert _lib.device_status() == 0
+
+
+@pytest.mark.parametrize("kda,L,R,H,HV", CONFIGS)
+def test_step_long_padded_tail(kda, L, R, H, HV):
+    """A CUDA-graph batch padded far beyond its live rows: 296 rows of which 40 are live, so every CTA meets runs of more
+    than sixteen consecutive dead programs (more than the stage descriptors it has)."""
+    N, NL, NS = 296, N_ROWS, N_ROWS + 1
+    cpu, gpu = make_pair(NS, HV, H, L, R, kda=kda, seed=12)
+    g = torch.Generator().manual_seed(3)
+    fill_windows(cpu, torch.randint(0, L, (NS, HV), generator=g), 4)
+    gpu.sync_from(cpu)
+    idx = torch.zeros(N, dtype=torch.int32)
+    idx[:NL // 2] = torch.arange(1, NL // 2 + 1, dtype=torch.int32)        # live rows at both ends, padding in between
+    idx[-(NL - NL // 2):] = torch.arange(NL // 2 + 1, NL + 1, dtype=torch.int32)
+    mixed, a, b_, A_log, dtb = step_inputs(N, H, HV, 1, 6, kda)
+    o_c = torch.zeros(N, HV, V, dtype=torch.bfloat16)
+    o_g = torch.full((N, HV, V), 3.0, dtype=torch.bfloat16, device="cuda")
+    cpu.step(mixed[0], a[0], b_[0], A_log, dtb, idx, o_c)
+    launch_step(gpu, kda, mixed[0], a[0], b_[0], A_log, dtb, idx, o_g)
+    mag = float(o_c.float().abs().max())
+    assert_close(o_g.cpu(), o_c, 8e-3, 1e-4 + 1e-3 * mag, "outputs")
+    assert float(o_g[NL // 2: N - (NL - NL // 2)].float().abs().max()) == 0.0, "padding rows must write zeros"
+    compare_window(cpu, gpu, list(range(NS)), "padded batch")
+    from leapquant_b200 import _lib
+    torch.cuda.synchronize()
+    assert _lib.device_status() == 0
+
+
+def all_windows_one_short(kda, L, R, H, HV, seed):
+    """CPU state with every window of slots 1 .. N_ROWS one entry short of full, filled by running the oracle for L - 1
+    steps (mild decay, so that the rebuilt state keeps a well-conditioned spectrum), and the inputs of the filling step."""
+    N, NS = N_ROWS, N_ROWS + 1
+    cpu = CpuSide(NS, HV, H, K, V, L, R, kda=kda)
+    cpu.ssm.copy_(random_states(NS, HV, V, K, seed))
+    idx = torch.arange(1, N + 1, dtype=torch.int32)
+    cpu.quantize(idx)
+    mixed, a, b_, A_log, dtb = step_inputs(N, H, HV, L, seed + 1, kda, gate_shift=4.0)
+    o = torch.zeros(N, HV, V, dtype=torch.bfloat16)
+    for t in range(L - 1):
+        cpu.step(mixed[t], a[t], b_[t], A_log, dtb, idx, o)
+    return cpu, idx, (mixed[L - 1], a[L - 1], b_[L - 1], A_log, dtb)
+
+
+@pytest.mark.parametrize("kda,L,R,H,HV", CONFIGS)
+def test_decode_every_window_fills(kda, L, R, H, HV):
+    """(ii) One decode call in which all 1 280 windows fill: every CTA of the fused kernel flushes eight or nine heads, each
+    team four or five, one after the other in the same shared memory.  Bit-identical to the step kernel followed by the
+    flush kernel."""
+    cpu, idx, (mixed, a, b_, A_log, dtb) = all_windows_one_short(kda, L, R, H, HV, 21)
+    gpu_f, gpu_s = GpuSide(cpu), GpuSide(cpu)
+    gpu_s.st.fused = False
+    N = idx.numel()
+    o_f = torch.zeros(N, HV, V, dtype=torch.bfloat16, device="cuda")
+    o_s = torch.zeros_like(o_f)
+    for gsd, o in ((gpu_f, o_f), (gpu_s, o_s)):
+        gsd.st.decode(gsd.ssm, mixed.cuda(), a.cuda(), b_.cuda(), A_log.cuda(), dtb.cuda(), idx.cuda(), o)
+    bits = lambda x: x.view(torch.int32) if x.dtype == torch.float32 else x.view(torch.int16) if x.element_size() == 2 else x
+    assert int(gpu_f.st.hcnt[1:].abs().max()) == 0, "every window must have been flushed"
+    assert torch.equal(bits(o_f), bits(o_s))
+    for name in ("Kbuf", "Ubuf", "Wbuf", "Pbuf", "hcnt") + (("Gbuf",) if kda else ()):
+        assert torch.equal(bits(getattr(gpu_f.st, name)), bits(getattr(gpu_s.st, name))), name
+    assert torch.equal(bits(gpu_f.ssm), bits(gpu_s.ssm))
+    from leapquant_b200 import _lib
+    torch.cuda.synchronize()
+    assert _lib.device_status() == 0
+
+
+@pytest.mark.parametrize("kda,L,R,H,HV", CONFIGS)
+def test_flush_many_due_heads_per_cta(kda, L, R, H, HV):
+    """(iii) The standalone flush with 1 280 due heads (more than its 296 CTAs: each flushes four or five), stage by stage
+    against the oracle from bit-identical inputs."""
+    cpu, idx, (mixed, a, b_, A_log, dtb) = all_windows_one_short(kda, L, R, H, HV, 23)
+    o = torch.zeros(idx.numel(), HV, V, dtype=torch.bfloat16)
+    cpu.step(mixed, a, b_, A_log, dtb, idx, o)                             # the filling step, on the oracle
+    assert int(cpu.bufs.hcnt[1:].min()) == L
+    gpu = GpuSide(cpu)
+    check_flush(cpu, gpu, idx, list(range(1, N_ROWS + 1)), f"flush of 1280 heads kda={kda}")
+    assert int(gpu.st.hcnt.abs().max()) == 0
