@@ -608,7 +608,7 @@ def run_b200(args, wl):
         if world == 1 and not args.batch:
             other = WORKLOADS["kda" if not kda else "gdn"]
             key = "kda" if not kda else "gdn"
-            del layer.graph
+            layer.graph = None
             ly2 = Layer(other, other["B"], device, seed=300, host_io=False)
             for t in range(3):
                 ly2.decode_resident(t)
@@ -642,7 +642,6 @@ def run_b200(args, wl):
                 torch.cuda.empty_cache()
             extras["batch_sweep"] = sweep
         if not args.batch:
-            del layer.graph
             layer.graph = None
             del layer
             torch.cuda.empty_cache()
