@@ -149,5 +149,7 @@ def test_flush_many_due_heads_per_cta(kda, L, R, H, HV):
     cpu.step(mixed, a, b_, A_log, dtb, idx, o)                             # the filling step, on the oracle
     assert int(cpu.bufs.hcnt[1:].min()) == L
     gpu = GpuSide(cpu)
-    check_flush(cpu, gpu, idx, list(range(1, N_ROWS + 1)), f"flush of 1280 heads kda={kda}")
+    # (21 million codes: the worst evaluation noise of the rebuilt state over that many elements is several times the typical
+    #  one, so the distance from a rounding boundary within which a code may differ is 0.05 code units here)
+    check_flush(cpu, gpu, idx, list(range(1, N_ROWS + 1)), f"flush of 1280 heads kda={kda}", code_tol=5e-2)
     assert int(gpu.st.hcnt.abs().max()) == 0

@@ -69,7 +69,13 @@ def check_quantized(S, got, ref, what):
     prod = lambda uq: torch.einsum("...rv,...rc->...vc", uq.float()[..., K:], uq.float()[..., :K])
     deq = lambda d: d["Sq"].float() / 127.0 * d["Sk"][..., None, :] * d["Sv"][..., :, None] + prod(d["uq"])
     close(prod(got["uq"]), prod(ref["uq"]), 1e-3, 2e-3 * mag, what + ": Q U^T")
-    close(deq(got), deq(ref), 1e-3, 2e-3 * mag, what + ": dequantised state")
+    # Dequantised state.  The two sets of factors differ at fp32 rounding level, so a residual that sits on a rounding
+    # boundary may become the neighbouring code: fewer than 0.1 % of the elements may be off by up to one code step.
+    err = (deq(got) - deq(ref)).abs()
+    lim = 2e-3 * mag + 1e-3 * deq(ref).abs()
+    step = ref["Sk"][..., None, :] * ref["Sv"][..., :, None] / 127.0
+    assert bool((err <= lim + 1.01 * step).all()), f"{what}: dequantised state off by more than one code step ({float(err.max()):.3e})"
+    assert int((err > lim).sum()) <= 1e-3 * err.numel(), f"{what}: {int((err > lim).sum())} elements beyond the tolerance"
     assert float((deq(ref) - S).abs().max()) <= 2e-2 * mag                  # (the reference's own checkpoint is that close)
 
 
