@@ -124,6 +124,53 @@ __device__ __forceinline__ uint4 ldg_stream(const void* p) {
     return r;
 }
 
+// ---- mbarriers, bounded waits, bulk copies (shared by the step and the flush kernels) ----
+constexpr uint32_t WAIT_LIMIT = 1u << 22;      // bounded spin: ~seconds at worst, then the kernel records a status and leaves
+constexpr int ST_PRODUCER_TIMEOUT = 1, ST_CONSUMER_TIMEOUT = 2, ST_PROLOGUE_TIMEOUT = 4, ST_FLUSH_TIMEOUT = 8;
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return uint32_t(__cvta_generic_to_shared(p)); }
+__device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive_expect_tx(uint64_t* bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n"
+        ".reg .pred p;\n"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n"
+        "selp.u32 %0, 1, 0, p;\n"
+        "}\n"
+        : "=r"(ok)
+        : "r"(smem_u32(bar)), "r"(parity)
+        : "memory");
+    return ok != 0;
+}
+// A whole warp waits for the phase with the given parity: lane 0 tests the barrier, the outcome is broadcast, and every
+// lane takes the same branch, so the warp stays converged (a lane that spins alone leaves the warp split in two, and every
+// later warp-synchronous shuffle then costs a rendezvous of the halves).  Gives up after WAIT_LIMIT polls.
+__device__ __forceinline__ bool warp_wait_bounded(uint64_t* bar, uint32_t parity, int lane) {
+    for (uint32_t it = 0; it < WAIT_LIMIT; ++it) {
+        uint32_t ok = 0;
+        if (lane == 0) ok = mbar_try_wait(bar, parity) ? 1u : 0u;
+        ok = __shfl_sync(0xffffffffu, ok, 0);
+        if (ok) return true;
+    }
+    return false;
+}
+// bulk asynchronous copy global -> this CTA's shared memory, completion counted in bytes on `bar`
+__device__ __forceinline__ void bulk_g2s(void* dst, const void* src, uint32_t bytes, uint64_t* bar) {
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(smem_u32(dst)),
+                 "l"(src), "r"(bytes), "r"(smem_u32(bar))
+                 : "memory");
+}
+__device__ __forceinline__ void fence_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
+
 // ---- host-side helpers ----
 int device_sm_count();
 int ensure_smem(const void* func, size_t bytes);

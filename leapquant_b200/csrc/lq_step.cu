@@ -661,52 +661,6 @@ __global__ void __launch_bounds__(GT, 2) step_direct_kernel(StepParams P) {
 // ------------------------------------------------------------------------------------------------------------------
 // driver 2: persistent CTAs, producer warp + bulk asynchronous copies into a ring of stages
 // ------------------------------------------------------------------------------------------------------------------
-constexpr uint32_t WAIT_LIMIT = 1u << 22;      // bounded spin: ~seconds at worst, then the kernel records a status and leaves
-constexpr int ST_PRODUCER_TIMEOUT = 1, ST_CONSUMER_TIMEOUT = 2, ST_PROLOGUE_TIMEOUT = 4;
-
-__device__ __forceinline__ uint32_t smem_u32(const void* p) { return uint32_t(__cvta_generic_to_shared(p)); }
-__device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {
-    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count) : "memory");
-}
-__device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
-    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
-}
-__device__ __forceinline__ void mbar_arrive_expect_tx(uint64_t* bar, uint32_t bytes) {
-    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
-}
-__device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
-    uint32_t ok;
-    asm volatile(
-        "{\n"
-        ".reg .pred p;\n"
-        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n"
-        "selp.u32 %0, 1, 0, p;\n"
-        "}\n"
-        : "=r"(ok)
-        : "r"(smem_u32(bar)), "r"(parity)
-        : "memory");
-    return ok != 0;
-}
-// A whole warp waits for the phase with the given parity: lane 0 tests the barrier, the outcome is broadcast, and every
-// lane takes the same branch, so the warp stays converged (a lane that spins alone leaves the warp split in two, and every
-// later warp-synchronous shuffle then costs a rendezvous of the halves).  Gives up after WAIT_LIMIT polls.
-__device__ __forceinline__ bool warp_wait_bounded(uint64_t* bar, uint32_t parity, int lane) {
-    for (uint32_t it = 0; it < WAIT_LIMIT; ++it) {
-        uint32_t ok = 0;
-        if (lane == 0) ok = mbar_try_wait(bar, parity) ? 1u : 0u;
-        ok = __shfl_sync(0xffffffffu, ok, 0);
-        if (ok) return true;
-    }
-    return false;
-}
-// bulk asynchronous copy global -> this CTA's shared memory, completion counted in bytes on `bar`
-__device__ __forceinline__ void bulk_g2s(void* dst, const void* src, uint32_t bytes, uint64_t* bar) {
-    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(smem_u32(dst)),
-                 "l"(src), "r"(bytes), "r"(smem_u32(bar))
-                 : "memory");
-}
-__device__ __forceinline__ void fence_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
-
 // warp 0: producer (places stages, publishes scalars), warp 1: copy issue, warp 2: prologue, warps 3 ..: NG consumer groups
 // of GW warps.
 // Shared memory: [ring of `ring_bytes`][NG group scratches][ND x (full, normed, empty) mbarriers][ND stage offsets][NG flags]
@@ -972,24 +926,49 @@ __global__ void __launch_bounds__(UT + NG * GT, 1) step_pipelined_kernel(StepPar
     };
     run_roles();
 
-    // ================= fused flush: the heads whose window this CTA just filled, two teams of 256 threads =================
+    // ================= fused flush: the heads whose window this CTA just filled =================
+    // While at least two heads are left the CTA works as two teams of 8 warps, each flushing one head in its own work area
+    // (carved from the dead ring) with its own 128 columns of tensor memory; a last single head -- or every head, when the
+    // ring has room for one work area only -- is flushed by all 16 warps as one team, which halves the stages that are
+    // parallel over the tile.  A serving batch whose sequences fill their windows at different steps gives most CTAs exactly
+    // one head per step, and the latency of that flush is what the step pays.
     if constexpr (FUSE) {
+        __shared__ uint32_t tm_slot;
         __syncthreads();                                         // every role is done; the ring is dead, this CTA's global writes are visible
         if (*abortf) return;
         const int ndl = *dl_n;
-        // a team is exactly 256 threads (its named barrier counts them): threads beyond the last whole team leave
-        constexpr int MAX_TEAMS = (UT + NG * GT) / 256;
-        static_assert(MAX_TEAMS >= 1, "the fused flush needs at least 256 threads");
-        const int nteams = ft.teams < MAX_TEAMS ? ft.teams : MAX_TEAMS;
+        if (ndl == 0) return;                                    // (before any tensor memory is held)
+        static_assert(UT + NG * GT == 512, "the fused flush is written for two teams of 256 threads");
+        const int nteams = ft.teams;                             // work areas that fit in the ring: 1 or 2
         const int team = tid >> 8, ttid = tid & 255;
-        if (ndl == 0 || team >= nteams) return;
-        const FlushSmem fs = flush_carve<R>(stage_smem + team * ft.team_bytes, L, KDA);
-        flush_init<R>(fs, ft.Q0, ttid);
+        if (warp == 0) tmem_alloc(&tm_slot, 2 * TMEM_COLS);
+        const FlushSmem fs = flush_carve<R>(stage_smem + (team < nteams ? team : 0) * ft.team_bytes, L, KDA);
+        if (team < nteams) flush_init<R>(fs, ft.Q0, ttid, 256);
+        tc_fence_before_sync();
+        __syncthreads();
+        tc_fence_after_sync();
+        const uint32_t tm = tm_slot;
         FlushArgs A;
         A.d = P.d; A.ssm = P.ssm; A.Kbuf = P.Kbuf; A.Ubuf = P.Ubuf; A.Wbuf = P.Wbuf; A.Pbuf = P.Pbuf; A.Gbuf = P.Gbuf;
         A.hcnt = P.hcnt; A.Q0 = ft.Q0; A.iters = ft.iters;
-        auto tsync = [&] { named_bar(8 + team, 256); };
-        for (int k = team; k < ndl; k += nteams) flush_head<R, KDA>(fs, A, dl[k], ttid, tsync);
+        int k = 0;
+        if (nteams == 2) {
+            auto tsync = [&] { named_bar(8 + team, 256); };
+            const int npair = ndl >> 1;
+            bool ok = true;
+            for (int i = 0; i < npair && ok; ++i) ok = flush_head<R, KDA, 8>(fs, A, dl[2 * i + team], ttid, tm + team * TMEM_COLS, tsync);
+            if (!ok && ttid == 0) *abortf = 1;
+            k = 2 * npair;
+            __syncthreads();
+        }
+        if (k < ndl && *abortf == 0) {
+            const FlushSmem f0 = flush_carve<R>(stage_smem, L, KDA);      // team 0's area, initialised above
+            for (; k < ndl; ++k)
+                if (!flush_head<R, KDA, 16>(f0, A, dl[k], tid, tm, [] { __syncthreads(); })) break;
+        }
+        tc_fence_before_sync();
+        __syncthreads();
+        if (warp == 0) tmem_dealloc(tm, 2 * TMEM_COLS);
     }
 }
 
@@ -1022,7 +1001,7 @@ static int launch_step(const StepParams& P, cudaStream_t st, const FuseTail* fus
     const int nprog = P.N * P.d.HV;
     const int grid = nprog < device_sm_count() ? nprog : device_sm_count();
     const int nit_max = (nprog + grid - 1) / grid;
-    const size_t budget = 227 * 1024;
+    const size_t budget = 227 * 1024 - 256;                      // (the kernel also has a few bytes of static shared memory)
     const size_t fixed = size_t(NG) * SCRATCH_BYTES + 4 * ND * sizeof(uint64_t) + (2 * ND + NG + 4) * sizeof(int) + 32 * sizeof(ProgScalars) +
                          (4 + size_t(nit_max)) * sizeof(int);
     const int lay_p = stage_layout(P.d.L, P.d.L, R, KDA, false).bytes;
