@@ -218,6 +218,39 @@ __device__ __forceinline__ void tall_product(const uint16_t* __restrict__ Bh, co
     mma_h_16816(d, z0, z1, 0u, 0u, bl, 0u);
 }
 
+// G = X^T X for X [128][R] fp32 in shared memory on the tensor cores: mma.sync m16n8k8 with every fp32 value split into a
+// tf32 head and a tf32 remainder (head x head + head x remainder + remainder x head: 21 mantissa bits, fp32 range).  The A
+// fragment (X^T, rows r) and the B fragment (X, columns c) of a k-step are the same values.  Warp w (of four) sums the 32
+// rows 32 w .. 32 w + 31 and writes its partial G[w * 64 + r * 8 + c] for r, c < 8 (rows and columns >= R are zero).
+__device__ __forceinline__ uint32_t to_tf32(float x) {
+    uint32_t r;
+    asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(r) : "f"(x));
+    return r;
+}
+__device__ __forceinline__ void mma_tf32_1688(float (&c)[4], uint32_t a0, uint32_t a2, uint32_t b0, uint32_t b1) {
+    asm volatile("mma.sync.aligned.m16n8k8.row.col.f32.tf32.tf32.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+                 : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+                 : "r"(a0), "r"(0u), "r"(a2), "r"(0u), "r"(b0), "r"(b1));
+}
+template <int R>
+__device__ __forceinline__ void gram_tf32(const float* __restrict__ Xs, float* __restrict__ G, int warp, int lane) {
+    const int gid = lane >> 2, tig = lane & 3;
+    Xs += warp * 32 * R;
+    G += warp * 64;
+    const bool on = gid < R;
+    float hh[4] = {0.f, 0.f, 0.f, 0.f}, hl[4] = {0.f, 0.f, 0.f, 0.f}, lh[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+    for (int ks = 0; ks < 4; ++ks) {
+        const float x0 = on ? Xs[(8 * ks + tig) * R + gid] : 0.f, x1 = on ? Xs[(8 * ks + tig + 4) * R + gid] : 0.f;
+        const uint32_t h0 = to_tf32(x0), h1 = to_tf32(x1);
+        const uint32_t l0 = to_tf32(x0 - __uint_as_float(h0)), l1 = to_tf32(x1 - __uint_as_float(h1));
+        mma_tf32_1688(hh, h0, h1, h0, h1);
+        mma_tf32_1688(hl, h0, h1, l0, l1);
+        mma_tf32_1688(lh, l0, l1, h0, h1);
+    }
+    *reinterpret_cast<float2*>(G + gid * 8 + 2 * tig) = make_float2(hh[0] + (hl[0] + lh[0]), hh[1] + (hl[1] + lh[1]));
+}
+
 // ---- CholeskyQR on X [128][R] by the first four warps (thread = row) ----
 // Sum over the 32 lanes of N values per lane with N + 4 shuffles instead of 5 N: every exchange level halves the number of
 // values a lane keeps.  On return the lane holds the totals of indices base .. base + max(N / 32, 1) - 1 in v[0 ..].
@@ -251,22 +284,31 @@ __device__ __forceinline__ int fold_over_lanes(float (&v)[N], int lane) {
 // registers (every thread redundantly), X <- X L^-T applied to the thread's own row.  DROP = false floors a dependent column's
 // pivot at 1e-6 g_jj (R <= 4, leapquant/kernels.py:1816-1829), DROP = true zeroes the column (R = 8, :1760-1774).
 template <int R, bool DROP, typename Sync>
-__device__ __forceinline__ void cholqr_pass_team(float (&x)[R], float* __restrict__ gpart, int tid, Sync sync) {
-    constexpr int NPP = (R == 4) ? 16 : 64;                 // R (R + 1) / 2 products, padded to a power of two
+__device__ __forceinline__ void cholqr_pass_team(float (&x)[R], float* __restrict__ Xs, bool x_in_smem, float* __restrict__ gpart,
+                                                 int tid, Sync sync) {
+    constexpr bool MMA_GRAM = R > 4;                        // 36 products per row are too many to fold with shuffles
+    constexpr int NPP = 16;                                 // R (R + 1) / 2 = 10 products, padded to a power of two (R = 4)
     const int warp = tid >> 5, lane = tid & 31;
-    if (tid < 128) {
-        float pr[NPP];
+    if constexpr (MMA_GRAM) {
+        if (!x_in_smem) {
+            if (tid < 128) {
 #pragma unroll
-        for (int i = 0; i < NPP; ++i) pr[i] = 0.f;
+                for (int r = 0; r < R; ++r) Xs[tid * R + r] = x[r];
+            }
+            sync();
+        }
+        if (tid < 128) gram_tf32<R>(Xs, gpart, warp, lane);
+    } else {
+        if (tid < 128) {
+            float pr[NPP];
 #pragma unroll
-        for (int r = 0; r < R; ++r)
+            for (int i = 0; i < NPP; ++i) pr[i] = 0.f;
 #pragma unroll
-            for (int c = 0; c <= r; ++c) pr[r * (r + 1) / 2 + c] = x[r] * x[c];
-        const int base = fold_over_lanes<NPP>(pr, lane);
-        constexpr int KEEP = NPP >= 32 ? NPP / 32 : 1;
-        if (NPP >= 32 || (lane & ((32 / NPP) - 1)) == 0) {
+            for (int r = 0; r < R; ++r)
 #pragma unroll
-            for (int i = 0; i < KEEP; ++i) gpart[warp * 64 + base + i] = pr[i];
+                for (int c = 0; c <= r; ++c) pr[r * (r + 1) / 2 + c] = x[r] * x[c];
+            const int base = fold_over_lanes<NPP>(pr, lane);
+            if ((lane & ((32 / NPP) - 1)) == 0) gpart[warp * 64 + base] = pr[0];
         }
     }
     sync();
@@ -276,31 +318,33 @@ __device__ __forceinline__ void cholqr_pass_team(float (&x)[R], float* __restric
         for (int r = 0; r < R; ++r)
 #pragma unroll
             for (int c = 0; c <= r; ++c) {
-                const int k = r * (r + 1) / 2 + c;
+                const int k = MMA_GRAM ? r * 8 + c : r * (r + 1) / 2 + c;
                 g[r][c] = (gpart[k] + gpart[64 + k]) + (gpart[128 + k] + gpart[192 + k]);
             }
-        float l[R][R], inv[R];
+        // Cholesky G = L L^T, column by column: once column j is final, its products are subtracted from everything to its
+        // right.  Each entry still receives its subtractions in the order m = 0, 1, ..., so the result is the one of the usual
+        // row-by-row recurrence, but the operations of a step are independent of one another.
+        float gd[R], inv[R];
+#pragma unroll
+        for (int j = 0; j < R; ++j) gd[j] = g[j][j];
 #pragma unroll
         for (int j = 0; j < R; ++j) {
+            const float d = g[j][j];
+            if (DROP) inv[j] = (d > 1e-6f * gd[j] + 1e-30f) ? rsqrtf(fmaxf(d, 1e-30f)) : 0.f;
+            else inv[j] = rsqrtf(fmaxf(fmaxf(d, 1e-6f * gd[j]), 1e-30f));
 #pragma unroll
-            for (int k = 0; k < j; ++k) {
-                float acc = g[j][k];
+            for (int i = j + 1; i < R; ++i) g[i][j] *= inv[j];                   // l[i][j]
 #pragma unroll
-                for (int m = 0; m < k; ++m) acc -= l[j][m] * l[k][m];
-                l[j][k] = acc * inv[k];
-            }
-            float d = g[j][j];
+            for (int i = j + 1; i < R; ++i)
 #pragma unroll
-            for (int m = 0; m < j; ++m) d -= l[j][m] * l[j][m];
-            if (DROP) inv[j] = (d > 1e-6f * g[j][j] + 1e-30f) ? rsqrtf(fmaxf(d, 1e-30f)) : 0.f;
-            else inv[j] = rsqrtf(fmaxf(fmaxf(d, 1e-6f * g[j][j]), 1e-30f));
+                for (int k = j + 1; k <= i; ++k) g[i][k] -= g[i][j] * g[k][j];
         }
+        // X <- X L^-T by forward substitution on the thread's own row, likewise column by column
 #pragma unroll
-        for (int j = 0; j < R; ++j) {
-            float acc = x[j];
+        for (int m = 0; m < R; ++m) {
+            x[m] *= inv[m];
 #pragma unroll
-            for (int m = 0; m < j; ++m) acc -= x[m] * l[j][m];
-            x[j] = acc * inv[j];
+            for (int j = m + 1; j < R; ++j) x[j] -= x[m] * g[j][m];
         }
     }
 }
@@ -412,7 +456,8 @@ __device__ __forceinline__ bool flush_head(const FlushSmem& s, const FlushArgs& 
         constexpr int NTC = 64 * 16 / NT;                   // window-row chunks (16 bytes) per thread (Lp <= 64)
         float wv = 0.f, pcv = 1.f, skv = 0.f, svv = 0.f, pcf[NF], wrow[NTC];
         uint16_t fu[NF], fq[NF];
-        uint4 tk[NTC], tu[NTC];
+        uint4 tk[NTC], tu[NTC], tg[KDA ? NTC : 1];
+        const uint4* gbc = reinterpret_cast<const uint4*>(Gbuf + (KDA ? sh * L * KD : 0));
         if (tid < L) wv = Wbuf[sh * L + tid];
         if (tid < 128) {
             if (KDA) pcv = Pbuf[sh * KD + tid];
@@ -434,6 +479,7 @@ __device__ __forceinline__ bool flush_head(const FlushSmem& s, const FlushArgs& 
             tk[u] = in ? kb[i] : make_uint4(0u, 0u, 0u, 0u);
             tu[u] = in ? ub[i] : make_uint4(0u, 0u, 0u, 0u);
             wrow[u] = (!KDA && in) ? Wbuf[sh * L + (i >> 4)] : 0.f;
+            if (KDA) tg[u] = in ? gbc[i] : make_uint4(0u, 0u, 0u, 0u);
         }
         if (tid < L) s.w[tid] = wv;
         if (tid < 128) {
@@ -466,6 +512,12 @@ __device__ __forceinline__ bool flush_head(const FlushSmem& s, const FlushArgs& 
                 if (KDA) {
                     *reinterpret_cast<uint4*>(s.tile[0] + off) = tu[u];
                     *reinterpret_cast<uint4*>(s.tile[1] + off) = tk[u];
+                    if (j < L) {                            // the row's step factors e_j[c], as fp32, where the key scales will be
+                        const float2 e0 = f16x2_to_f2(tg[u].x), e1 = f16x2_to_f2(tg[u].y), e2 = f16x2_to_f2(tg[u].z), e3 = f16x2_to_f2(tg[u].w);
+                        float4* tp = reinterpret_cast<float4*>(s.tab + j * 128 + c16 * 8);
+                        tp[0] = make_float4(e0.x, e0.y, e1.x, e1.y);
+                        tp[1] = make_float4(e2.x, e2.y, e3.x, e3.y);
+                    }
                 } else {
                     const float sc[8] = {wrow[u], wrow[u], wrow[u], wrow[u], wrow[u], wrow[u], wrow[u], wrow[u]};
                     uint4 hi, lo;
@@ -478,41 +530,42 @@ __device__ __forceinline__ bool flush_head(const FlushSmem& s, const FlushArgs& 
         }
     }
     if (KDA) {
-        // key scale w_j D_j[c] with D_{L-1} = 1, D_j = D_{j+1} e_{j+1}: the L rows are cut into four segments (L % 4 == 0), a
-        // thread takes one column of one segment (of two, in a team of 8 warps); first the product of each segment's factors,
-        // then the running products.  The order of the multiplications does not depend on the size of the team.
+        // key scale w_j D_j[c] with D_{L-1} = 1, D_j = D_{j+1} e_{j+1}, in place over the step factors: the L rows are cut into
+        // four segments (L % 4 == 0), a thread takes one column of one segment (of two, in a team of 8 warps); first the
+        // product of each segment's factors, then the running products.  The order of the multiplications does not depend
+        // on the size of the team.
+        sync();                                             // the step factors are in shared memory
         constexpr int SPT = 4 * 128 / NT;                   // segments per thread
         const int c = tid & 127, slen = L >> 2;
-        const uint16_t* gb = Gbuf + sh * L * KD + c;
-        float ev[SPT][16];
 #pragma unroll
         for (int q2 = 0; q2 < SPT; ++q2) {
-            const int j1 = ((tid >> 7) + q2 * (NT / 128) + 1) * slen;
+            const int seg = (tid >> 7) + q2 * (NT / 128);
+            float ev[16], prod = 1.f;
 #pragma unroll
-            for (int k = 0; k < 16; ++k) ev[q2][k] = (k < slen) ? f16_to_f(gb[(j1 - 1 - k) * KD]) : 1.f;      // e_{j1-1}, e_{j1-2}, ...
-        }
+            for (int k = 0; k < 16; ++k) ev[k] = (k < slen) ? s.tab[((seg + 1) * slen - 1 - k) * 128 + c] : 1.f;
 #pragma unroll
-        for (int q2 = 0; q2 < SPT; ++q2) {
-            float prod = 1.f;
-#pragma unroll
-            for (int k = 0; k < 16; ++k) prod *= ev[q2][k];
-            s.segprod[((tid >> 7) + q2 * (NT / 128)) * 128 + c] = prod;
+            for (int k = 0; k < 16; ++k) prod *= ev[k];
+            s.segprod[seg * 128 + c] = prod;
         }
         sync();
 #pragma unroll
         for (int q2 = 0; q2 < SPT; ++q2) {
-            const int seg = (tid >> 7) + q2 * (NT / 128), j1 = (seg + 1) * slen;
+            const int seg = (tid >> 7) + q2 * (NT / 128);
             float dcur = 1.f;
 #pragma unroll
             for (int s2 = 3; s2 > 0; --s2)
                 if (s2 > seg) dcur *= s.segprod[s2 * 128 + c];
+            float ev[16], wv2[16];
 #pragma unroll
             for (int k = 0; k < 16; ++k) {
-                if (k < slen) {
-                    const int j = j1 - 1 - k;
-                    s.tab[j * 128 + c] = s.w[j] * dcur;
-                    dcur *= ev[q2][k];
-                }
+                const int j = (seg + 1) * slen - 1 - k;
+                ev[k] = (k < slen) ? s.tab[j * 128 + c] : 1.f;
+                wv2[k] = (k < slen) ? s.w[j] : 0.f;
+            }
+#pragma unroll
+            for (int k = 0; k < 16; ++k) {
+                if (k < slen) s.tab[((seg + 1) * slen - 1 - k) * 128 + c] = wv2[k] * dcur;
+                dcur *= ev[k];
             }
         }
         sync();
@@ -635,9 +688,9 @@ __device__ __forceinline__ bool flush_head(const FlushSmem& s, const FlushArgs& 
             float x[R];
 #pragma unroll
             for (int r = 0; r < R; ++r) x[r] = (tid < 128) ? s.Qn[tid * R + r] : 0.f;
-            cholqr_pass_team<R, (R > 4)>(x, s.gpart, tid, sync);
-            sync();                                         // the partial sums are read: the second pass may overwrite them
-            cholqr_pass_team<R, (R > 4)>(x, s.gpart, tid, sync);
+            cholqr_pass_team<R, (R > 4)>(x, s.Qn, true, s.gpart, tid, sync);
+            sync();                                         // the Gram matrix is read: the second pass may overwrite it
+            cholqr_pass_team<R, (R > 4)>(x, s.Qn, false, s.gpart, tid, sync);
             if (tid < 128) {
 #pragma unroll
                 for (int r = 0; r < R; ++r) s.Qh[r * HS + tid] = f_to_f16(x[r]);
