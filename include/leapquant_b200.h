@@ -109,6 +109,47 @@ int lq_kda_decode(const lq_dims* d, void* ssm, void* Kbuf, void* Ubuf, float* Wb
                   const float* dt_bias, const int32_t* idx, void* o, int32_t N, float scale, float gate_lower_bound,
                   const float* Q0, int32_t iters, void* stream);
 
+/* Operands of the causal conv1d update that precedes every decode step in the serving engine (the reference plugin calls
+ * vLLM's causal_conv1d_update right before LeapQuantState.decode: reference leapquant/vllm/gdn.py:31-33, glm.py:72-73).
+ * Per row with slot = idx[n] > 0 and per channel c of the q | k | v projection:
+ *     window = (state[slot][c][0], state[slot][c][1], state[slot][c][2], x[n][c])
+ *     y      = bias[c] + sum_t bf16(weight[c][t] * window[t])      (fp32 sum, taps in order: the engine kernel's arithmetic)
+ *     out    = bf16(y / (1 + exp(-y)))                             (SiLU)
+ *     state[slot][c][:] <- (window[1], window[2], window[3])
+ * All tensors are bf16.  The state is addressed through three element strides, so both layouts of the engine's cache work:
+ * (slot, channel, tap) and (slot, tap, channel); the second one (stride_dim == 1) is read with 8-byte accesses and then
+ * needs stride_tap and stride_slot to be multiples of 4.  width must be 4. */
+typedef struct lq_conv1d {
+    const void* x;          /* bf16 [N, x_stride]: raw projections of the N rows; channels 0 .. 2*H*K + HV*V - 1 are used */
+    int64_t x_stride;       /* elements between rows: >= the channel count, a multiple of 8; x 16-byte aligned */
+    void* state;            /* bf16 conv state, element (slot, channel, tap) at slot*stride_slot + channel*stride_dim + tap*stride_tap */
+    int64_t stride_slot, stride_dim, stride_tap;
+    const void* weight;     /* bf16 [channels, width] contiguous (a depthwise conv1d weight [channels, 1, width] viewed 2-D) */
+    const void* bias;       /* bf16 [channels] or NULL */
+    int32_t width;          /* taps: 4 (the state keeps width - 1 = 3 past inputs) */
+} lq_conv1d;
+
+/* Fused conv1d update + decode: lq_gdn_decode / lq_kda_decode with the q | k | v row computed inside the kernel from the raw
+ * projections (see lq_conv1d) instead of read from `mixed`; the conv state of every row with idx[n] > 0 is advanced.  Replaces
+ * the pair causal_conv1d_update -> LeapQuantState.decode of the reference plugin (leapquant/vllm/gdn.py:25-36,
+ * leapquant/vllm/glm.py:71-75) by ONE launch that never writes the intermediate q | k | v row to memory.  Results equal
+ * lq_causal_conv1d_update followed by lq_*_decode bit for bit.  Only the fused single-launch form exists: a configuration
+ * whose flush work area does not fit beside the step pipeline returns LQ_ERR_UNSUPPORTED. */
+int lq_gdn_decode_conv(const lq_dims* d, void* ssm, void* Kbuf, void* Ubuf, float* Wbuf, float* Pbuf, int32_t* hcnt,
+                       const lq_conv1d* conv, const void* a, const void* b, const float* A_log, const float* dt_bias,
+                       const int32_t* idx, void* o, int32_t N, float scale, const float* Q0, int32_t iters, void* stream);
+int lq_kda_decode_conv(const lq_dims* d, void* ssm, void* Kbuf, void* Ubuf, float* Wbuf, float* Pbuf, void* Gbuf,
+                       int32_t* hcnt, const lq_conv1d* conv, const void* a, const void* b, const float* A_log,
+                       const float* dt_bias, const int32_t* idx, void* o, int32_t N, float scale, float gate_lower_bound,
+                       const float* Q0, int32_t iters, void* stream);
+
+/* The conv1d update alone (same arithmetic as inside the fused kernels): out bf16 [N, out_stride] receives the activated
+ * q | k | v rows, the state is advanced.  Stands in for vLLM's causal_conv1d_update on single-token rows (call sites
+ * reference leapquant/vllm/gdn.py:32, glm.py:72).  Rows with idx[n] <= 0 are skipped (nothing read or written).  `channels`
+ * must be a multiple of 8; NS is the number of slots of the state. */
+int lq_causal_conv1d_update(const lq_conv1d* conv, const int32_t* idx, int32_t N, int32_t channels, int32_t NS, void* out,
+                            int64_t out_stride, void* stream);
+
 /* Standalone quantize.  Replaces the kernel built by make_quantize (reference leapquant/kernels.py:2126-2242);
  * with kda != 0 it also stands in for LeapQuantState._kda_checkpoint (reference leapquant/state.py:130-142, which
  * calls lowrank_factor with 3 iterations).  For every idx[n] > 0 and every head: reads the fp32 state [V][K] that

@@ -13,7 +13,8 @@ _HERE = os.path.dirname(os.path.abspath(__file__))
 LIB_PATH = os.environ.get("LEAPQUANT_B200_LIB") or os.path.join(_HERE, "libleapquant_b200.so")
 
 EXPORTS = ("lq_version", "lq_strerror", "lq_last_cuda_error", "lq_device_status", "lq_set_option", "lq_gdn_step", "lq_kda_step",
-           "lq_flush", "lq_gdn_decode", "lq_kda_decode", "lq_quantize", "lq_dequant", "lq_lowrank")
+           "lq_flush", "lq_gdn_decode", "lq_kda_decode", "lq_gdn_decode_conv", "lq_kda_decode_conv", "lq_causal_conv1d_update",
+           "lq_quantize", "lq_dequant", "lq_lowrank")
 
 _P = ctypes.c_void_p
 _I = ctypes.c_int32
@@ -23,6 +24,12 @@ _F = ctypes.c_float
 class LqDims(ctypes.Structure):
     """struct lq_dims of include/leapquant_b200.h."""
     _fields_ = [("NS", _I), ("HV", _I), ("H", _I), ("K", _I), ("V", _I), ("L", _I), ("R", _I), ("SS", ctypes.c_int64)]
+
+
+class LqConv1d(ctypes.Structure):
+    """struct lq_conv1d of include/leapquant_b200.h."""
+    _fields_ = [("x", _P), ("x_stride", ctypes.c_int64), ("state", _P), ("stride_slot", ctypes.c_int64), ("stride_dim", ctypes.c_int64),
+                ("stride_tap", ctypes.c_int64), ("weight", _P), ("bias", _P), ("width", _I)]
 
 
 class LeapQuantError(RuntimeError):
@@ -53,10 +60,15 @@ def lib():
         L.lq_flush.argtypes = [D, _P, _P, _P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _P]
         L.lq_gdn_decode.argtypes = [D, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _I, _F, _P, _I, _P]
         L.lq_kda_decode.argtypes = [D, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _I, _F, _F, _P, _I, _P]
+        C = ctypes.POINTER(LqConv1d)
+        L.lq_gdn_decode_conv.argtypes = [D, _P, _P, _P, _P, _P, _P, C, _P, _P, _P, _P, _P, _P, _I, _F, _P, _I, _P]
+        L.lq_kda_decode_conv.argtypes = [D, _P, _P, _P, _P, _P, _P, _P, C, _P, _P, _P, _P, _P, _P, _I, _F, _F, _P, _I, _P]
+        L.lq_causal_conv1d_update.argtypes = [C, _P, _I, _I, _I, _P, ctypes.c_int64, _P]
         L.lq_quantize.argtypes = [D, _P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _P]
         L.lq_dequant.argtypes = [D, _P, _P, _P, _P, _P, _P, _P, _P, _I, _I, _P]
         L.lq_lowrank.argtypes = [_P, _P, _P, _P, _I, _I, _I, _I, _I, _P]
-        for name in ("lq_device_status", "lq_gdn_step", "lq_kda_step", "lq_flush", "lq_quantize", "lq_dequant", "lq_lowrank"):
+        for name in ("lq_device_status", "lq_gdn_step", "lq_kda_step", "lq_flush", "lq_quantize", "lq_dequant", "lq_lowrank",
+                     "lq_gdn_decode", "lq_kda_decode", "lq_gdn_decode_conv", "lq_kda_decode_conv", "lq_causal_conv1d_update"):
             getattr(L, name).restype = _I
         _lib = L
     return _lib
@@ -72,6 +84,20 @@ def check(rc, what):
 
 def dims(NS, HV, H, K, V, L, R, SS):
     return LqDims(int(NS), int(HV), int(H), int(K), int(V), int(L), int(R), int(SS))
+
+
+def conv1d(x, conv_state, weight, bias):
+    """struct lq_conv1d for one call: x bf16 [N, C'] (row stride free), conv_state bf16 viewed as (slot, channel, tap) with any
+    strides (pass the engine's cache transposed if it is stored (slot, tap, channel)), weight bf16 [C, 4], bias bf16 [C] or None."""
+    for t in (x, conv_state, weight) + ((bias,) if bias is not None else ()):
+        if t.dtype != torch.bfloat16:
+            raise LeapQuantError(f"the conv1d update works on bf16 tensors, got {t.dtype}")
+    if x.stride(-1) != 1 or not weight.is_contiguous() or (bias is not None and not bias.is_contiguous()):
+        raise LeapQuantError("conv1d update: x rows, weight and bias must be contiguous")
+    if conv_state.dim() != 3 or conv_state.shape[2] != weight.shape[1] - 1:
+        raise LeapQuantError(f"conv state must be (slot, channel, width - 1), got {tuple(conv_state.shape)}")
+    return LqConv1d(ptr(x), x.stride(0), ptr(conv_state), conv_state.stride(0), conv_state.stride(1), conv_state.stride(2),
+                    ptr(weight), ptr(bias) if bias is not None else None, int(weight.shape[1]))
 
 
 def ptr(t):

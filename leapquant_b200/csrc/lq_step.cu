@@ -80,7 +80,113 @@ struct StepParams {
     int N;
     float scale;
     float glb;
+    // fused causal conv1d update (CONV kernels only): q | k | v are computed from the raw projections
+    const uint16_t* cx;          // bf16 [N, cx_stride] raw projections, MIX = 2 H K + HV V channels per row
+    uint16_t* cstate;            // bf16 conv state, element (slot, channel, tap) at slot * cs_slot + channel * cs_dim + tap * cs_tap
+    const uint16_t* cw;          // bf16 [MIX][4] depthwise taps
+    const uint16_t* cb;          // bf16 [MIX] bias or null
+    int64_t cs_slot, cs_dim, cs_tap;
+    int64_t cx_stride;
 };
+
+// ------------------------------------------------------------------------------------------------------------------
+// causal conv1d update of NC consecutive channels of one row: out = silu(bias + sum_t w[c][t] window[t]) with
+// window = (state[0], state[1], state[2], x), new state = (state[1], state[2], x).  The arithmetic is the serving engine's
+// Triton kernel's: every tap product is rounded to bf16, the sum runs in fp32 from the bias on, taps in order, and the
+// activation is x / (1 + exp(-x)) in fp32, rounded to bf16 at the end.
+// ------------------------------------------------------------------------------------------------------------------
+constexpr int CONV_W = 4;
+template <int NC>
+struct ConvRegs {
+    uint16_t x[NC], st[CONV_W - 1][NC], w[NC][CONV_W], b[NC];
+};
+template <int NC>
+__device__ __forceinline__ void ld_bf16_vec(const uint16_t* p, uint16_t (&out)[NC]) {
+    static_assert(NC == 2 || NC == 4, "two or four channels per thread");
+    if constexpr (NC == 4) {
+        const uint2 v = *reinterpret_cast<const uint2*>(p);
+        out[0] = uint16_t(v.x); out[1] = uint16_t(v.x >> 16); out[2] = uint16_t(v.y); out[3] = uint16_t(v.y >> 16);
+    } else {
+        const uint32_t v = *reinterpret_cast<const uint32_t*>(p);
+        out[0] = uint16_t(v); out[1] = uint16_t(v >> 16);
+    }
+}
+template <int NC>
+__device__ __forceinline__ void st_bf16_vec(uint16_t* p, const uint16_t (&in)[NC]) {
+    if constexpr (NC == 4) *reinterpret_cast<uint2*>(p) = make_uint2(uint32_t(in[0]) | (uint32_t(in[1]) << 16), uint32_t(in[2]) | (uint32_t(in[3]) << 16));
+    else *reinterpret_cast<uint32_t*>(p) = uint32_t(in[0]) | (uint32_t(in[1]) << 16);
+}
+// loads only (no arithmetic on what was loaded), so that a caller can issue them well ahead of conv_eval()
+template <int NC>
+__device__ __forceinline__ ConvRegs<NC> conv_load(const StepParams& P, int n, int slot, int c0) {
+    ConvRegs<NC> r;
+    ld_bf16_vec<NC>(P.cx + int64_t(n) * P.cx_stride + c0, r.x);
+    uint16_t* sb = P.cstate + int64_t(slot) * P.cs_slot;
+    if (P.cs_dim == 1) {                                     // (slot, tap, channel): the channels of a tap are contiguous
+#pragma unroll
+        for (int t = 0; t < CONV_W - 1; ++t) ld_bf16_vec<NC>(sb + t * P.cs_tap + c0, r.st[t]);
+    } else {
+#pragma unroll
+        for (int t = 0; t < CONV_W - 1; ++t)
+#pragma unroll
+            for (int e = 0; e < NC; ++e) r.st[t][e] = sb[int64_t(c0 + e) * P.cs_dim + t * P.cs_tap];
+    }
+    {
+        uint16_t wf[NC * CONV_W];
+        if constexpr (NC == 4) {
+            const uint4 a = *reinterpret_cast<const uint4*>(P.cw + int64_t(c0) * CONV_W), b = *reinterpret_cast<const uint4*>(P.cw + int64_t(c0) * CONV_W + 8);
+            const uint32_t ww[8] = {a.x, a.y, a.z, a.w, b.x, b.y, b.z, b.w};
+#pragma unroll
+            for (int i = 0; i < 8; ++i) { wf[2 * i] = uint16_t(ww[i]); wf[2 * i + 1] = uint16_t(ww[i] >> 16); }
+        } else {
+            const uint4 a = *reinterpret_cast<const uint4*>(P.cw + int64_t(c0) * CONV_W);
+            const uint32_t ww[4] = {a.x, a.y, a.z, a.w};
+#pragma unroll
+            for (int i = 0; i < 4; ++i) { wf[2 * i] = uint16_t(ww[i]); wf[2 * i + 1] = uint16_t(ww[i] >> 16); }
+        }
+#pragma unroll
+        for (int e = 0; e < NC; ++e)
+#pragma unroll
+            for (int t = 0; t < CONV_W; ++t) r.w[e][t] = wf[e * CONV_W + t];
+    }
+    if (P.cb) ld_bf16_vec<NC>(P.cb + c0, r.b);
+    else {
+#pragma unroll
+        for (int e = 0; e < NC; ++e) r.b[e] = 0;
+    }
+    return r;
+}
+template <int NC>
+__device__ __forceinline__ void conv_eval(const ConvRegs<NC>& r, uint16_t (&out)[NC]) {
+#pragma unroll
+    for (int e = 0; e < NC; ++e) {
+        float acc = bf16_to_f(r.b[e]);
+#pragma unroll
+        for (int t = 0; t < CONV_W; ++t) {
+            const float xv = bf16_to_f(t < CONV_W - 1 ? r.st[t][e] : r.x[e]);
+            acc += round_bf16(xv * bf16_to_f(r.w[e][t]));
+        }
+        out[e] = f_to_bf16(acc / (1.0f + expf(-acc)));
+    }
+}
+// new state (state[1], state[2], x) of the NC channels
+template <int NC>
+__device__ __forceinline__ void conv_store_state(const StepParams& P, int slot, int c0, const ConvRegs<NC>& r) {
+    uint16_t* sb = P.cstate + int64_t(slot) * P.cs_slot;
+    if (P.cs_dim == 1) {
+        st_bf16_vec<NC>(sb + c0, r.st[1]);
+        st_bf16_vec<NC>(sb + P.cs_tap + c0, r.st[2]);
+        st_bf16_vec<NC>(sb + 2 * P.cs_tap + c0, r.x);
+    } else {
+#pragma unroll
+        for (int e = 0; e < NC; ++e) {
+            uint16_t* cp = sb + int64_t(c0 + e) * P.cs_dim;
+            cp[0] = r.st[1][e];
+            cp[P.cs_tap] = r.st[2][e];
+            cp[2 * P.cs_tap] = r.x[e];
+        }
+    }
+}
 
 // per-program scalars, produced once and read by the whole group
 struct ProgScalars {
@@ -366,7 +472,7 @@ __device__ __forceinline__ void step_prologue(const StepParams& P, const ProgSca
 // `release()` is called by every thread after its last read of the stage and BEFORE the program's global stores: the
 // stage hand-back is an mbarrier arrive with release semantics, which would otherwise wait for those stores to drain.
 constexpr int MT = (VD / GW) / 16;                 // m16 tiles of tile rows per warp
-template <int R, bool KDA, typename Release>
+template <int R, bool KDA, bool CONV, typename Release>
 __device__ __forceinline__ void step_body(const StepParams& P, const ProgScalars& sc, char* st, const StageLayout& lay,
                                           const GroupScratch& gs, int t, int bar, Release release) {
     const int w = t >> 5, lane = t & 31, l8 = lane & 7, g = lane >> 3;
@@ -374,8 +480,13 @@ __device__ __forceinline__ void step_body(const StepParams& P, const ProgScalars
     const int64_t sh = int64_t(sc.slot) * P.d.HV + sc.hv;
     const float* nrm = reinterpret_cast<const float*>(st + lay.nrm);
     // this lane's two values of the token's v, straight from global memory: issued now, used in the last phase
-    const uint32_t vraw = __ldg(reinterpret_cast<const uint32_t*>(
-        P.mixed + int64_t(sc.n) * (2 * P.d.H * KD + P.d.HV * VD) + 2 * P.d.H * KD + sc.hv * VD) + (64 / GW) * w + ((t & 31) % (64 / GW)));
+    // (CONV: the two raw projections, their conv state and taps; the value follows from conv_eval() at the end)
+    uint32_t vraw = 0u;
+    ConvRegs<2> vconv = {};
+    const int vch = 2 * P.d.H * KD + sc.hv * VD + 2 * ((64 / GW) * w + ((t & 31) % (64 / GW)));      // this lane's first channel of v
+    if constexpr (CONV) {
+        if ((t & 31) < 64 / GW) vconv = conv_load<2>(P, sc.n, sc.slot, vch);      // (the lanes that finish the program)
+    } else vraw = __ldg(reinterpret_cast<const uint32_t*>(P.mixed + int64_t(sc.n) * (2 * P.d.H * KD + P.d.HV * VD) + vch));
 
     // ---- KDA: decayed window keys K_j D_j (bf16, in place), D_j = en prod_{j<i<h} e_i; thread per key channel ----
     if (KDA) {
@@ -570,6 +681,11 @@ __device__ __forceinline__ void step_body(const StepParams& P, const ProgScalars
     float u0 = 0.f, u1 = 0.f, y0 = 0.f, y1 = 0.f, pn = 0.f;
     if (jh == 0) {
         const float2 m0 = gs.mqy[2 * vp], m1 = gs.mqy[2 * vp + 1];
+        if constexpr (CONV) {
+            uint16_t vo[2];
+            conv_eval<2>(vconv, vo);
+            vraw = uint32_t(vo[0]) | (uint32_t(vo[1]) << 16);
+        }
         const float2 vv = bf16x2_to_f2(vraw);
         const float beta = sc.beta;
         const float kq = *reinterpret_cast<const float*>(st + lay.sc + 32);
@@ -590,6 +706,7 @@ __device__ __forceinline__ void step_body(const StepParams& P, const ProgScalars
     if (jh == 0) {
         reinterpret_cast<uint32_t*>(P.o)[(int64_t(sc.n) * P.d.HV + sc.hv) * 64 + vp] = f2_to_bf16x2(y0, y1);
         reinterpret_cast<uint32_t*>(P.Ubuf)[(sh * L + h) * 64 + vp] = f2_to_bf16x2(u0, u1);
+        if constexpr (CONV) conv_store_state<2>(P, sc.slot, vch, vconv);
         if (t == 0) {
             if (!KDA) P.Pbuf[sh] = pn;
             P.Wbuf[sh * L + h] = 1.f;
@@ -653,7 +770,7 @@ __global__ void __launch_bounds__(GT, 2) step_direct_kernel(StepParams P) {
     if (t < 32) step_prologue<KDA>(P, sc, st, lay, t, [] {});
     __syncthreads();
     const GroupScratch gs = carve_scratch(stage_smem + stage_layout(P.d.L, P.d.L, R, KDA).bytes);
-    step_body<R, KDA>(P, sc, st, lay, gs, t, 1, [] {});
+    step_body<R, KDA, false>(P, sc, st, lay, gs, t, 1, [] {});
 }
 
 #include "lq_step_warp.cuh"
@@ -682,7 +799,11 @@ constexpr int NPW = LQ_NPW;                     // prologue warps; warp 2 + k ta
 constexpr int UT = 32 * (2 + NPW);              // utility threads ahead of the consumer groups: producer, copy issue, prologues
 constexpr int ND = 16;                         // descriptors = most programs resident in the ring at once
 
-template <int R, bool KDA, int NG, bool FUSE>
+// CONV: q | k | v come out of the fused causal conv1d update.  The q and k channels of a key head are shared by its GQA
+// value heads, and their conv state may be rewritten only once every one of those programs has read it; so the CONV kernels
+// deal out KEY-HEAD UNITS (row n, key head hk) to the CTAs instead of single programs: a CTA runs the GQA programs of a unit
+// one after the other, and ONE prologue warp takes all of them, computes q and k once and then writes the state back.
+template <int R, bool KDA, int NG, bool FUSE, bool CONV>
 __global__ void __launch_bounds__(UT + NG * GT, 1) step_pipelined_kernel(StepParams P, int ring_bytes, FuseTail ft) {
     extern __shared__ __align__(128) char stage_smem[];
     char* scratch0 = stage_smem + ring_bytes;
@@ -698,9 +819,22 @@ __global__ void __launch_bounds__(UT + NG * GT, 1) step_pipelined_kernel(StepPar
     int* dl = dl_n + 4;
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int HV = P.d.HV, H = P.d.H, L = P.d.L;
-    const int nprog = P.N * HV;
     const int grid = gridDim.x, bid = blockIdx.x;
-    const int nit = (nprog - bid + grid - 1) / grid;
+    const int gqa = HV / H;
+    // program i of this CTA: (row, value head).  Plain kernels: program index bid + i * grid.  CONV: unit bid + (i / gqa) * grid.
+    const int nunits = CONV ? P.N * H : P.N * HV;
+    const int nit = ((nunits - bid + grid - 1) / grid) * (CONV ? gqa : 1);
+    auto row_head = [&](int i, int& n, int& hv) {
+        if constexpr (CONV) {
+            const int u = bid + (i / gqa) * grid;
+            n = u / H;
+            hv = (u - n * H) * gqa + (i % gqa);
+        } else {
+            const int pgm = bid + i * grid;
+            n = pgm / HV;
+            hv = pgm - n * HV;
+        }
+    };
 
     if (tid == 0) {
         *dl_n = 0;
@@ -724,11 +858,16 @@ __global__ void __launch_bounds__(UT + NG * GT, 1) step_pipelined_kernel(StepPar
         // Scalars of 32 programs per batch, one program per lane, fetched two levels ahead: while batch b is placed, the
         // counters and gates of batch b + 1 and the slots of batch b + 2 are in flight.
         ProgScalars cur;
-        auto slot_of = [&](int i) -> int { return i < nit ? P.idx[(bid + i * grid) / HV] : 0; };
+        auto slot_of = [&](int i) -> int {
+            if (i >= nit) return 0;
+            int n, hv;
+            row_head(i, n, hv);
+            return P.idx[n];
+        };
         auto raw_of = [&](int i, int slot) {
-            const int p = i < nit ? bid + i * grid : bid;
-            const int n = p / HV;
-            return load_raw(P, n, p - n * HV, i < nit ? slot : 0, KDA);
+            int n, hv;
+            row_head(i < nit ? i : 0, n, hv);
+            return load_raw(P, n, hv, i < nit ? slot : 0, KDA);
         };
         int slot_b;
         RawScalars rnx;
@@ -797,7 +936,6 @@ __global__ void __launch_bounds__(UT + NG * GT, 1) step_pipelined_kernel(StepPar
 
     if (warp == 1) {
         // ================= copy issue: one bulk asynchronous copy per lane and program =================
-        const int gqa = HV / H;
         // Per-lane copy descriptor, fixed for the whole kernel: lane k < ncopy issues copy k of every program from
         //   src = base + slot * c_slot + hv * c_hv + n * c_n + hk * c_hk,   bytes = b_fix + h * b_h,
         // into stage + o_fix + h * o_h (the stage layout moves with the live rows h).
@@ -858,24 +996,11 @@ __global__ void __launch_bounds__(UT + NG * GT, 1) step_pipelined_kernel(StepPar
         // ================= prologue warps: programs dealt round-robin, each warp in fill order =================
         // q and k of a program come straight from global memory into this warp's registers (lane = four channels), fetched
         // one program of this warp ahead: row and key head follow from the program index alone
-        const int MIXq = 2 * H * KD + HV * VD, gqaq = HV / H;
-        uint2 q_nx = make_uint2(0u, 0u), k_nx = make_uint2(0u, 0u);
-        auto qk_fetch = [&](int i2) {
-            if (i2 >= nit) return;
-            const int p2 = bid + i2 * grid;
-            const int n2 = p2 / HV, hk2 = (p2 - n2 * HV) / gqaq;
-            const uint2* mrow = reinterpret_cast<const uint2*>(P.mixed + int64_t(n2) * MIXq);
-            q_nx = __ldg(mrow + hk2 * 32 + lane);
-            k_nx = __ldg(mrow + (H + hk2) * 32 + lane);
-        };
-        qk_fetch(warp - 2);
-        for (int i = warp - 2; i < nit; i += NPW) {
+        auto run_prologue = [&](int i, const uint2& q_cur, const uint2& k_cur) -> bool {
             const int dsc = i % ND;
-            const uint2 q_cur = q_nx, k_cur = k_nx;
-            qk_fetch(i + NPW);
             if (!warp_wait_bounded(full + dsc, uint32_t(i / ND) & 1u, lane)) {
                 if (lane == 0) { atomicOr(&g_status, ST_PROLOGUE_TIMEOUT); *abortf = 1; }
-                return;
+                return false;
             }
             char* st = stage_smem + doff[dsc];
             const int rows = doff[ND + NG + dsc];                  // rows the stage was sized for (h, or 0 for a dead program)
@@ -885,6 +1010,60 @@ __global__ void __launch_bounds__(UT + NG * GT, 1) step_pipelined_kernel(StepPar
                 step_prologue<KDA>(P, sc, st, lay, lane, [&] { mbar_arrive(normed + dsc); }, true, q_cur, k_cur);
             } else {
                 mbar_arrive(normed + dsc);
+            }
+            return true;
+        };
+        if constexpr (CONV) {
+            // warp k takes the units k, k + NPW, ... of this CTA: the raw q and k projections of the unit, their conv state and
+            // taps are fetched one unit ahead; the conv runs once, the new state is written back at once (every reader of the
+            // old one is this warp), and the unit's GQA programs all use the result
+            const int nun = nit / gqa;
+            ConvRegs<4> cq = {}, ck = {};
+            int slot_nx = 0;
+            auto unit_fetch = [&](int uu) {
+                slot_nx = 0;
+                if (uu >= nun) return;
+                const int u = bid + uu * grid, n2 = u / H, hk2 = u - n2 * H;
+                const int sl = P.idx[n2];
+                if (sl <= 0 || sl >= P.d.NS) return;
+                slot_nx = sl;
+                cq = conv_load<4>(P, n2, sl, hk2 * KD + 4 * lane);
+                ck = conv_load<4>(P, n2, sl, (H + hk2) * KD + 4 * lane);
+            };
+            unit_fetch(warp - 2);
+            for (int uu = warp - 2; uu < nun; uu += NPW) {
+                uint2 q_cur = make_uint2(0u, 0u), k_cur = make_uint2(0u, 0u);
+                if (slot_nx > 0) {
+                    const int u = bid + uu * grid, n1 = u / H, hk1 = u - n1 * H;
+                    uint16_t qo[4], ko[4];
+                    conv_eval<4>(cq, qo);
+                    conv_eval<4>(ck, ko);
+                    q_cur = make_uint2(uint32_t(qo[0]) | (uint32_t(qo[1]) << 16), uint32_t(qo[2]) | (uint32_t(qo[3]) << 16));
+                    k_cur = make_uint2(uint32_t(ko[0]) | (uint32_t(ko[1]) << 16), uint32_t(ko[2]) | (uint32_t(ko[3]) << 16));
+                    conv_store_state<4>(P, slot_nx, hk1 * KD + 4 * lane, cq);
+                    conv_store_state<4>(P, slot_nx, (H + hk1) * KD + 4 * lane, ck);
+                }
+                unit_fetch(uu + NPW);
+                for (int g2 = 0; g2 < gqa; ++g2)
+                    if (!run_prologue(uu * gqa + g2, q_cur, k_cur)) return;
+            }
+        } else {
+            const int MIXq = 2 * H * KD + HV * VD;
+            uint2 q_nx = make_uint2(0u, 0u), k_nx = make_uint2(0u, 0u);
+            auto qk_fetch = [&](int i2) {
+                if (i2 >= nit) return;
+                int n2, hv2;
+                row_head(i2, n2, hv2);
+                const int hk2 = hv2 / gqa;
+                const uint2* mrow = reinterpret_cast<const uint2*>(P.mixed + int64_t(n2) * MIXq);
+                q_nx = __ldg(mrow + hk2 * 32 + lane);
+                k_nx = __ldg(mrow + (H + hk2) * 32 + lane);
+            };
+            qk_fetch(warp - 2);
+            for (int i = warp - 2; i < nit; i += NPW) {
+                const uint2 q_cur = q_nx, k_cur = k_nx;
+                qk_fetch(i + NPW);
+                if (!run_prologue(i, q_cur, k_cur)) return;
             }
         }
         return;
@@ -914,13 +1093,21 @@ __global__ void __launch_bounds__(UT + NG * GT, 1) step_pipelined_kernel(StepPar
         const ProgScalars sc = *reinterpret_cast<const ProgScalars*>(st + lay.sc);
         auto release = [&] { mbar_arrive(empty + dsc); };
         if (prog_live(sc, L)) {
-            step_body<R, KDA>(P, sc, st, lay, gs, t, bar, release);
+            step_body<R, KDA, CONV>(P, sc, st, lay, gs, t, bar, release);
             if (FUSE && t == 0 && sc.h + 1 == L) dl[atomicAdd(dl_n, 1)] = sc.slot * HV + sc.hv;      // window just filled
         } else {
             if (FUSE && t == 0 && sc.slot > 0 && sc.h == L) dl[atomicAdd(dl_n, 1)] = sc.slot * HV + sc.hv;   // was full already
             release();
-            const int p = bid + i * grid;
-            if (t < 64) reinterpret_cast<uint32_t*>(P.o)[int64_t(p) * 64 + t] = 0u;
+            int n0, hv0;
+            row_head(i, n0, hv0);
+            if (t < 64) reinterpret_cast<uint32_t*>(P.o)[(int64_t(n0) * HV + hv0) * 64 + t] = 0u;
+            if constexpr (CONV) {                           // the row still advances its conv state (v channels of this head)
+                if (t < 64 && sc.slot > 0) {
+                    const int vch = 2 * H * KD + hv0 * VD + 2 * t;
+                    const ConvRegs<2> r2 = conv_load<2>(P, n0, sc.slot, vch);
+                    conv_store_state<2>(P, sc.slot, vch, r2);
+                }
+            }
         }
     }
     };
@@ -978,10 +1165,12 @@ static std::atomic<int> g_step_impl{0};
 // fuse != nullptr: the pipelined driver also flushes, in the same launch, the heads whose window it fills (Q0, iters from
 // *fuse).  Returns LQ_ERR_UNSUPPORTED when the fused form is not available for the configuration (debug drivers, a flush
 // team that does not fit in the ring): the caller then launches the two kernels separately.
+// conv: q | k | v come from the fused causal conv1d update (P.cx etc. are set); only the fused pipelined form exists for it.
 template <int R, bool KDA>
-static int launch_step(const StepParams& P, cudaStream_t st, const FuseTail* fuse) {
+static int launch_step(const StepParams& P, cudaStream_t st, const FuseTail* fuse, bool conv = false) {
     const StageLayout lay = stage_layout(P.d.L, P.d.L, R, KDA);
-    const int impl = g_step_impl.load(std::memory_order_relaxed);      // read once: one call never mixes two drivers
+    const int impl = (conv && fuse) ? 0 : g_step_impl.load(std::memory_order_relaxed);      // read once: one call never mixes two drivers
+    if (conv && !fuse) return LQ_ERR_UNSUPPORTED;
     if (impl != 0 && fuse && !(impl == 2 && KDA)) return LQ_ERR_UNSUPPORTED;
     if (impl == 1) {
         const size_t smem = size_t(lay.bytes) + SCRATCH_BYTES;
@@ -999,8 +1188,9 @@ static int launch_step(const StepParams& P, cudaStream_t st, const FuseTail* fus
     }
     constexpr int NG = LQ_NG;
     const int nprog = P.N * P.d.HV;
-    const int grid = nprog < device_sm_count() ? nprog : device_sm_count();
-    const int nit_max = (nprog + grid - 1) / grid;
+    const int nunits = conv ? P.N * P.d.H : nprog;               // what the CTAs are dealt: key-head units (conv) or programs
+    const int grid = nunits < device_sm_count() ? nunits : device_sm_count();
+    const int nit_max = ((nunits + grid - 1) / grid) * (conv ? P.d.HV / P.d.H : 1);
     const size_t budget = 227 * 1024 - 256;                      // (the kernel also has a few bytes of static shared memory)
     const size_t fixed = size_t(NG) * SCRATCH_BYTES + 4 * ND * sizeof(uint64_t) + (2 * ND + NG + 4) * sizeof(int) + 32 * sizeof(ProgScalars) +
                          (4 + size_t(nit_max)) * sizeof(int);
@@ -1016,24 +1206,50 @@ static int launch_step(const StepParams& P, cudaStream_t st, const FuseTail* fus
         ft.team_bytes = int((flush_smem_bytes<R>(P.d.L, 0, KDA) + 127) & ~size_t(127));
         ft.teams = (2 * ft.team_bytes <= ring_bytes) ? 2 : (ft.team_bytes <= ring_bytes ? 1 : 0);
         if (ft.teams == 0) return LQ_ERR_UNSUPPORTED;
-        int rc = ensure_smem((const void*)step_pipelined_kernel<R, KDA, NG, true>, smem);
-        if (rc) return rc;
-        le = launch_dependent(step_pipelined_kernel<R, KDA, NG, true>, unsigned(grid), unsigned(UT + NG * GT), smem, st, P, ring_bytes, ft);
+        if (conv) {
+            int rc = ensure_smem((const void*)step_pipelined_kernel<R, KDA, NG, true, true>, smem);
+            if (rc) return rc;
+            le = launch_dependent(step_pipelined_kernel<R, KDA, NG, true, true>, unsigned(grid), unsigned(UT + NG * GT), smem, st, P, ring_bytes, ft);
+        } else {
+            int rc = ensure_smem((const void*)step_pipelined_kernel<R, KDA, NG, true, false>, smem);
+            if (rc) return rc;
+            le = launch_dependent(step_pipelined_kernel<R, KDA, NG, true, false>, unsigned(grid), unsigned(UT + NG * GT), smem, st, P, ring_bytes, ft);
+        }
     } else {
-        int rc = ensure_smem((const void*)step_pipelined_kernel<R, KDA, NG, false>, smem);
+        int rc = ensure_smem((const void*)step_pipelined_kernel<R, KDA, NG, false, false>, smem);
         if (rc) return rc;
-        le = launch_dependent(step_pipelined_kernel<R, KDA, NG, false>, unsigned(grid), unsigned(UT + NG * GT), smem, st, P, ring_bytes, ft);
+        le = launch_dependent(step_pipelined_kernel<R, KDA, NG, false, false>, unsigned(grid), unsigned(UT + NG * GT), smem, st, P, ring_bytes, ft);
     }
     if (le != cudaSuccess) { set_last_cuda_error(le); return LQ_ERR_LAUNCH; }
     return finish_launch();
 }
 
+static int check_conv(const lq_conv1d* c, int channels) {
+    if (!c->x || !c->state || !c->weight) return LQ_ERR_NULL;
+    if (c->width != CONV_W) return LQ_ERR_UNSUPPORTED;
+    if (c->x_stride < channels || (c->x_stride & 7)) return LQ_ERR_RANGE;
+    if (misaligned16({c->x, c->weight}) || (reinterpret_cast<uintptr_t>(c->state) & 7) || (c->bias && (reinterpret_cast<uintptr_t>(c->bias) & 7)))
+        return LQ_ERR_ALIGN;
+    // channels contiguous per tap: the kernels move four channels of a tap with one 8-byte access
+    if (c->stride_dim == 1 && ((c->stride_tap & 3) || (c->stride_slot & 3))) return LQ_ERR_ALIGN;
+    return LQ_OK;
+}
+static void set_conv(StepParams& P, const lq_conv1d* c) {
+    P.cx = (const uint16_t*)c->x; P.cx_stride = c->x_stride; P.cstate = (uint16_t*)c->state; P.cw = (const uint16_t*)c->weight;
+    P.cb = (const uint16_t*)c->bias; P.cs_slot = c->stride_slot; P.cs_dim = c->stride_dim; P.cs_tap = c->stride_tap;
+}
+
 static int step_common(const lq_dims* d, void* ssm, void* Kbuf, void* Ubuf, float* Wbuf, float* Pbuf, void* Gbuf,
                        int32_t* hcnt, const void* mixed, const void* a, const void* b, const float* A_log,
                        const float* dt_bias, const int32_t* idx, void* o, int32_t N, float scale, float glb, bool kda,
-                       void* stream, const FuseTail* fuse = nullptr) {
+                       void* stream, const FuseTail* fuse = nullptr, const lq_conv1d* conv = nullptr) {
     int rc = check_dims(d);
     if (rc) return rc;
+    if (conv) {
+        rc = check_conv(conv, 2 * d->H * d->K + d->HV * d->V);
+        if (rc) return rc;
+        mixed = conv->x;                                         // (takes the place of the q | k | v rows in the checks below)
+    }
     if (!ssm || !Kbuf || !Ubuf || !Wbuf || !Pbuf || !hcnt || !A_log || !dt_bias || (kda && !Gbuf)) return LQ_ERR_NULL;
     if (N < 0) return LQ_ERR_RANGE;
     if (N == 0) return LQ_OK;
@@ -1046,9 +1262,25 @@ static int step_common(const lq_dims* d, void* ssm, void* Kbuf, void* Ubuf, floa
     P.b = (const uint16_t*)b; P.A_log = A_log; P.dt_bias = dt_bias; P.idx = idx; P.o = (uint16_t*)o; P.N = N;
     P.scale = scale > 0.f ? scale : 1.0f / sqrtf(float(d->K));
     P.glb = glb;
+    P.cx = nullptr; P.cstate = nullptr; P.cw = nullptr; P.cb = nullptr; P.cs_slot = P.cs_dim = P.cs_tap = 0; P.cx_stride = 0;
+    if (conv) set_conv(P, conv);
     cudaStream_t s = static_cast<cudaStream_t>(stream);
-    if (kda) return d->R == 4 ? launch_step<4, true>(P, s, fuse) : launch_step<8, true>(P, s, fuse);
-    return d->R == 4 ? launch_step<4, false>(P, s, fuse) : launch_step<8, false>(P, s, fuse);
+    const bool cv = conv != nullptr;
+    if (kda) return d->R == 4 ? launch_step<4, true>(P, s, fuse, cv) : launch_step<8, true>(P, s, fuse, cv);
+    return d->R == 4 ? launch_step<4, false>(P, s, fuse, cv) : launch_step<8, false>(P, s, fuse, cv);
+}
+
+// standalone conv update: one thread per two channels of a row, the arithmetic of the fused kernels
+__global__ void __launch_bounds__(256) conv1d_update_kernel(StepParams P, int C, uint16_t* out, int64_t out_stride) {
+    const int n = blockIdx.y, c0 = 2 * (blockIdx.x * 256 + threadIdx.x);
+    if (c0 >= C) return;
+    const int slot = P.idx[n];
+    if (slot <= 0 || slot >= P.d.NS) return;                     // padding row: nothing read, nothing written
+    const ConvRegs<2> r = conv_load<2>(P, n, slot, c0);
+    uint16_t o2[2];
+    conv_eval<2>(r, o2);
+    *reinterpret_cast<uint32_t*>(out + int64_t(n) * out_stride + c0) = uint32_t(o2[0]) | (uint32_t(o2[1]) << 16);
+    conv_store_state<2>(P, slot, c0, r);
 }
 
 }  // namespace lq
@@ -1087,13 +1319,13 @@ extern "C" int lq_kda_step(const lq_dims* d, void* ssm, void* Kbuf, void* Ubuf, 
 static int decode_common(const lq_dims* d, void* ssm, void* Kbuf, void* Ubuf, float* Wbuf, float* Pbuf, void* Gbuf, int32_t* hcnt,
                          const void* mixed, const void* a, const void* b, const float* A_log, const float* dt_bias,
                          const int32_t* idx, void* o, int32_t N, float scale, float glb, bool kda, const float* Q0, int32_t iters,
-                         void* stream) {
+                         void* stream, const lq_conv1d* conv = nullptr) {
     if (!Q0) return LQ_ERR_NULL;
     if (iters < 0) return LQ_ERR_RANGE;
     lq::FuseTail ft = {Q0, iters, 0, 0};
     int rc = lq::step_common(d, ssm, Kbuf, Ubuf, Wbuf, Pbuf, Gbuf, hcnt, mixed, a, b, A_log, dt_bias, idx, o, N, scale, glb, kda,
-                             stream, &ft);
-    if (rc != LQ_ERR_UNSUPPORTED) return rc;
+                             stream, &ft, conv);
+    if (rc != LQ_ERR_UNSUPPORTED || conv) return rc;           // (the conv form exists as one fused launch only)
     rc = lq::step_common(d, ssm, Kbuf, Ubuf, Wbuf, Pbuf, Gbuf, hcnt, mixed, a, b, A_log, dt_bias, idx, o, N, scale, glb, kda, stream);
     if (rc) return rc;
     return lq_flush(d, ssm, Kbuf, Ubuf, Wbuf, Pbuf, Gbuf, hcnt, Q0, idx, N, kda ? 1 : 0, iters, stream);
@@ -1112,4 +1344,38 @@ extern "C" int lq_kda_decode(const lq_dims* d, void* ssm, void* Kbuf, void* Ubuf
                              int32_t iters, void* stream) {
     return decode_common(d, ssm, Kbuf, Ubuf, Wbuf, Pbuf, Gbuf, hcnt, mixed, a, b, A_log, dt_bias, idx, o, N, scale, glb, true, Q0,
                          iters, stream);
+}
+
+extern "C" int lq_gdn_decode_conv(const lq_dims* d, void* ssm, void* Kbuf, void* Ubuf, float* Wbuf, float* Pbuf, int32_t* hcnt,
+                                  const lq_conv1d* conv, const void* a, const void* b, const float* A_log, const float* dt_bias,
+                                  const int32_t* idx, void* o, int32_t N, float scale, const float* Q0, int32_t iters, void* stream) {
+    if (!conv) return LQ_ERR_NULL;
+    return decode_common(d, ssm, Kbuf, Ubuf, Wbuf, Pbuf, nullptr, hcnt, nullptr, a, b, A_log, dt_bias, idx, o, N, scale, 0.f, false, Q0,
+                         iters, stream, conv);
+}
+
+extern "C" int lq_kda_decode_conv(const lq_dims* d, void* ssm, void* Kbuf, void* Ubuf, float* Wbuf, float* Pbuf, void* Gbuf,
+                                  int32_t* hcnt, const lq_conv1d* conv, const void* a, const void* b, const float* A_log,
+                                  const float* dt_bias, const int32_t* idx, void* o, int32_t N, float scale, float glb,
+                                  const float* Q0, int32_t iters, void* stream) {
+    if (!conv) return LQ_ERR_NULL;
+    return decode_common(d, ssm, Kbuf, Ubuf, Wbuf, Pbuf, Gbuf, hcnt, nullptr, a, b, A_log, dt_bias, idx, o, N, scale, glb, true, Q0,
+                         iters, stream, conv);
+}
+
+extern "C" int lq_causal_conv1d_update(const lq_conv1d* conv, const int32_t* idx, int32_t N, int32_t channels, int32_t NS, void* out,
+                                       int64_t out_stride, void* stream) {
+    if (!conv || !out || (N > 0 && !idx)) return LQ_ERR_NULL;
+    if (N < 0 || channels <= 0 || (channels & 7) || NS < 1 || out_stride < channels || (out_stride & 1)) return LQ_ERR_RANGE;
+    int rc = lq::check_conv(conv, channels);
+    if (rc) return rc;
+    if (reinterpret_cast<uintptr_t>(out) & 3) return LQ_ERR_ALIGN;
+    if (N == 0) return LQ_OK;
+    lq::StepParams P = {};
+    P.d.NS = NS;
+    P.idx = idx;
+    lq::set_conv(P, conv);
+    dim3 grid(unsigned((channels / 2 + 255) / 256), unsigned(N));
+    lq::conv1d_update_kernel<<<grid, 256, 0, static_cast<cudaStream_t>(stream)>>>(P, channels, (uint16_t*)out, out_stride);
+    return lq::finish_launch();
 }

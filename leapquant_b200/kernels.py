@@ -96,6 +96,51 @@ def make_decode(NS, HV, H, K, V, L, SS, R=4, ITERS=1, KDA=False, GLB=0.0, scale=
     return decode
 
 
+def make_decode_conv(NS, HV, H, K, V, L, SS, R=4, ITERS=1, KDA=False, GLB=0.0, scale=None):
+    """causal conv1d update + step + flush in one launch (no counterpart factory in the reference, whose plugin calls vLLM's
+    causal_conv1d_update and then LeapQuantState.decode: leapquant/vllm/gdn.py:31-36, leapquant/vllm/glm.py:71-75).  Returns, for
+    GDN, decode(Sq, Kbuf, Ubuf, Wbuf, Pbuf, hcnt, x, conv_state, conv_weight, conv_bias, a, b, A_log, dt_bias, Q0, idx, o) and
+    for KDA the same with Gbuf after Pbuf.  x holds the raw q | k | v projections (bf16 [N, >= 2HK + HV V]); conv_state is the
+    engine's conv cache viewed (slot, channel, width - 1) and is advanced in place; results equal make_conv1d_update followed by
+    make_decode bit for bit."""
+    _need_128(K, V, "make_decode_conv")
+    d = _lib.dims(NS, HV, H, K, V, L, R, SS)
+    sc = float(K ** -0.5 if scale is None else scale)
+    iters, glb = int(ITERS), float(GLB)
+    p = _lib.ptr
+    if KDA:
+        fn = _lib.lib().lq_kda_decode_conv
+
+        def decode(Sq, Kbuf, Ubuf, Wbuf, Pbuf, Gbuf, hcnt, x, conv_state, conv_weight, conv_bias, a, b, A_log, dt_bias, Q0, idx, o):
+            cv = _lib.conv1d(x, conv_state, conv_weight, conv_bias)
+            _launch(fn, "lq_kda_decode_conv", Sq, d, p(Sq), p(Kbuf), p(Ubuf), p(Wbuf), p(Pbuf), p(Gbuf), p(hcnt), cv, p(a), p(b),
+                    p(A_log), p(dt_bias), p(idx), p(o), int(x.shape[0]), sc, glb, p(Q0), iters)
+    else:
+        fn = _lib.lib().lq_gdn_decode_conv
+
+        def decode(Sq, Kbuf, Ubuf, Wbuf, Pbuf, hcnt, x, conv_state, conv_weight, conv_bias, a, b, A_log, dt_bias, Q0, idx, o):
+            cv = _lib.conv1d(x, conv_state, conv_weight, conv_bias)
+            _launch(fn, "lq_gdn_decode_conv", Sq, d, p(Sq), p(Kbuf), p(Ubuf), p(Wbuf), p(Pbuf), p(hcnt), cv, p(a), p(b),
+                    p(A_log), p(dt_bias), p(idx), p(o), int(x.shape[0]), sc, p(Q0), iters)
+
+    return decode
+
+
+def make_conv1d_update(NS, channels):
+    """The causal conv1d update alone, with the arithmetic of the fused kernels.  Returns
+    update(x, conv_state, conv_weight, conv_bias, idx, out): out bf16 [N, channels] receives the activated rows, conv_state
+    (slot, channel, width - 1) is advanced; rows with idx <= 0 are skipped.  Stands in for vLLM's causal_conv1d_update on
+    single-token rows (call sites reference leapquant/vllm/gdn.py:32, leapquant/vllm/glm.py:72)."""
+    fn = _lib.lib().lq_causal_conv1d_update
+    p = _lib.ptr
+
+    def update(x, conv_state, conv_weight, conv_bias, idx, out):
+        cv = _lib.conv1d(x, conv_state, conv_weight, conv_bias)
+        _launch(fn, "lq_causal_conv1d_update", x, cv, p(idx), int(x.shape[0]), int(channels), int(NS), p(out), out.stride(0))
+
+    return update
+
+
 def make_flush(NS, HV, K, V, L, SS, R=4, ITERS=1, SMS=148, NCG=3, MAXIT=128, PAD=8, KDA=False, MMT="bf16", PNMIN=1e-20,
                NMAX=0, NTP=0, RSG=None):
     """End-of-window flush of every head of the rows idx whose window is full.  Returns

@@ -89,6 +89,8 @@ class LeapQuantState:
         self.kflush = KN.make_flush(NS, HV, K, V, L, SS, R=R, ITERS=1, KDA=kda, NMAX=nmax)
         self.kdecode = KN.make_decode(NS, HV, H, K, V, L, SS, R=R, ITERS=1, KDA=kda, GLB=float(gate_lower_bound),
                                       scale=(128 ** -0.5 if kda else None))
+        self.kdecode_conv = KN.make_decode_conv(NS, HV, H, K, V, L, SS, R=R, ITERS=1, KDA=kda, GLB=float(gate_lower_bound),
+                                                scale=(128 ** -0.5 if kda else None))
         self.fused = True                                     # decode() = one fused launch; False = step then flush
         self.kdeq = KN.make_dequant(NS, HV, K, V, L, SS, buf_dtype=KN.BF16, R=R, kda=kda)
         self.kquant = KN.make_quantize(NS, HV, K, V, L, SS, R=R, ITERS=3 if kda else 1, kda=kda)
@@ -139,6 +141,21 @@ class LeapQuantState:
             G = self.Gd
         self.kflush(v["q32"], v["Sk"], v["Sv"], v["skv"], self.Kbuf, self.Ubuf, self.Wbuf, self.Pbuf, G, self.hcnt,
                     v["sq16"], v["uq"], self.Q0, idx)
+
+    def decode_conv(self, ssm, x, conv_state, conv_weight, conv_bias, a, b, A_log, dt_bias, idx, out):
+        """decode() with the causal conv1d update of the step fused in: x bf16 [N, >= 2HK + HV*V] holds the RAW q | k | v
+        projections, conv_state is the engine's conv cache viewed (slot, channel, width - 1) (any strides; advanced in place),
+        conv_weight bf16 [channels, 4], conv_bias bf16 [channels] or None.  One launch; the activated q | k | v row is never
+        written to memory.  No counterpart in the reference, whose plugin calls vLLM's causal_conv1d_update first."""
+        A_log = A_log if A_log.dtype == torch.float32 else self._p32(A_log)
+        dt_bias = dt_bias if dt_bias.dtype == torch.float32 else self._p32(dt_bias)
+        KA = self.K if self.kda else 1
+        a = a.reshape(a.shape[0], self.HV, KA).contiguous()
+        dt_bias = dt_bias.reshape(self.HV, KA).contiguous()
+        idx = idx if idx.dtype == torch.int32 else idx.to(torch.int32)
+        v = self.views(ssm)
+        bufs = (self.Kbuf, self.Ubuf, self.Wbuf, self.Pbuf) + ((self.Gbuf,) if self.kda else ()) + (self.hcnt,)
+        self.kdecode_conv(v["q32"], *bufs, x, conv_state, conv_weight, conv_bias, a, b, A_log, dt_bias, self.Q0, idx, out)
 
     def dequantize(self, ssm, idx):
         """Materialize the fp32 state of the slots idx in place (before the engine's own prefill kernel runs on them)."""

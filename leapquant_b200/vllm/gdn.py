@@ -25,6 +25,7 @@ class GdnAdapter:
         self.engine_core = getattr(self.cls, self.core_name)
         self.engine_decode_kernel = getattr(module, "fused_sigmoid_gating_delta_rule_update", None)
         self.mixed_layer = None                               # the layer whose MIXED step is inside the engine's forward right now
+        self.fuse_conv = True                                 # pure decode: conv1d update fused into the decode launch
 
     # ---- pieces ----
     def state_of(self, layer):
@@ -36,6 +37,12 @@ class GdnAdapter:
         slots = md.non_spec_state_indices_tensor[:n]
         conv_cache, ssm = layer.kv_cache[0], layer.kv_cache[1]
         conv_state = conv_cache if self.conv_state_dim_first() else conv_cache.transpose(-1, -2)
+        if self.fuse_conv and layer.activation in ("silu", "swish") and mixed_qkv.dtype == torch.bfloat16:
+            # conv1d update, step and flush as ONE launch: the activated q | k | v row never goes through memory
+            st = self.state_of(layer)
+            st.decode_conv(ssm, mixed_qkv[:n], conv_state, conv_weight_2d(layer.conv1d), layer.conv1d.bias, a[:n].contiguous(),
+                           b[:n].contiguous(), layer.A_log, layer.dt_bias, slots, core_attn_out[:n].view(n, st.HV, st.V))
+            return
         mixed = self.conv_update(mixed_qkv[:n], conv_state, conv_weight_2d(layer.conv1d), layer.conv1d.bias, layer.activation,
                                  conv_state_indices=slots, validate_data=False)
         st = self.state_of(layer)

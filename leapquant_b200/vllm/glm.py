@@ -21,6 +21,7 @@ class KdaAdapter:
         self.conv_update = causal_conv1d_update
         self.eager_break = eager_break
         self.engine_forward = getattr(self.cls._forward, "__wrapped__", self.cls._forward)
+        self.fuse_conv = True                                 # pure decode: conv1d update fused into the decode launch
 
     def state_of(self, layer):
         return get_state(layer, layer.kv_cache[1], H=layer.local_num_heads, kda=True,
@@ -78,6 +79,10 @@ class KdaAdapter:
                                                     layer.A_log.view(-1), layer.dt_bias, slots, core_attn_out[0, :cnt])
         if plan.route is Route.DECODE:
             slots = m.non_spec_state_indices_tensor[:n]
+            if self.fuse_conv and qkv_proj_states.dtype == torch.bfloat16:
+                st.decode_conv(ssm, qkv_proj_states[:n], conv_state, wconv, layer.q_conv1d.bias, g1[0, :n], beta[0, :n].contiguous(),
+                               layer.A_log.view(-1), layer.dt_bias, slots, core_attn_out[0, :n])
+                return
             mixed = self.conv_update(qkv_proj_states[:n], conv_state, wconv, layer.q_conv1d.bias, activation="silu",
                                      conv_state_indices=slots)
             decode(mixed, n, slots)

@@ -630,6 +630,37 @@ def fp32_kda_recurrence(S, q, k, v, alpha, beta, scale=None):
 
 
 # --------------------------------------------------------------------------------------------------------------
+# causal conv1d update that precedes the decode step in the serving engine (not part of the reference package: the plugin
+# calls vLLM's Triton kernel, call sites leapquant/vllm/gdn.py:32 and leapquant/vllm/glm.py:72; vllm==0.30.0 is not vendored)
+# --------------------------------------------------------------------------------------------------------------
+def causal_conv1d_update(x, conv_state, weight, bias, idx):
+    """Single-token causal conv1d update with SiLU, restating the published algorithm of vLLM's
+    `causal_conv1d_update` (vllm/model_executor/layers/mamba/ops/causal_conv1d.py, `_causal_conv1d_update_kernel`):
+    per row n with slot = idx[n] > 0 and channel c: window = (state[slot, c, 0 .. W-2], x[n, c]); every product
+    weight[c, t] * window[t] is a bf16 x bf16 product rounded to bf16; they are added to the bias in fp32, taps in order;
+    out = acc / (1 + exp(-acc)) rounded to bf16; state[slot, c] <- window[1:].  x bf16 [N, C], conv_state bf16 (slot, channel,
+    W - 1) (any strides; updated in place), weight bf16 [C, W], bias bf16 [C] or None.  Rows with idx <= 0 are skipped and their
+    output rows are left as they are (zeros here).  Parity at this boundary is unpinned by the reference: its repository holds
+    no test or vector for it."""
+    N, C = x.shape[0], weight.shape[0]
+    W = weight.shape[1]
+    out = torch.zeros(N, C, dtype=torch.bfloat16)
+    idx = idx.to(torch.int64)
+    rows = torch.nonzero(idx > 0).flatten()
+    if rows.numel() == 0:
+        return out
+    sl = idx[rows]
+    win = torch.cat([conv_state[sl].to(torch.float32), x[rows, :C].to(torch.float32)[..., None]], -1)      # [n, C, W]
+    acc = (bias.to(torch.float32) if bias is not None else torch.zeros(C))[None].expand(rows.numel(), C).clone()
+    wf = weight.to(torch.float32)
+    for t in range(W):
+        acc = acc + _bf16(win[..., t] * wf[None, :, t])
+    out[rows] = (acc / (1.0 + torch.exp(-acc))).to(torch.bfloat16)
+    conv_state[sl] = win[..., 1:].to(torch.bfloat16)
+    return out
+
+
+# --------------------------------------------------------------------------------------------------------------
 # synthetic workloads (the seeded distributions of the benchmark configurations)
 # --------------------------------------------------------------------------------------------------------------
 def synth_inputs(N, H, HV, K, V, steps, seed, kda=False, dtype=torch.bfloat16):

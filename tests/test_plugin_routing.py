@@ -43,6 +43,12 @@ class Recorder:
         self.log.append(("decode", tuple(mixed.shape), tuple(a.shape), tuple(b.shape), ints(idx), tuple(out.shape)))
         out.fill_(1)
 
+    def decode_conv(self, ssm, x, conv_state, conv_weight, conv_bias, a, b, A_log, dt_bias, idx, out):
+        assert b.is_contiguous()
+        self.log.append(("decode_conv", tuple(x.shape), tuple(conv_state.shape), tuple(conv_weight.shape), tuple(a.shape), ints(idx),
+                         tuple(out.shape)))
+        out.fill_(1)
+
     def dequantize(self, ssm, idx):
         self.log.append(("dequantize", ints(idx)))
 
@@ -174,7 +180,7 @@ def gdn_layer(eng, prefix="layers.3.linear_attn"):
                A_log=torch.zeros(HV), dt_bias=torch.zeros(HV), engine_plan=None, engine_slots=None, engine_kw={}), C
 
 
-def run_gdn_scenarios(which):
+def run_gdn_scenarios(which, fuse=False):
     log = []
     eng = StubEngine(log)
     try:
@@ -185,10 +191,12 @@ def run_gdn_scenarios(which):
             log.append(("get_state", kw.get("H"), kw.get("nmax"), bool(kw.get("kda", False))))
             return states.setdefault(id(layer), Recorder(log, kw))
         gmod.get_state = fake_get_state
-        gmod.install([48])
+        adapter = gmod.install([48])
+        if adapter is not None:
+            adapter.fuse_conv = fuse                              # (the reference plugin has no fused conv: compare without it)
         layer, C = gdn_layer(eng)
         T = 6
-        x, b, a, out = torch.zeros(T, C), torch.zeros(T, 4), torch.zeros(T, 4), torch.zeros(T, 4 * 128)
+        x, b, a, out = torch.zeros(T, C, dtype=torch.bfloat16 if fuse else torch.float32), torch.zeros(T, 4), torch.zeros(T, 4), torch.zeros(T, 4 * 128)
         I = lambda *v: torch.tensor(v, dtype=torch.int32)
         call = lambda: layer._forward_core(mixed_qkv=x, b=b, a=a, core_attn_out=out)
 
@@ -248,7 +256,7 @@ def kda_layer(eng, prefix="layers.1.linear_attn"):
                dt_bias=torch.zeros(HV * D)), C
 
 
-def run_kda_scenarios(which):
+def run_kda_scenarios(which, fuse=False):
     log = []
     eng = StubEngine(log)
     try:
@@ -259,10 +267,12 @@ def run_kda_scenarios(which):
             log.append(("get_state", kw.get("H"), kw.get("nmax"), bool(kw.get("kda", False)), kw.get("gate_lower_bound")))
             return states.setdefault(id(layer), Recorder(log, kw))
         kmod.get_state = fake_get_state
-        kmod.install([16])
+        adapter = kmod.install([16])
+        if adapter is not None:
+            adapter.fuse_conv = fuse
         layer, C = kda_layer(eng)
         T = 7
-        x, g1, beta = torch.zeros(T, C), torch.zeros(1, T, 4, 128), torch.zeros(1, T, 4)
+        x, g1, beta = torch.zeros(T, C, dtype=torch.bfloat16 if fuse else torch.float32), torch.zeros(1, T, 4, 128), torch.zeros(1, T, 4)
         out = torch.zeros(1, T, 4, 128)
         I = lambda *v: torch.tensor(v, dtype=torch.int32)
         call = lambda: layer._forward(qkv_proj_states=x, g1=g1, beta=beta, core_attn_out=out)
@@ -343,6 +353,21 @@ def test_kda_routes_and_call_sequence():
     spec = sect("-- speculative decoding: round trip of every touched slot around the engine's forward")
     assert spec == [("get_state", 4, 16, True, -5.0), ("dequantize", [8, 1, 2, 3, 0]), ("engine_forward", (7, 1536)),
                     ("quantize", [8, 1, 2, 3, 0])]
+
+
+def test_pure_decode_uses_the_fused_conv_launch_by_default():
+    """With the default setting a pure decode step is ONE call: conv1d update + decode, the engine's conv kernel is not called."""
+    sect = lambda log, name: log[log.index(name) + 1: next((i for i in range(log.index(name) + 1, len(log)) if isinstance(log[i], str)), len(log))]
+    g = sect(run_gdn_scenarios("ours", fuse=True), "-- pure decode, 3 live rows of a padded batch")
+    assert [e[0] for e in g] == ["get_state", "decode_conv"]
+    assert g[1] == ("decode_conv", (3, 1024), (9, 1024, 3), (1024, 4), (3, 4), [4, 2, 7], (3, 4, 128))
+    k = sect(run_kda_scenarios("ours", fuse=True), "-- pure decode, 3 rows")
+    assert [e[0] for e in k] == ["get_state", "decode_conv"]
+    assert k[1] == ("decode_conv", (3, 1536), (9, 1536, 3), (1536, 4), (3, 4, 128), [4, 2, 7], (3, 4, 128))
+    import leapquant_b200.vllm.gdn as G
+    import leapquant_b200.vllm.glm as KM
+    src = open(G.__file__).read() + open(KM.__file__).read()
+    assert src.count("self.fuse_conv = True") == 2
 
 
 @pytest.mark.skipif(not HAVE_REF, reason="reference checkout not present")
