@@ -692,6 +692,45 @@ def run_b200(args, wl):
         dist.destroy_process_group()
 
 
+def run_config4(args):
+    """End-to-end tensor-parallel decode of the hybrid model (leapquant_b200/harness.py), 8-bit state against fp32 state, on the
+    GPUs of this launch (TP = world size).  `--c4 small` runs a reduced model for a quick check."""
+    import torch.distributed as dist
+    from leapquant_b200.harness import HybridConfig, run_generation
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+    if args.c4 == "small":
+        cfg = HybridConfig(hidden=1024, layers=8, gdn_key_heads=8, gdn_value_heads=16, attn_q_heads=16, attn_kv_heads=8, mlp=2048, vocab=8192)
+        batch, prompt, new = 16, 256, 64
+    else:
+        cfg = HybridConfig()
+        batch, prompt, new = 64, 4096, args.c4_new_tokens
+    res = {}
+    for state in ("fp32", "int8"):
+        res[state] = run_generation(cfg, state, batch, prompt, new, seed=5)
+        torch.cuda.empty_cache()
+    if rank == 0:
+        a, b = res["int8"], res["fp32"]
+        line = {"metric": "tp_decode_tokens_per_s", "value": a["decode_tokens_per_s"], "unit": "tokens/s", "n_gpus": world,
+                "steps": a["decode_steps_timed"], "warmup": 2, "ms_per_step": a["ms_per_decode_step"], "higher_is_better": True,
+                "scaling": "strong", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+                "config": {"workload": "hybrid_tp_decode_hidden%d_L%d_gdn%d_attn%d_mlp%d_vocab%d" % (
+                    cfg.hidden, cfg.layers, cfg.layers - cfg.layers // cfg.full_attention_every, cfg.layers // cfg.full_attention_every,
+                    cfg.mlp, cfg.vocab), "tensor_parallel": world, "batch": batch, "prompt_len": prompt, "new_tokens": new,
+                    "weights": "random init bf16", "prompts": "uniformly random token ids"},
+                "int8_state": a, "fp32_state": b,
+                "decode_speedup_int8_over_fp32": (b["ms_per_decode_step"] / a["ms_per_decode_step"]) if a["ms_per_decode_step"] else None,
+                "first_tokens_equal": a["first_tokens"] == b["first_tokens"]}
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
 def layer_h2d_d2h(wl, B):
     H, HV, kda = wl["H"], wl["HV"], wl["kda"]
     mixed = B * (2 * H * K + HV * V) * 2
@@ -706,7 +745,9 @@ def main():
     ap.add_argument("--steps", type=int, default=4096)
     ap.add_argument("--warmup", type=int, default=64)
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
-    ap.add_argument("--workload", default="gdn", choices=sorted(WORKLOADS))
+    ap.add_argument("--workload", default="gdn", choices=sorted(WORKLOADS) + ["config4"])
+    ap.add_argument("--c4", default="full", choices=["full", "small"], help="config4: the full hybrid model or a reduced one")
+    ap.add_argument("--c4-new-tokens", type=int, default=2048)
     ap.add_argument("--batch", type=int, default=0)
     ap.add_argument("--only-main", action="store_true", help="skip the secondary keys (kda, batch_sweep, config3, ...)")
     ap.add_argument("--step-impl", type=int, default=-1, help="debug: step kernel driver (see lq_set_option)")
@@ -714,6 +755,8 @@ def main():
                     help="for a profiler: quantize, stagger the fill levels (L - 1 decode launches), 4 more decode launches, "
                          "the prefill round trip once, exit; prints nothing")
     args = ap.parse_args()
+    if args.workload == "config4":
+        return run_config4(args)
     wl = WORKLOADS[args.workload]
     if args.step_impl >= 0:
         from leapquant_b200 import _lib
