@@ -468,6 +468,74 @@ def secondary_layer_numbers(layer, peak, reps_step=3):
     return out
 
 
+def conv_and_fp32_baseline(wl, B, device, peak, graph_steps=16):
+    """Two figures for the Gated DeltaNet layer, staggered fill levels, CUDA graphs of `graph_steps` steps:
+    (a) the decode step with the conv1d update fused in (one launch) against the standalone conv kernel followed by decode;
+    (b) the serving engine's own path on an fp32 state -- vLLM's causal_conv1d_update + packed-decode kernels, the path the
+        reference plugin replaces -- when that vLLM is importable: the kernel-level speed-up the reference publishes is
+        measured against this."""
+    from leapquant_b200.kernels import make_conv1d_update
+    H, HV, L = wl["H"], wl["HV"], wl["L"]
+    C = 2 * H * K + HV * V
+    ly = Layer(wl, B, device, seed=500, host_io=False)
+    NS = ly.ssm.shape[0]
+    g = torch.Generator(device=device).manual_seed(9)
+    x = (torch.randn(L, B, C, generator=g, device=device) * 0.7).to(torch.bfloat16)
+    conv_store = torch.randn(NS, 3, C, generator=g, device=device).to(torch.bfloat16)       # (slot, tap, channel)
+    conv_state = conv_store.transpose(-1, -2)
+    w = (torch.randn(C, 4, generator=g, device=device) * 0.5).to(torch.bfloat16)
+    bias = torch.zeros(C, dtype=torch.bfloat16, device=device)
+    for t in range(3):
+        ly.decode_resident(t)
+    ly.to_lockstep()
+    ly.stagger()
+    conv = make_conv1d_update(NS, C)
+    mixed = torch.zeros(B, C, dtype=torch.bfloat16, device=device)
+
+    def fused(t):
+        ly.st.decode_conv(ly.ssm, x[t % L], conv_state, w, bias, ly.a[t % L], ly.b[t % L], ly.A_log, ly.dtb, ly.idx, ly.out)
+
+    def unfused(t):
+        conv(x[t % L], conv_state, w, bias, ly.idx, mixed)
+        ly.st.decode(ly.ssm, mixed, ly.a[t % L], ly.b[t % L], ly.A_log, ly.dtb, ly.idx, ly.out)
+
+    def time_graph(fn, nsteps):
+        for t in range(2):
+            fn(t)
+        torch.cuda.synchronize()
+        gr = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(gr):
+            for t in range(nsteps):
+                fn(t)
+        dt, reps = replay_timed(gr, 1, 0.1)
+        return dt / (reps * nsteps)
+
+    out = {"batch": B}
+    tf, tu = time_graph(fused, L), time_graph(unfused, L)
+    out["conv_fused_decode"] = {"ms_per_step_fused": 1e3 * tf, "ms_per_step_conv_then_decode": 1e3 * tu, "launches_fused": 1,
+                                "launches_unfused": 2, "saved_us_per_step": 1e6 * (tu - tf)}
+    try:
+        from vllm.model_executor.layers.fla.ops.fused_recurrent import fused_recurrent_gated_delta_rule_packed_decode as eng_decode
+        from vllm.model_executor.layers.mamba.ops.causal_conv1d import causal_conv1d_update as eng_conv
+        ssm32 = torch.randn(NS, HV, V, K, generator=g, device=device) * 0.1
+        o32 = torch.zeros(B, 1, HV, V, dtype=torch.bfloat16, device=device)
+        a16, b16 = ly.a.contiguous(), ly.b.contiguous()
+
+        def engine(t):
+            m = eng_conv(x[t % L], conv_state, w, bias, "silu", conv_state_indices=ly.idx)
+            eng_decode(mixed_qkv=m, a=a16[t % L], b=b16[t % L], A_log=ly.A_log, dt_bias=ly.dtb, scale=K ** -0.5, initial_state=ssm32,
+                       out=o32, ssm_state_indices=ly.idx, use_qk_l2norm_in_kernel=True)
+
+        te = time_graph(engine, graph_steps)
+        out["fp32_state_engine_kernels"] = {"ms_per_step": 1e3 * te, "head_steps_per_s": B * HV / te,
+                                            "gbs": B * HV * 2 * 4 * V * K / te / 1e9, "frac_of_measured_hbm": B * HV * 2 * 4 * V * K / te / 1e9 / peak,
+                                            "kernels": "vllm causal_conv1d_update + fused_recurrent_gated_delta_rule_packed_decode (Triton), fp32 state",
+                                            "speedup_of_fused_int8_decode": te / tf}
+    except Exception as e:                                       # the engine is not importable here: no fp32-state figure
+        out["fp32_state_engine_kernels"] = {"unavailable": str(e).splitlines()[0][:160] if str(e) else type(e).__name__}
+    return out
+
+
 def outlier_quantize(layer, peak):
     """The isolated quantize on fp32 states drawn as N(0,1) with 1 % of the rows and of the columns scaled by 50."""
     wl, B = layer.wl, layer.B
@@ -641,6 +709,8 @@ def run_b200(args, wl):
                 del lys
                 torch.cuda.empty_cache()
             extras["batch_sweep"] = sweep
+            if not kda:
+                extras["conv_and_fp32_state"] = [conv_and_fp32_baseline(wl, Bs, device, peak) for Bs in (32, 128, 256)]
         if not args.batch:
             layer.graph = None
             del layer

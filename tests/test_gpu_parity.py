@@ -447,9 +447,10 @@ def test_decode_free_running(kda, L, R, steps, step_impl):
     full = gpu.full_state(idx)
     state_err = float((full - S).abs().max() / S.abs().max())
     print(f"free-running kda={kda}: worst vs oracle {worst_oracle:.3e}, vs fp32 recurrence {worst_fp32:.3e}, state {state_err:.3e}")
-    assert worst_oracle < 2e-2, worst_oracle
-    assert worst_fp32 < 3e-2, worst_fp32
-    assert state_err < 3e-2
+    # observed on a B200: 3.3e-3 vs the oracle, 5.9e-3 vs the fp32 recurrence, 2.5e-3 on the state; twice that is the bound
+    assert worst_oracle < 7e-3, worst_oracle
+    assert worst_fp32 < 1.2e-2, worst_fp32
+    assert state_err < 6e-3
 
 
 def test_config0_prefill_then_512_decode_steps():
@@ -494,10 +495,11 @@ def test_config0_prefill_then_512_decode_steps():
     state_err = float((full - S).abs().max() / S.abs().max())
     print(f"config 0: worst vs oracle {worst_oracle:.3e}, vs fp32 recurrence {worst_fp32:.3e}, rms {(sq_err / sq_ref) ** 0.5:.3e}, "
           f"state {state_err:.3e}")
-    assert worst_oracle < 2e-2, worst_oracle
-    assert worst_fp32 < 3e-2, worst_fp32
-    assert (sq_err / sq_ref) ** 0.5 < 1e-2, (sq_err / sq_ref) ** 0.5         # relative RMS error of the outputs over the run
-    assert state_err < 3e-2
+    # observed on a B200: 3.7e-3 vs the oracle, 5.7e-3 vs the fp32 recurrence, 1.9e-3 relative RMS, 2.7e-3 on the state
+    assert worst_oracle < 8e-3, worst_oracle
+    assert worst_fp32 < 1.2e-2, worst_fp32
+    assert (sq_err / sq_ref) ** 0.5 < 4e-3, (sq_err / sq_ref) ** 0.5         # relative RMS error of the outputs over the run
+    assert state_err < 6e-3
 
 
 def test_sharded_equals_unsharded():
