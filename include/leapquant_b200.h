@@ -65,7 +65,10 @@ int lq_device_status(int* status);
  * asynchronous copies (default), 1 = one CTA per (row, head) with plain loads and the same arithmetic, 2 = one warp per
  * (row, head) in registers (GDN only; KDA keeps the default).  1 and 2 exist for debugging and comparison.
  * "pdl": 1 (default) launches the step and flush kernels with programmatic stream serialisation, so that the launch and
- * set-up of one overlap the tail of its predecessor on the stream; 0 = plain launches. */
+ * set-up of one overlap the tail of its predecessor on the stream; 0 = plain launches.
+ * "work_list_min_programs": the fewest (row, head) programs of a fused decode call for which the `work` list passed to it
+ * is used (-1 = default, sixteen per SM; 0 = whenever `work` is given).  The list costs a few global atomics per launch,
+ * about three microseconds, and saves the flush of one head when the due heads sit unevenly on the CTAs. */
 int lq_set_option(const char* name, int32_t value);
 
 /* GDN decode step.  Replaces the kernel built by make_gdn_step (reference leapquant/kernels.py:27-692, launch
@@ -100,14 +103,27 @@ int lq_flush(const lq_dims* d, void* ssm, void* Kbuf, void* Ubuf, float* Wbuf, f
  * flushes that head itself after its last program, so the flush needs no due scan, no second launch and finds the
  * head's window rows in cache.  Same arguments as the step plus the flush's Q0 and iters; same results as the two calls.
  * Where the fused form is not available (a debug step driver is selected, or the working set of one flush team does not
- * fit in the shared memory the step pipeline leaves behind) the two kernels are launched one after the other. */
+ * fit in the shared memory the step pipeline leaves behind) the two kernels are launched one after the other.
+ *
+ * `work` (optional, may be NULL): device scratch of at least lq_decode_work_bytes(min(N, NS), HV) bytes, 8-byte aligned, ALL
+ * ZERO before the first call that uses it; the kernel leaves it all zero again.  With it the CTAs share one list of the
+ * heads whose window filled in this call: a CTA flushes the first such head of its own and appends the others, and a CTA
+ * that has none left takes them over (a serving batch fills the windows of a few rows per step, and the program-to-CTA
+ * map puts their heads on the same CTAs now and then).  Results do not depend on it.  Calls that use the same `work` must
+ * not overlap on the GPU.  The list makes CTAs wait for one another, so every CTA of the launch must be resident at once:
+ * the launch uses one CTA per SM, which a process that owns the whole GPU gives; under a limit on the SMs a context may
+ * use (MPS active-thread percentage, green contexts) pass NULL.  Small calls ignore it (see "work_list_min_programs").
+ * NS * HV must stay below 2^23. */
 int lq_gdn_decode(const lq_dims* d, void* ssm, void* Kbuf, void* Ubuf, float* Wbuf, float* Pbuf, int32_t* hcnt,
                   const void* mixed, const void* a, const void* b, const float* A_log, const float* dt_bias,
-                  const int32_t* idx, void* o, int32_t N, float scale, const float* Q0, int32_t iters, void* stream);
+                  const int32_t* idx, void* o, int32_t N, float scale, const float* Q0, int32_t iters, void* work,
+                  int64_t work_bytes, void* stream);
 int lq_kda_decode(const lq_dims* d, void* ssm, void* Kbuf, void* Ubuf, float* Wbuf, float* Pbuf, void* Gbuf,
                   int32_t* hcnt, const void* mixed, const void* a, const void* b, const float* A_log,
                   const float* dt_bias, const int32_t* idx, void* o, int32_t N, float scale, float gate_lower_bound,
-                  const float* Q0, int32_t iters, void* stream);
+                  const float* Q0, int32_t iters, void* work, int64_t work_bytes, void* stream);
+/* Bytes of the `work` scratch for calls of up to `rows` live rows with HV value heads. */
+int64_t lq_decode_work_bytes(int32_t rows, int32_t HV);
 
 /* Operands of the causal conv1d update that precedes every decode step in the serving engine (the reference plugin calls
  * vLLM's causal_conv1d_update right before LeapQuantState.decode: reference leapquant/vllm/gdn.py:31-33, glm.py:72-73).
@@ -137,11 +153,12 @@ typedef struct lq_conv1d {
  * whose flush work area does not fit beside the step pipeline returns LQ_ERR_UNSUPPORTED. */
 int lq_gdn_decode_conv(const lq_dims* d, void* ssm, void* Kbuf, void* Ubuf, float* Wbuf, float* Pbuf, int32_t* hcnt,
                        const lq_conv1d* conv, const void* a, const void* b, const float* A_log, const float* dt_bias,
-                       const int32_t* idx, void* o, int32_t N, float scale, const float* Q0, int32_t iters, void* stream);
+                       const int32_t* idx, void* o, int32_t N, float scale, const float* Q0, int32_t iters, void* work,
+                       int64_t work_bytes, void* stream);
 int lq_kda_decode_conv(const lq_dims* d, void* ssm, void* Kbuf, void* Ubuf, float* Wbuf, float* Pbuf, void* Gbuf,
                        int32_t* hcnt, const lq_conv1d* conv, const void* a, const void* b, const float* A_log,
                        const float* dt_bias, const int32_t* idx, void* o, int32_t N, float scale, float gate_lower_bound,
-                       const float* Q0, int32_t iters, void* stream);
+                       const float* Q0, int32_t iters, void* work, int64_t work_bytes, void* stream);
 
 /* The conv1d update alone (same arithmetic as inside the fused kernels): out bf16 [N, out_stride] receives the activated
  * q | k | v rows, the state is advanced.  Stands in for vLLM's causal_conv1d_update on single-token rows (call sites

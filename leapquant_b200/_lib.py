@@ -14,6 +14,7 @@ LIB_PATH = os.environ.get("LEAPQUANT_B200_LIB") or os.path.join(_HERE, "libleapq
 
 EXPORTS = ("lq_version", "lq_strerror", "lq_last_cuda_error", "lq_device_status", "lq_set_option", "lq_gdn_step", "lq_kda_step",
            "lq_flush", "lq_gdn_decode", "lq_kda_decode", "lq_gdn_decode_conv", "lq_kda_decode_conv", "lq_causal_conv1d_update",
+           "lq_decode_work_bytes",
            "lq_quantize", "lq_dequant", "lq_lowrank")
 
 _P = ctypes.c_void_p
@@ -58,11 +59,14 @@ def lib():
         L.lq_gdn_step.argtypes = [D, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _I, _F, _P]
         L.lq_kda_step.argtypes = [D, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _I, _F, _F, _P]
         L.lq_flush.argtypes = [D, _P, _P, _P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _P]
-        L.lq_gdn_decode.argtypes = [D, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _I, _F, _P, _I, _P]
-        L.lq_kda_decode.argtypes = [D, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _I, _F, _F, _P, _I, _P]
+        I64 = ctypes.c_int64
+        L.lq_gdn_decode.argtypes = [D, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _I, _F, _P, _I, _P, I64, _P]
+        L.lq_kda_decode.argtypes = [D, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _I, _F, _F, _P, _I, _P, I64, _P]
+        L.lq_decode_work_bytes.argtypes = [_I, _I]
+        L.lq_decode_work_bytes.restype = I64
         C = ctypes.POINTER(LqConv1d)
-        L.lq_gdn_decode_conv.argtypes = [D, _P, _P, _P, _P, _P, _P, C, _P, _P, _P, _P, _P, _P, _I, _F, _P, _I, _P]
-        L.lq_kda_decode_conv.argtypes = [D, _P, _P, _P, _P, _P, _P, _P, C, _P, _P, _P, _P, _P, _P, _I, _F, _F, _P, _I, _P]
+        L.lq_gdn_decode_conv.argtypes = [D, _P, _P, _P, _P, _P, _P, C, _P, _P, _P, _P, _P, _P, _I, _F, _P, _I, _P, I64, _P]
+        L.lq_kda_decode_conv.argtypes = [D, _P, _P, _P, _P, _P, _P, _P, C, _P, _P, _P, _P, _P, _P, _I, _F, _F, _P, _I, _P, I64, _P]
         L.lq_causal_conv1d_update.argtypes = [C, _P, _I, _I, _I, _P, ctypes.c_int64, _P]
         L.lq_quantize.argtypes = [D, _P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _P]
         L.lq_dequant.argtypes = [D, _P, _P, _P, _P, _P, _P, _P, _P, _I, _I, _P]

@@ -349,8 +349,10 @@ __device__ __forceinline__ void cholqr_pass_team(float (&x)[R], float* __restric
     }
 }
 
-// Arguments of the flush of one head (plain pointers: the fused decode kernel flushes heads whose window rows it wrote
-// itself a moment before, so none of them may be read through the non-coherent path).
+// Arguments of the flush of one head (plain pointers: the fused decode kernel flushes heads whose window rows it -- or, with
+// the shared work list, ANOTHER CTA of the same launch -- wrote a moment before: none of them may be read through the
+// non-coherent path, and what the step writes (window rows, weights, decay) is read with ld.global.cg, past the L1 of an SM
+// that may hold an older copy of a line it shares with a neighbouring head).
 struct FlushArgs {
     lq_dims d;
     char* ssm;
@@ -444,7 +446,7 @@ __device__ __forceinline__ bool flush_head(const FlushSmem& s, const FlushArgs& 
     const int64_t sh = q;
     char* base = head_base(ssm, d.SS, slot, hv);
     float p = 1.f;
-    if (!KDA) p = fmaxf(Pbuf[sh], PNMIN);
+    if (!KDA) p = fmaxf(__ldcg(Pbuf + sh), PNMIN);
 
     // ---- stage A: operands to shared memory; every global load of the stage is issued before the first store so that
     //      their latencies overlap.  The window rows go straight into the tensor-core operand tiles. ----
@@ -458,9 +460,9 @@ __device__ __forceinline__ bool flush_head(const FlushSmem& s, const FlushArgs& 
         uint16_t fu[NF], fq[NF];
         uint4 tk[NTC], tu[NTC], tg[KDA ? NTC : 1];
         const uint4* gbc = reinterpret_cast<const uint4*>(Gbuf + (KDA ? sh * L * KD : 0));
-        if (tid < L) wv = Wbuf[sh * L + tid];
+        if (tid < L) wv = __ldcg(Wbuf + sh * L + tid);
         if (tid < 128) {
-            if (KDA) pcv = Pbuf[sh * KD + tid];
+            if (KDA) pcv = __ldcg(Pbuf + sh * KD + tid);
             skv = reinterpret_cast<const float*>(base + CK_SK)[tid];
             svv = reinterpret_cast<const float*>(base + CK_SV)[tid];
         }
@@ -470,16 +472,16 @@ __device__ __forceinline__ bool flush_head(const FlushSmem& s, const FlushArgs& 
             const bool in = i < R * 128;
             fu[u] = in ? uq[r * (KD + VD) + c] : uint16_t(0);
             fq[u] = in ? uq[r * (KD + VD) + KD + c] : uint16_t(0);
-            pcf[u] = (KDA && in) ? Pbuf[sh * KD + c] : 0.f;
+            pcf[u] = (KDA && in) ? __ldcg(Pbuf + sh * KD + c) : 0.f;
         }
 #pragma unroll
         for (int u = 0; u < NTC; ++u) {
             const int i = tid + u * NT;
             const bool in = i < L * 16;
-            tk[u] = in ? kb[i] : make_uint4(0u, 0u, 0u, 0u);
-            tu[u] = in ? ub[i] : make_uint4(0u, 0u, 0u, 0u);
-            wrow[u] = (!KDA && in) ? Wbuf[sh * L + (i >> 4)] : 0.f;
-            if (KDA) tg[u] = in ? gbc[i] : make_uint4(0u, 0u, 0u, 0u);
+            tk[u] = in ? __ldcg(kb + i) : make_uint4(0u, 0u, 0u, 0u);
+            tu[u] = in ? __ldcg(ub + i) : make_uint4(0u, 0u, 0u, 0u);
+            wrow[u] = (!KDA && in) ? __ldcg(Wbuf + sh * L + (i >> 4)) : 0.f;
+            if (KDA) tg[u] = in ? __ldcg(gbc + i) : make_uint4(0u, 0u, 0u, 0u);
         }
         if (tid < L) s.w[tid] = wv;
         if (tid < 128) {

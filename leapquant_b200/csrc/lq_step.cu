@@ -790,7 +790,28 @@ struct FuseTail {
     int iters;
     int teams;                                      // teams of 256 threads that fit in the ring side by side (1 or 2)
     int team_bytes;                                 // shared memory of one team
+    int* work;                                      // shared list of due heads (global scratch, see WL_*) or null: every CTA flushes its own
 };
+// Shared work list of the fused flush (global scratch of the caller, all zero between launches).  A CTA keeps the first head
+// whose window it filled and appends the others; when it has flushed its own it draws tickets (fetch-and-add) and flushes
+// the entries its tickets name, whoever appended them, so a CTA without due heads takes over the second or third head of a
+// CTA that has several.  One 64-bit word holds the three counters -- tickets drawn, entries appended, CTAs that have
+// reported -- so one atomic both draws a ticket and tells whether the list is final.  A ticket past the end of the list is
+// resolved when every CTA has reported: its holder waits for the slowest CTA's step, as the launch does anyway.  That wait
+// needs every CTA of the launch to be resident at once, which one CTA per SM on a whole GPU gives; a context limited to
+// part of the SMs must run without the list (the wait is bounded and ends with ST_FLUSH_TIMEOUT in the status word).  The
+// last CTA to leave zeroes the list for the next launch.
+constexpr int WL_EXITED = 2, WL_ITEMS = 16;                      // int offsets (the counter word is ints 0 and 1); item = head + 1, 0 = not written yet
+constexpr int WL_FIELD = 24;                                     // bits of the ticket and entry counters
+constexpr unsigned long long WL_TAKEN1 = 1ull, WL_COUNT1 = 1ull << WL_FIELD, WL_DONE1 = 1ull << (2 * WL_FIELD);
+__device__ __forceinline__ int wl_taken(unsigned long long w) { return int(w & (WL_COUNT1 - 1)); }
+__device__ __forceinline__ int wl_count(unsigned long long w) { return int((w >> WL_FIELD) & (WL_COUNT1 - 1)); }
+__device__ __forceinline__ int wl_done(unsigned long long w) { return int(w >> (2 * WL_FIELD)); }
+__device__ __forceinline__ void st_volatile_i32(int* p, int v) { *reinterpret_cast<volatile int*>(p) = v; }
+__device__ __forceinline__ int ld_volatile_i32(const int* p) { return *reinterpret_cast<const volatile int*>(p); }
+__device__ __forceinline__ unsigned long long ld_volatile_u64(const unsigned long long* p) {
+    return *reinterpret_cast<const volatile unsigned long long*>(p);
+}
 
 #ifndef LQ_NPW
 #define LQ_NPW 2
@@ -1121,46 +1142,142 @@ __global__ void __launch_bounds__(UT + NG * GT, 1) step_pipelined_kernel(StepPar
     // one head per step, and the latency of that flush is what the step pays.
     if constexpr (FUSE) {
         __shared__ uint32_t tm_slot;
-        __syncthreads();                                         // every role is done; the ring is dead, this CTA's global writes are visible
-        if (*abortf) return;
-        const int ndl = *dl_n;
-        if (ndl == 0) return;                                    // (before any tensor memory is held)
+        __shared__ int s_pop[4];
         static_assert(UT + NG * GT == 512, "the fused flush is written for two teams of 256 threads");
         const int nteams = ft.teams;                             // work areas that fit in the ring: 1 or 2
         const int team = tid >> 8, ttid = tid & 255;
-        if (warp == 0) tmem_alloc(&tm_slot, 2 * TMEM_COLS);
-        const FlushSmem fs = flush_carve<R>(stage_smem + (team < nteams ? team : 0) * ft.team_bytes, L, KDA);
-        if (team < nteams) flush_init<R>(fs, ft.Q0, ttid, 256);
-        tc_fence_before_sync();
-        __syncthreads();
-        tc_fence_after_sync();
-        const uint32_t tm = tm_slot;
         FlushArgs A;
         A.d = P.d; A.ssm = P.ssm; A.Kbuf = P.Kbuf; A.Ubuf = P.Ubuf; A.Wbuf = P.Wbuf; A.Pbuf = P.Pbuf; A.Gbuf = P.Gbuf;
         A.hcnt = P.hcnt; A.Q0 = ft.Q0; A.iters = ft.iters;
-        int k = 0;
-        if (nteams == 2) {
-            auto tsync = [&] { named_bar(8 + team, 256); };
-            const int npair = ndl >> 1;
-            bool ok = true;
-            for (int i = 0; i < npair && ok; ++i) ok = flush_head<R, KDA, 8>(fs, A, dl[2 * i + team], ttid, tm + team * TMEM_COLS, tsync);
-            if (!ok && ttid == 0) *abortf = 1;
-            k = 2 * npair;
+        __syncthreads();                                         // every role is done; the ring is dead, this CTA's global writes are issued
+        const int ndl = *abortf ? 0 : *dl_n;
+        int* const wl = ft.work;
+        unsigned long long* const wlw = reinterpret_cast<unsigned long long*>(wl);
+        if (wl == nullptr && ndl == 0) return;                   // (before any tensor memory is held)
+        // Rounds of heads: without the list one round of this CTA's own heads; with it, the CTA's first head and then one
+        // round per ticket.  `heads` points into shared memory (the CTA's own list or the ticket's entries).
+        const int* heads = dl;
+        int nh = ndl;
+        unsigned long long seen = 0;                             // (thread 0) the counter word as last read
+        int ticket = -1, held = 1;                               // (thread 0) a ticket drawn but not resolved yet, and how many it stands for
+        if (wl != nullptr) {
+            nh = ndl > 0 ? 1 : 0;
+            if (ndl > 1) __threadfence();                        // the step's stores of the appended heads come before their entries
             __syncthreads();
+            if (tid == 0) {
+                if (ndl == 1) {
+                    atomicAdd(wlw, WL_DONE1);                     // nothing to append, nothing to learn yet
+                } else if (ndl == 0) {
+                    seen = atomicAdd(wlw, WL_DONE1 + WL_TAKEN1) + WL_DONE1;
+                    ticket = wl_taken(seen);
+                } else {
+                    seen = atomicAdd(wlw, WL_DONE1 + (ndl - 1) * WL_COUNT1);
+                    const int base = wl_count(seen);
+                    for (int i = 1; i < ndl; ++i) st_volatile_i32(wl + WL_ITEMS + base + i - 1, dl[i] + 1);
+                    seen += WL_DONE1 + (ndl - 1) * WL_COUNT1;
+                }
+            }
         }
-        if (k < ndl && *abortf == 0) {
-            const FlushSmem f0 = flush_carve<R>(stage_smem, L, KDA);      // team 0's area, initialised above
-            for (; k < ndl; ++k)
-                if (!flush_head<R, KDA, 16>(f0, A, dl[k], tid, tm, [] { __syncthreads(); })) break;
+        bool have_tm = false;
+        bool more = true;
+        while (more) {
+            if (nh == 0) {                                       // (shared list only) the next ticket
+                if (tid == 0) {
+                    int q0 = -1, q1 = -1;
+                    if (!*abortf) {
+                        if (ticket < 0) {
+                            // more entries waiting than CTAs: two side by side (throughput); else one by the whole CTA (latency)
+                            held = (nteams == 2 && wl_count(seen) - wl_taken(seen) > grid) ? 2 : 1;
+                            seen = atomicAdd(wlw, held * WL_TAKEN1);
+                            ticket = wl_taken(seen);
+                        }
+                        const int want = held;
+                        bool gave_up = true;
+                        for (uint32_t it = 0; it < WAIT_LIMIT; ++it) {
+                            if (ticket < wl_count(seen) || wl_done(seen) >= grid) { gave_up = false; break; }
+                            if (it > 8) __nanosleep(64);
+                            seen = ld_volatile_u64(wlw);
+                        }
+                        const int valid = gave_up ? 0 : min(want, wl_count(seen) - ticket);
+                        for (int j = 0; j < valid; ++j) {        // between the count and the entry: a moment
+                            int q = -1;
+                            for (uint32_t it = 0; it < WAIT_LIMIT && q < 0; ++it) q = ld_volatile_i32(wl + WL_ITEMS + ticket + j) - 1;
+                            if (q < 0) { gave_up = true; q0 = q1 = -1; break; }
+                            if (j == 0) q0 = q; else q1 = q;
+                        }
+                        if (gave_up) atomicOr(&g_status, ST_FLUSH_TIMEOUT);
+                        __threadfence();                         // the head's data is read after its entry
+                        ticket = -1;
+                        // a long list keeps every CTA busy anyway: draw the next tickets now, so that the atomic's round trip
+                        // runs under this flush (a short list is left to whoever is idle)
+                        if (q0 >= 0 && wl_count(seen) - wl_taken(seen) > 3 * grid) {
+                            held = nteams == 2 ? 2 : 1;
+                            seen = atomicAdd(wlw, held * WL_TAKEN1);
+                            ticket = wl_taken(seen);
+                        }
+                    }
+                    s_pop[0] = q0;
+                    s_pop[1] = q1;
+                }
+                __syncthreads();
+                heads = s_pop;
+                nh = s_pop[0] < 0 ? 0 : (s_pop[1] < 0 ? 1 : 2);
+            }
+            more = nh > 0 && wl != nullptr;
+            if (nh > 0) {
+            if (!have_tm) {                                      // first head of this CTA: tensor memory and the per-team constants
+                if (warp == 0) tmem_alloc(&tm_slot, 2 * TMEM_COLS);
+                const FlushSmem fi = flush_carve<R>(stage_smem + (team < nteams ? team : 0) * ft.team_bytes, L, KDA);
+                if (team < nteams) flush_init<R>(fi, ft.Q0, ttid, 256);
+                tc_fence_before_sync();
+                __syncthreads();
+                tc_fence_after_sync();
+                have_tm = true;
+            }
+            const uint32_t tm = tm_slot;
+            int k = 0;
+            if (nteams == 2 && nh >= 2) {                        // pairs: each team of 8 warps goes through its own heads
+                const FlushSmem fs = flush_carve<R>(stage_smem + team * ft.team_bytes, L, KDA);
+                auto tsync = [&] { named_bar(8 + team, 256); };
+                const int npair = nh >> 1;
+                bool ok = true;
+                for (int i = 0; i < npair && ok; ++i) ok = flush_head<R, KDA, 8>(fs, A, heads[2 * i + team], ttid, tm + team * TMEM_COLS, tsync);
+                if (!ok && ttid == 0) *abortf = 1;
+                k = 2 * npair;
+                __syncthreads();
+            }
+            if (k < nh && *abortf == 0) {                        // a last single head: all 16 warps
+                const FlushSmem f0 = flush_carve<R>(stage_smem, L, KDA);
+                for (; k < nh; ++k)
+                    if (!flush_head<R, KDA, 16>(f0, A, heads[k], tid, tm, [] { __syncthreads(); })) {
+                        if (tid == 0) *abortf = 1;
+                        k = nh;
+                    }
+            }
+            __syncthreads();                                     // (s_pop is rewritten by the next round; abort flag settled)
+            }
+            nh = 0;
         }
         tc_fence_before_sync();
         __syncthreads();
-        if (warp == 0) tmem_dealloc(tm, 2 * TMEM_COLS);
+        if (have_tm && warp == 0) tmem_dealloc(tm_slot, 2 * TMEM_COLS);
+        if (wl != nullptr) {
+            // the last CTA to leave zeroes the list: every other CTA is past its last access
+            if (tid == 0) s_pop[2] = (atomicAdd(wl + WL_EXITED, 1) == grid - 1) ? wl_count(ld_volatile_u64(wlw)) : -1;
+            __syncthreads();
+            const int nclean = s_pop[2];
+            if (nclean >= 0) {
+                for (int i = tid; i < nclean; i += UT + NG * GT) wl[WL_ITEMS + i] = 0;
+                if (tid == 0) { *wlw = 0ull; wl[WL_EXITED] = 0; }
+            }
+        }
     }
 }
 
 // 0 = pipelined, 1 = direct, 2 = one warp per program (GDN; KDA falls back to the pipelined driver)
 static std::atomic<int> g_step_impl{0};
+// fewest (row, head) programs of a decode call for which the shared work list is used; -1 = sixteen per SM
+static std::atomic<int> g_work_list_min{-1};
 
 // fuse != nullptr: the pipelined driver also flushes, in the same launch, the heads whose window it fills (Q0, iters from
 // *fuse).  Returns LQ_ERR_UNSUPPORTED when the fused form is not available for the configuration (debug drivers, a flush
@@ -1199,13 +1316,16 @@ static int launch_step(const StepParams& P, cudaStream_t st, const FuseTail* fus
     const int ring_bytes = int((budget - fixed) & ~size_t(127));
     if (ring_bytes < lay_p) return LQ_ERR_UNSUPPORTED;
     const size_t smem = size_t(ring_bytes) + fixed;
-    FuseTail ft = {nullptr, 0, 0, 0};
+    FuseTail ft = {nullptr, 0, 0, 0, nullptr};
     cudaError_t le;
     if (fuse) {
         ft = *fuse;
         ft.team_bytes = int((flush_smem_bytes<R>(P.d.L, 0, KDA) + 127) & ~size_t(127));
         ft.teams = (2 * ft.team_bytes <= ring_bytes) ? 2 : (ft.team_bytes <= ring_bytes ? 1 : 0);
         if (ft.teams == 0) return LQ_ERR_UNSUPPORTED;
+        // the list costs two or three microseconds of atomics per launch: it pays once a CTA has many programs
+        const int wl_min = g_work_list_min.load(std::memory_order_relaxed);
+        if (int64_t(P.N) * P.d.HV < (wl_min >= 0 ? int64_t(wl_min) : int64_t(16) * device_sm_count())) ft.work = nullptr;
         if (conv) {
             int rc = ensure_smem((const void*)step_pipelined_kernel<R, KDA, NG, true, true>, smem);
             if (rc) return rc;
@@ -1292,6 +1412,10 @@ extern "C" int lq_set_option(const char* name, int32_t value) {
         lq::g_step_impl.store(value, std::memory_order_relaxed);
         return LQ_OK;
     }
+    if (strcmp(name, "work_list_min_programs") == 0) {
+        lq::g_work_list_min.store(value < 0 ? -1 : value, std::memory_order_relaxed);
+        return LQ_OK;
+    }
     if (strcmp(name, "pdl") == 0) {
         lq::g_pdl.store(value != 0, std::memory_order_relaxed);
         return LQ_OK;
@@ -1319,10 +1443,15 @@ extern "C" int lq_kda_step(const lq_dims* d, void* ssm, void* Kbuf, void* Ubuf, 
 static int decode_common(const lq_dims* d, void* ssm, void* Kbuf, void* Ubuf, float* Wbuf, float* Pbuf, void* Gbuf, int32_t* hcnt,
                          const void* mixed, const void* a, const void* b, const float* A_log, const float* dt_bias,
                          const int32_t* idx, void* o, int32_t N, float scale, float glb, bool kda, const float* Q0, int32_t iters,
-                         void* stream, const lq_conv1d* conv = nullptr) {
+                         void* work, int64_t work_bytes, void* stream, const lq_conv1d* conv = nullptr) {
     if (!Q0) return LQ_ERR_NULL;
     if (iters < 0) return LQ_ERR_RANGE;
-    lq::FuseTail ft = {Q0, iters, 0, 0};
+    if (work) {                                                  // shared list of due heads: one entry per head the call can fill
+        if (reinterpret_cast<uintptr_t>(work) & 7) return LQ_ERR_ALIGN;
+        if (d && int64_t(d->NS) * d->HV >= (int64_t(1) << (lq::WL_FIELD - 1))) return LQ_ERR_RANGE;    // the counters are 24-bit fields
+        if (d && N > 0 && work_bytes < lq_decode_work_bytes(N < d->NS ? N : d->NS, d->HV)) return LQ_ERR_RANGE;
+    }
+    lq::FuseTail ft = {Q0, iters, 0, 0, static_cast<int*>(work)};
     int rc = lq::step_common(d, ssm, Kbuf, Ubuf, Wbuf, Pbuf, Gbuf, hcnt, mixed, a, b, A_log, dt_bias, idx, o, N, scale, glb, kda,
                              stream, &ft, conv);
     if (rc != LQ_ERR_UNSUPPORTED || conv) return rc;           // (the conv form exists as one fused launch only)
@@ -1331,36 +1460,42 @@ static int decode_common(const lq_dims* d, void* ssm, void* Kbuf, void* Ubuf, fl
     return lq_flush(d, ssm, Kbuf, Ubuf, Wbuf, Pbuf, Gbuf, hcnt, Q0, idx, N, kda ? 1 : 0, iters, stream);
 }
 
+extern "C" int64_t lq_decode_work_bytes(int32_t rows, int32_t HV) {
+    return 4 * (int64_t(lq::WL_ITEMS) + int64_t(rows > 0 ? rows : 0) * int64_t(HV > 0 ? HV : 0));
+}
+
 extern "C" int lq_gdn_decode(const lq_dims* d, void* ssm, void* Kbuf, void* Ubuf, float* Wbuf, float* Pbuf, int32_t* hcnt,
                              const void* mixed, const void* a, const void* b, const float* A_log, const float* dt_bias,
-                             const int32_t* idx, void* o, int32_t N, float scale, const float* Q0, int32_t iters, void* stream) {
+                             const int32_t* idx, void* o, int32_t N, float scale, const float* Q0, int32_t iters, void* work,
+                             int64_t work_bytes, void* stream) {
     return decode_common(d, ssm, Kbuf, Ubuf, Wbuf, Pbuf, nullptr, hcnt, mixed, a, b, A_log, dt_bias, idx, o, N, scale, 0.f, false, Q0,
-                         iters, stream);
+                         iters, work, work_bytes, stream);
 }
 
 extern "C" int lq_kda_decode(const lq_dims* d, void* ssm, void* Kbuf, void* Ubuf, float* Wbuf, float* Pbuf, void* Gbuf,
                              int32_t* hcnt, const void* mixed, const void* a, const void* b, const float* A_log,
                              const float* dt_bias, const int32_t* idx, void* o, int32_t N, float scale, float glb, const float* Q0,
-                             int32_t iters, void* stream) {
+                             int32_t iters, void* work, int64_t work_bytes, void* stream) {
     return decode_common(d, ssm, Kbuf, Ubuf, Wbuf, Pbuf, Gbuf, hcnt, mixed, a, b, A_log, dt_bias, idx, o, N, scale, glb, true, Q0,
-                         iters, stream);
+                         iters, work, work_bytes, stream);
 }
 
 extern "C" int lq_gdn_decode_conv(const lq_dims* d, void* ssm, void* Kbuf, void* Ubuf, float* Wbuf, float* Pbuf, int32_t* hcnt,
                                   const lq_conv1d* conv, const void* a, const void* b, const float* A_log, const float* dt_bias,
-                                  const int32_t* idx, void* o, int32_t N, float scale, const float* Q0, int32_t iters, void* stream) {
+                                  const int32_t* idx, void* o, int32_t N, float scale, const float* Q0, int32_t iters, void* work,
+                                  int64_t work_bytes, void* stream) {
     if (!conv) return LQ_ERR_NULL;
     return decode_common(d, ssm, Kbuf, Ubuf, Wbuf, Pbuf, nullptr, hcnt, nullptr, a, b, A_log, dt_bias, idx, o, N, scale, 0.f, false, Q0,
-                         iters, stream, conv);
+                         iters, work, work_bytes, stream, conv);
 }
 
 extern "C" int lq_kda_decode_conv(const lq_dims* d, void* ssm, void* Kbuf, void* Ubuf, float* Wbuf, float* Pbuf, void* Gbuf,
                                   int32_t* hcnt, const lq_conv1d* conv, const void* a, const void* b, const float* A_log,
                                   const float* dt_bias, const int32_t* idx, void* o, int32_t N, float scale, float glb,
-                                  const float* Q0, int32_t iters, void* stream) {
+                                  const float* Q0, int32_t iters, void* work, int64_t work_bytes, void* stream) {
     if (!conv) return LQ_ERR_NULL;
     return decode_common(d, ssm, Kbuf, Ubuf, Wbuf, Pbuf, Gbuf, hcnt, nullptr, a, b, A_log, dt_bias, idx, o, N, scale, glb, true, Q0,
-                         iters, stream, conv);
+                         iters, work, work_bytes, stream, conv);
 }
 
 extern "C" int lq_causal_conv1d_update(const lq_conv1d* conv, const int32_t* idx, int32_t N, int32_t channels, int32_t NS, void* out,

@@ -37,6 +37,18 @@ def _launch(fn, what, dev_tensor, *args):
         _lib.check(fn(*args, _lib.stream_of(dev_tensor)), what)
 
 
+def _work(work):
+    """(pointer, bytes) of the optional shared work list of the fused decode (an int32 tensor, all zero), or (None, 0)."""
+    if work is None:
+        return None, 0
+    return _lib.ptr(work), work.numel() * work.element_size()
+
+
+def decode_work_ints(rows, HV):
+    """int32 elements of the `work` tensor the fused decode needs for calls of up to `rows` live rows."""
+    return int(_lib.lib().lq_decode_work_bytes(int(rows), int(HV))) // 4
+
+
 def make_gdn_step(NS, HV, H, K, V, L, SS, R=4, SMS=148, NSTAGE=None, NCG=None, NNW=None, scale=None, MAXIT=256):
     """Gated DeltaNet decode step on the 8-bit state.  Returns
     step(Sq, Sk, Sv, Skv, Kbuf, Ubuf, Wbuf, Pbuf, hcnt, mixed, a, b, A_log, dt_bias, UQ, idx, o)."""
@@ -83,15 +95,15 @@ def make_decode(NS, HV, H, K, V, L, SS, R=4, ITERS=1, KDA=False, GLB=0.0, scale=
     if KDA:
         fn = _lib.lib().lq_kda_decode
 
-        def decode(Sq, Kbuf, Ubuf, Wbuf, Pbuf, Gbuf, hcnt, mixed, a, b, A_log, dt_bias, Q0, idx, o):
+        def decode(Sq, Kbuf, Ubuf, Wbuf, Pbuf, Gbuf, hcnt, mixed, a, b, A_log, dt_bias, Q0, idx, o, work=None):
             _launch(fn, "lq_kda_decode", Sq, d, p(Sq), p(Kbuf), p(Ubuf), p(Wbuf), p(Pbuf), p(Gbuf), p(hcnt), p(mixed), p(a), p(b),
-                    p(A_log), p(dt_bias), p(idx), p(o), int(mixed.shape[0]), sc, glb, p(Q0), iters)
+                    p(A_log), p(dt_bias), p(idx), p(o), int(mixed.shape[0]), sc, glb, p(Q0), iters, *_work(work))
     else:
         fn = _lib.lib().lq_gdn_decode
 
-        def decode(Sq, Kbuf, Ubuf, Wbuf, Pbuf, hcnt, mixed, a, b, A_log, dt_bias, Q0, idx, o):
+        def decode(Sq, Kbuf, Ubuf, Wbuf, Pbuf, hcnt, mixed, a, b, A_log, dt_bias, Q0, idx, o, work=None):
             _launch(fn, "lq_gdn_decode", Sq, d, p(Sq), p(Kbuf), p(Ubuf), p(Wbuf), p(Pbuf), p(hcnt), p(mixed), p(a), p(b),
-                    p(A_log), p(dt_bias), p(idx), p(o), int(mixed.shape[0]), sc, p(Q0), iters)
+                    p(A_log), p(dt_bias), p(idx), p(o), int(mixed.shape[0]), sc, p(Q0), iters, *_work(work))
 
     return decode
 
@@ -111,17 +123,18 @@ def make_decode_conv(NS, HV, H, K, V, L, SS, R=4, ITERS=1, KDA=False, GLB=0.0, s
     if KDA:
         fn = _lib.lib().lq_kda_decode_conv
 
-        def decode(Sq, Kbuf, Ubuf, Wbuf, Pbuf, Gbuf, hcnt, x, conv_state, conv_weight, conv_bias, a, b, A_log, dt_bias, Q0, idx, o):
+        def decode(Sq, Kbuf, Ubuf, Wbuf, Pbuf, Gbuf, hcnt, x, conv_state, conv_weight, conv_bias, a, b, A_log, dt_bias, Q0, idx, o,
+                   work=None):
             cv = _lib.conv1d(x, conv_state, conv_weight, conv_bias)
             _launch(fn, "lq_kda_decode_conv", Sq, d, p(Sq), p(Kbuf), p(Ubuf), p(Wbuf), p(Pbuf), p(Gbuf), p(hcnt), cv, p(a), p(b),
-                    p(A_log), p(dt_bias), p(idx), p(o), int(x.shape[0]), sc, glb, p(Q0), iters)
+                    p(A_log), p(dt_bias), p(idx), p(o), int(x.shape[0]), sc, glb, p(Q0), iters, *_work(work))
     else:
         fn = _lib.lib().lq_gdn_decode_conv
 
-        def decode(Sq, Kbuf, Ubuf, Wbuf, Pbuf, hcnt, x, conv_state, conv_weight, conv_bias, a, b, A_log, dt_bias, Q0, idx, o):
+        def decode(Sq, Kbuf, Ubuf, Wbuf, Pbuf, hcnt, x, conv_state, conv_weight, conv_bias, a, b, A_log, dt_bias, Q0, idx, o, work=None):
             cv = _lib.conv1d(x, conv_state, conv_weight, conv_bias)
             _launch(fn, "lq_gdn_decode_conv", Sq, d, p(Sq), p(Kbuf), p(Ubuf), p(Wbuf), p(Pbuf), p(hcnt), cv, p(a), p(b),
-                    p(A_log), p(dt_bias), p(idx), p(o), int(x.shape[0]), sc, p(Q0), iters)
+                    p(A_log), p(dt_bias), p(idx), p(o), int(x.shape[0]), sc, p(Q0), iters, *_work(work))
 
     return decode
 

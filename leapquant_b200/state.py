@@ -92,6 +92,9 @@ class LeapQuantState:
         self.kdecode_conv = KN.make_decode_conv(NS, HV, H, K, V, L, SS, R=R, ITERS=1, KDA=kda, GLB=float(gate_lower_bound),
                                                 scale=(128 ** -0.5 if kda else None))
         self.fused = True                                     # decode() = one fused launch; False = step then flush
+        # shared list of the heads whose window fills in a call (all zero between calls): lets a CTA without such a head take
+        # over a head of a CTA that has several.  No counterpart in the reference.
+        self.work = torch.zeros(KN.decode_work_ints(NS, HV), dtype=torch.int32, device=dev)
         self.kdeq = KN.make_dequant(NS, HV, K, V, L, SS, buf_dtype=KN.BF16, R=R, kda=kda)
         self.kquant = KN.make_quantize(NS, HV, K, V, L, SS, R=R, ITERS=3 if kda else 1, kda=kda)
         self._vkey = None
@@ -126,10 +129,10 @@ class LeapQuantState:
         if self.fused:
             if self.kda:
                 self.kdecode(v["q32"], self.Kbuf, self.Ubuf, self.Wbuf, self.Pbuf, self.Gbuf, self.hcnt, mixed, a, b, A_log,
-                             dt_bias, self.Q0, idx, out)
+                             dt_bias, self.Q0, idx, out, self.work)
             else:
                 self.kdecode(v["q32"], self.Kbuf, self.Ubuf, self.Wbuf, self.Pbuf, self.hcnt, mixed, a, b, A_log, dt_bias,
-                             self.Q0, idx, out)
+                             self.Q0, idx, out, self.work)
             return
         if self.kda:
             self.kstep(v["q32"], v["Sk"], v["Sv"], v["skv"], self.Kbuf, self.Ubuf, self.Wbuf, self.Pbuf, self.Gbuf,
@@ -155,7 +158,7 @@ class LeapQuantState:
         idx = idx if idx.dtype == torch.int32 else idx.to(torch.int32)
         v = self.views(ssm)
         bufs = (self.Kbuf, self.Ubuf, self.Wbuf, self.Pbuf) + ((self.Gbuf,) if self.kda else ()) + (self.hcnt,)
-        self.kdecode_conv(v["q32"], *bufs, x, conv_state, conv_weight, conv_bias, a, b, A_log, dt_bias, self.Q0, idx, out)
+        self.kdecode_conv(v["q32"], *bufs, x, conv_state, conv_weight, conv_bias, a, b, A_log, dt_bias, self.Q0, idx, out, self.work)
 
     def dequantize(self, ssm, idx):
         """Materialize the fp32 state of the slots idx in place (before the engine's own prefill kernel runs on them)."""

@@ -56,12 +56,14 @@ def test_argument_errors_are_codes_not_crashes():
     assert L.lq_flush(good, one, one, one, one, one, mis, one, one, one, 1, 1, 1, None) == -3       # KDA: Gbuf
     # fused decode: the step's checks plus the flush's Q0 / iters
     dec = (good, one, one, one, one, one, one, one, one, one, one, one, one, one, 1, 0.0)
-    assert L.lq_gdn_decode(*dec, None, 1, None) == -1                                                # NULL Q0
-    assert L.lq_gdn_decode(*dec, one, -1, None) == -4                                                # negative iters
-    assert L.lq_gdn_decode(good, mis, *dec[2:], one, 1, None) == -3                                  # misaligned state
-    assert L.lq_gdn_decode(*dec[:14], 0, 0.0, one, 1, None) == 0                                     # N == 0
+    assert L.lq_gdn_decode(*dec, None, 1, None, 0, None) == -1                                       # NULL Q0
+    assert L.lq_gdn_decode(*dec, one, -1, None, 0, None) == -4                                       # negative iters
+    assert L.lq_gdn_decode(good, mis, *dec[2:], one, 1, None, 0, None) == -3                         # misaligned state
+    assert L.lq_gdn_decode(*dec[:14], 0, 0.0, one, 1, None, 0, None) == 0                            # N == 0
+    assert L.lq_gdn_decode(*dec, one, 1, one, 16, None) == -4                                        # work list too small for the call
+    assert L.lq_decode_work_bytes(8, 4) == 4 * (16 + 32)
     assert L.lq_kda_decode(good, one, one, one, one, one, None, one, one, one, one, one, one, one, one, 1, 0.0, 0.0, one, 1,
-                           None) == -1                                                               # KDA needs Gbuf
+                           None, 0, None) == -1                                                      # KDA needs Gbuf
     assert L.lq_set_option(b"pdl", 1) == 0 and L.lq_set_option(b"no_such_option", 1) == -2
     assert L.lq_lowrank(one, one, one, one, 1, 64, 128, 4, 3, None) == -2
     assert L.lq_lowrank(one, one, one, one, 0, 128, 128, 4, 3, None) == 0

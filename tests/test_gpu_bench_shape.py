@@ -12,7 +12,7 @@ import torch
 
 from lq_testlib import CpuSide, GpuSide, assert_close, random_states
 from oracle import lq_oracle as O
-from test_gpu_parity import check_flush, compare_window, make_pair, step_inputs
+from test_gpu_parity import check_flush, compare_window, make_pair, step_inputs, work_list  # noqa: F401 (fixture)
 
 pytestmark = pytest.mark.gpu
 K = V = 128
@@ -117,10 +117,10 @@ def all_windows_one_short(kda, L, R, H, HV, seed):
 
 
 @pytest.mark.parametrize("kda,L,R,H,HV", CONFIGS)
-def test_decode_every_window_fills(kda, L, R, H, HV):
+def test_decode_every_window_fills(kda, L, R, H, HV, work_list):
     """(ii) One decode call in which all 1 280 windows fill: every CTA of the fused kernel flushes eight or nine heads, each
-    team four or five, one after the other in the same shared memory.  Bit-identical to the step kernel followed by the
-    flush kernel."""
+    team four or five, one after the other in the same shared memory (or, sharing one list, its first head and then pairs
+    and single heads by ticket).  Bit-identical to the step kernel followed by the flush kernel."""
     cpu, idx, (mixed, a, b_, A_log, dtb) = all_windows_one_short(kda, L, R, H, HV, 21)
     gpu_f, gpu_s = GpuSide(cpu), GpuSide(cpu)
     gpu_s.st.fused = False
@@ -153,3 +153,50 @@ def test_flush_many_due_heads_per_cta(kda, L, R, H, HV):
     #  one, so the distance from a rounding boundary within which a code may differ is 0.05 code units here)
     check_flush(cpu, gpu, idx, list(range(1, N_ROWS + 1)), f"flush of 1280 heads kda={kda}", code_tol=5e-2)
     assert int(gpu.st.hcnt.abs().max()) == 0
+
+
+@pytest.mark.parametrize("kda,L,R,H,HV", CONFIGS)
+def test_shared_work_list_staggered_fill(kda, L, R, H, HV):
+    """(iv) A serving batch: 200 sequences whose windows fill at different steps (sequence n starts with n mod L entries), so
+    every step fills the windows of a few rows and their heads land on a few CTAs.  The fused decode that shares one list of
+    due heads among the CTAs, the fused decode in which every CTA flushes its own heads, and step-then-flush give the same
+    bits at every step; the list is left all zero by every launch."""
+    from leapquant_b200 import _lib
+    from leapquant_b200.state import LeapQuantState
+    N, NS = 200, 201                               # 6 400 programs: above the size from which the list is used by default
+    g = torch.Generator(device="cuda").manual_seed(31)
+    base = torch.randn(NS, HV, V, K, device="cuda", generator=g) * 0.5
+    idx = torch.arange(1, N + 1, dtype=torch.int32, device="cuda")
+    arms = []
+    for name in ("shared", "own", "split"):
+        ssm = base.clone()
+        st = LeapQuantState(ssm, H, kda=kda, gate_lower_bound=-5.0 if kda else 0.0, L=L, R=R)
+        st.quantize(ssm, idx)
+        if name == "own":
+            st.work = None
+        if name == "split":
+            st.fused = False
+        arms.append((ssm, st, torch.zeros(N, HV, V, dtype=torch.bfloat16, device="cuda")))
+    T = 2 * L + 3
+    mixed, a, b_, A_log, dtb = step_inputs(N, H, HV, T, 32, kda, gate_shift=3.0)
+    A_log, dtb = A_log.cuda(), dtb.cuda()
+    bits = lambda x: x.view(torch.int32) if x.dtype == torch.float32 else x.view(torch.int16) if x.element_size() == 2 else x
+    start = torch.arange(N) % L
+    for t in range(T):
+        # the first L - 1 steps build the stagger: row n joins at step L - 1 - (n mod L)
+        rows = torch.nonzero(start >= L - 1 - t).flatten() if t < L - 1 else torch.arange(N)
+        m, aa, bb = mixed[t][rows].cuda(), a[t][rows].cuda(), b_[t][rows].cuda()
+        for ssm, st, o in arms:
+            st.decode(ssm, m, aa, bb, A_log, dtb, idx[rows.cuda()].contiguous(), o[: rows.numel()])
+        n = rows.numel()
+        for ssm, st, o in arms[1:]:
+            assert torch.equal(bits(arms[0][2][:n]), bits(o[:n])), t
+            assert torch.equal(arms[0][1].hcnt, st.hcnt), t
+        assert int(arms[0][1].work.abs().max()) == 0, t
+    assert int(arms[0][1].hcnt.max()) < L
+    for ssm, st, o in arms[1:]:
+        for name in ("Kbuf", "Ubuf", "Wbuf", "Pbuf") + (("Gbuf",) if kda else ()):
+            assert torch.equal(bits(getattr(arms[0][1], name)), bits(getattr(st, name))), name
+        assert torch.equal(bits(arms[0][0]), bits(ssm))
+    torch.cuda.synchronize()
+    assert _lib.device_status() == 0

@@ -32,6 +32,16 @@ def step_inputs(N, H, HV, steps, seed, kda, gate_shift=0.0):
     return mixed, a, b, A_log, dtb
 
 
+@pytest.fixture(params=[False, True], ids=["own_heads", "shared_list"])
+def work_list(request):
+    """Runs a fused-decode test twice: every CTA flushing the heads it filled, and the CTAs sharing one list of them
+    (forced on for calls of any size; by default small calls skip it)."""
+    from leapquant_b200 import _lib
+    _lib.set_option("work_list_min_programs", 0 if request.param else 1 << 30)
+    yield request.param
+    _lib.set_option("work_list_min_programs", -1)
+
+
 @pytest.fixture(params=[0, 1, 2], ids=["pipelined", "direct", "warp"])
 def step_impl(request):
     """Runs a test once per driver of the step kernel (persistent bulk-copy pipeline / one CTA per program)."""
@@ -523,7 +533,7 @@ def test_sharded_equals_unsharded():
 
 @pytest.mark.parametrize("kda,L,R,H,HV", [(False, 16, 4, 2, 4), (False, 64, 4, 1, 2), (True, 16, 4, 2, 2), (True, 32, 8, 2, 2),
                                           (False, 64, 8, 1, 2), (True, 64, 8, 2, 2)])     # the last one has room for one flush team only
-def test_fused_decode_equals_step_then_flush(kda, L, R, H, HV):
+def test_fused_decode_equals_step_then_flush(kda, L, R, H, HV, work_list):
     """One fused launch per token gives bit-identical outputs, window buffers and packed state to the step kernel followed
     by the flush kernel, over more than two windows and with rows whose windows fill at different steps."""
     NS, N, T = 12, 10, 2 * L + 7
@@ -546,6 +556,7 @@ def test_fused_decode_equals_step_then_flush(kda, L, R, H, HV):
     for name in ("Kbuf", "Ubuf", "Wbuf", "Pbuf") + (("Gbuf",) if kda else ()):
         assert torch.equal(bits(getattr(gpu_f.st, name)), bits(getattr(gpu_s.st, name))), name
     assert torch.equal(bits(gpu_f.ssm), bits(gpu_s.ssm))
+    assert int(gpu_f.st.work.abs().max()) == 0, "the shared list is left all zero"
     from leapquant_b200 import _lib
     torch.cuda.synchronize()
     assert _lib.device_status() == 0
