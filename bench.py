@@ -493,7 +493,9 @@ def conv_and_fp32_baseline(wl, B, device, peak, graph_steps=16):
     mixed = torch.zeros(B, C, dtype=torch.bfloat16, device=device)
 
     def fused(t):
+        ly.st.conv_one_launch = True
         ly.st.decode_conv(ly.ssm, x[t % L], conv_state, w, bias, ly.a[t % L], ly.b[t % L], ly.A_log, ly.dtb, ly.idx, ly.out)
+        ly.st.conv_one_launch = False
 
     def unfused(t):
         conv(x[t % L], conv_state, w, bias, ly.idx, mixed)
@@ -512,8 +514,9 @@ def conv_and_fp32_baseline(wl, B, device, peak, graph_steps=16):
 
     out = {"batch": B}
     tf, tu = time_graph(fused, L), time_graph(unfused, L)
-    out["conv_fused_decode"] = {"ms_per_step_fused": 1e3 * tf, "ms_per_step_conv_then_decode": 1e3 * tu, "launches_fused": 1,
-                                "launches_unfused": 2, "saved_us_per_step": 1e6 * (tu - tf)}
+    out["conv_and_decode"] = {"ms_per_step_one_launch": 1e3 * tf, "ms_per_step_two_launches": 1e3 * tu,
+                              "default": "two launches (conv1d update kernel, then decode)",
+                              "note": "replayed from a CUDA graph; the single launch pays where launches are issued one by one"}
     try:
         from vllm.model_executor.layers.fla.ops.fused_recurrent import fused_recurrent_gated_delta_rule_packed_decode as eng_decode
         from vllm.model_executor.layers.mamba.ops.causal_conv1d import causal_conv1d_update as eng_conv
@@ -530,7 +533,7 @@ def conv_and_fp32_baseline(wl, B, device, peak, graph_steps=16):
         out["fp32_state_engine_kernels"] = {"ms_per_step": 1e3 * te, "head_steps_per_s": B * HV / te,
                                             "gbs": B * HV * 2 * 4 * V * K / te / 1e9, "frac_of_measured_hbm": B * HV * 2 * 4 * V * K / te / 1e9 / peak,
                                             "kernels": "vllm causal_conv1d_update + fused_recurrent_gated_delta_rule_packed_decode (Triton), fp32 state",
-                                            "speedup_of_fused_int8_decode": te / tf}
+                                            "speedup_of_int8_conv_and_decode": te / min(tf, tu)}
     except Exception as e:                                       # the engine is not importable here: no fp32-state figure
         out["fp32_state_engine_kernels"] = {"unavailable": str(e).splitlines()[0][:160] if str(e) else type(e).__name__}
     return out

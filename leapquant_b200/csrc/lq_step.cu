@@ -96,63 +96,54 @@ struct StepParams {
 // activation is x / (1 + exp(-x)) in fp32, rounded to bf16 at the end.
 // ------------------------------------------------------------------------------------------------------------------
 constexpr int CONV_W = 4;
+// The raw words of NC consecutive channels (two bf16 per word), as loaded: nothing is unpacked before conv_eval(), and the
+// loads of the contiguous layout are volatile asm, so that they are issued where the caller puts them -- a whole program
+// ahead of their use -- and not next to it.
 template <int NC>
 struct ConvRegs {
-    uint16_t x[NC], st[CONV_W - 1][NC], w[NC][CONV_W], b[NC];
+    uint32_t x[NC / 2], st[CONV_W - 1][NC / 2], w[NC * CONV_W / 2], b[NC / 2];
 };
-template <int NC>
-__device__ __forceinline__ void ld_bf16_vec(const uint16_t* p, uint16_t (&out)[NC]) {
-    static_assert(NC == 2 || NC == 4, "two or four channels per thread");
-    if constexpr (NC == 4) {
-        const uint2 v = *reinterpret_cast<const uint2*>(p);
-        out[0] = uint16_t(v.x); out[1] = uint16_t(v.x >> 16); out[2] = uint16_t(v.y); out[3] = uint16_t(v.y >> 16);
-    } else {
-        const uint32_t v = *reinterpret_cast<const uint32_t*>(p);
-        out[0] = uint16_t(v); out[1] = uint16_t(v >> 16);
-    }
+__device__ __forceinline__ uint32_t ld_early_u32(const void* p) {
+    uint32_t v;
+    asm volatile("ld.global.u32 %0, [%1];" : "=r"(v) : "l"(p));
+    return v;
 }
-template <int NC>
-__device__ __forceinline__ void st_bf16_vec(uint16_t* p, const uint16_t (&in)[NC]) {
-    if constexpr (NC == 4) *reinterpret_cast<uint2*>(p) = make_uint2(uint32_t(in[0]) | (uint32_t(in[1]) << 16), uint32_t(in[2]) | (uint32_t(in[3]) << 16));
-    else *reinterpret_cast<uint32_t*>(p) = uint32_t(in[0]) | (uint32_t(in[1]) << 16);
+__device__ __forceinline__ void ld_early_words(const void* p, uint32_t (&out)[1]) { out[0] = ld_early_u32(p); }
+__device__ __forceinline__ void ld_early_words(const void* p, uint32_t (&out)[2]) {
+    asm volatile("ld.global.v2.u32 {%0, %1}, [%2];" : "=r"(out[0]), "=r"(out[1]) : "l"(p));
 }
-// loads only (no arithmetic on what was loaded), so that a caller can issue them well ahead of conv_eval()
+__device__ __forceinline__ void ld_early_words(const void* p, uint32_t (&out)[4]) {
+    asm volatile("ld.global.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(out[0]), "=r"(out[1]), "=r"(out[2]), "=r"(out[3]) : "l"(p));
+}
+__device__ __forceinline__ void ld_early_words(const void* p, uint32_t (&out)[8]) {
+    asm volatile("ld.global.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(out[0]), "=r"(out[1]), "=r"(out[2]), "=r"(out[3]) : "l"(p));
+    asm volatile("ld.global.v4.u32 {%0, %1, %2, %3}, [%4+16];" : "=r"(out[4]), "=r"(out[5]), "=r"(out[6]), "=r"(out[7]) : "l"(p));
+}
+__device__ __forceinline__ void st_words(void* p, const uint32_t (&in)[1]) { *reinterpret_cast<uint32_t*>(p) = in[0]; }
+__device__ __forceinline__ void st_words(void* p, const uint32_t (&in)[2]) { *reinterpret_cast<uint2*>(p) = make_uint2(in[0], in[1]); }
+__device__ __forceinline__ uint16_t half_of(const uint32_t* w, int e) { return uint16_t(w[e >> 1] >> (16 * (e & 1))); }
 template <int NC>
 __device__ __forceinline__ ConvRegs<NC> conv_load(const StepParams& P, int n, int slot, int c0) {
+    static_assert(NC == 2 || NC == 4, "two or four channels per thread");
     ConvRegs<NC> r;
-    ld_bf16_vec<NC>(P.cx + int64_t(n) * P.cx_stride + c0, r.x);
-    uint16_t* sb = P.cstate + int64_t(slot) * P.cs_slot;
+    ld_early_words(P.cx + int64_t(n) * P.cx_stride + c0, r.x);
+    const uint16_t* sb = P.cstate + int64_t(slot) * P.cs_slot;
     if (P.cs_dim == 1) {                                     // (slot, tap, channel): the channels of a tap are contiguous
 #pragma unroll
-        for (int t = 0; t < CONV_W - 1; ++t) ld_bf16_vec<NC>(sb + t * P.cs_tap + c0, r.st[t]);
-    } else {
+        for (int t = 0; t < CONV_W - 1; ++t) ld_early_words(sb + t * P.cs_tap + c0, r.st[t]);
+    } else {                                                 // (slot, channel, tap): one element at a time
 #pragma unroll
         for (int t = 0; t < CONV_W - 1; ++t)
 #pragma unroll
-            for (int e = 0; e < NC; ++e) r.st[t][e] = sb[int64_t(c0 + e) * P.cs_dim + t * P.cs_tap];
+            for (int e = 0; e < NC; e += 2)
+                r.st[t][e >> 1] = uint32_t(sb[int64_t(c0 + e) * P.cs_dim + t * P.cs_tap]) |
+                                  (uint32_t(sb[int64_t(c0 + e + 1) * P.cs_dim + t * P.cs_tap]) << 16);
     }
-    {
-        uint16_t wf[NC * CONV_W];
-        if constexpr (NC == 4) {
-            const uint4 a = *reinterpret_cast<const uint4*>(P.cw + int64_t(c0) * CONV_W), b = *reinterpret_cast<const uint4*>(P.cw + int64_t(c0) * CONV_W + 8);
-            const uint32_t ww[8] = {a.x, a.y, a.z, a.w, b.x, b.y, b.z, b.w};
-#pragma unroll
-            for (int i = 0; i < 8; ++i) { wf[2 * i] = uint16_t(ww[i]); wf[2 * i + 1] = uint16_t(ww[i] >> 16); }
-        } else {
-            const uint4 a = *reinterpret_cast<const uint4*>(P.cw + int64_t(c0) * CONV_W);
-            const uint32_t ww[4] = {a.x, a.y, a.z, a.w};
-#pragma unroll
-            for (int i = 0; i < 4; ++i) { wf[2 * i] = uint16_t(ww[i]); wf[2 * i + 1] = uint16_t(ww[i] >> 16); }
-        }
-#pragma unroll
-        for (int e = 0; e < NC; ++e)
-#pragma unroll
-            for (int t = 0; t < CONV_W; ++t) r.w[e][t] = wf[e * CONV_W + t];
-    }
-    if (P.cb) ld_bf16_vec<NC>(P.cb + c0, r.b);
+    ld_early_words(P.cw + int64_t(c0) * CONV_W, r.w);
+    if (P.cb) ld_early_words(P.cb + c0, r.b);
     else {
 #pragma unroll
-        for (int e = 0; e < NC; ++e) r.b[e] = 0;
+        for (int e = 0; e < NC / 2; ++e) r.b[e] = 0u;
     }
     return r;
 }
@@ -160,32 +151,38 @@ template <int NC>
 __device__ __forceinline__ void conv_eval(const ConvRegs<NC>& r, uint16_t (&out)[NC]) {
 #pragma unroll
     for (int e = 0; e < NC; ++e) {
-        float acc = bf16_to_f(r.b[e]);
+        float acc = bf16_to_f(half_of(r.b, e));
 #pragma unroll
         for (int t = 0; t < CONV_W; ++t) {
-            const float xv = bf16_to_f(t < CONV_W - 1 ? r.st[t][e] : r.x[e]);
-            acc += round_bf16(xv * bf16_to_f(r.w[e][t]));
+            const float xv = bf16_to_f(t < CONV_W - 1 ? half_of(r.st[t], e) : half_of(r.x, e));
+            acc += round_bf16(xv * bf16_to_f(half_of(r.w, e * CONV_W + t)));
         }
-        out[e] = f_to_bf16(acc / (1.0f + expf(-acc)));
+        out[e] = f_to_bf16(__fdividef(acc, 1.0f + __expf(-acc)));       // (the result is rounded to bf16: eight bits)
     }
 }
-// new state (state[1], state[2], x) of the NC channels
+// new state of the NC channels, tap by tap: nw[t] = the words of tap t
 template <int NC>
-__device__ __forceinline__ void conv_store_state(const StepParams& P, int slot, int c0, const ConvRegs<NC>& r) {
+__device__ __forceinline__ void conv_store_words(const StepParams& P, int slot, int c0, const uint32_t (&nw)[CONV_W - 1][NC / 2]) {
     uint16_t* sb = P.cstate + int64_t(slot) * P.cs_slot;
     if (P.cs_dim == 1) {
-        st_bf16_vec<NC>(sb + c0, r.st[1]);
-        st_bf16_vec<NC>(sb + P.cs_tap + c0, r.st[2]);
-        st_bf16_vec<NC>(sb + 2 * P.cs_tap + c0, r.x);
+#pragma unroll
+        for (int t = 0; t < CONV_W - 1; ++t) st_words(sb + t * P.cs_tap + c0, nw[t]);
     } else {
 #pragma unroll
         for (int e = 0; e < NC; ++e) {
             uint16_t* cp = sb + int64_t(c0 + e) * P.cs_dim;
-            cp[0] = r.st[1][e];
-            cp[P.cs_tap] = r.st[2][e];
-            cp[2 * P.cs_tap] = r.x[e];
+#pragma unroll
+            for (int t = 0; t < CONV_W - 1; ++t) cp[t * P.cs_tap] = half_of(nw[t], e);
         }
     }
+}
+// new state (state[1], state[2], x)
+template <int NC>
+__device__ __forceinline__ void conv_store_state(const StepParams& P, int slot, int c0, const ConvRegs<NC>& r) {
+    uint32_t nw[CONV_W - 1][NC / 2];
+#pragma unroll
+    for (int e = 0; e < NC / 2; ++e) { nw[0][e] = r.st[1][e]; nw[1][e] = r.st[2][e]; nw[2][e] = r.x[e]; }
+    conv_store_words<NC>(P, slot, c0, nw);
 }
 
 // per-program scalars, produced once and read by the whole group
@@ -1039,19 +1036,22 @@ __global__ void __launch_bounds__(UT + NG * GT, 1) step_pipelined_kernel(StepPar
             // taps are fetched one unit ahead; the conv runs once, the new state is written back at once (every reader of the
             // old one is this warp), and the unit's GQA programs all use the result
             const int nun = nit / gqa;
+            // The conv inputs of a unit are loaded one unit of this warp ahead and its slot two units ahead, so that no
+            // load waits for another: index -> slot one trip, slot -> conv state and projections the next.
             ConvRegs<4> cq = {}, ck = {};
-            int slot_nx = 0;
-            auto unit_fetch = [&](int uu) {
+            int slot_nx = 0, raw_nx2 = 0;
+            auto slot_fetch = [&](int uu) { raw_nx2 = uu < nun ? P.idx[(bid + uu * grid) / H] : 0; };      // (a load, nothing else)
+            auto unit_fetch = [&](int uu, int raw) {
                 slot_nx = 0;
-                if (uu >= nun) return;
+                if (uu >= nun || raw <= 0 || raw >= P.d.NS) return;
                 const int u = bid + uu * grid, n2 = u / H, hk2 = u - n2 * H;
-                const int sl = P.idx[n2];
-                if (sl <= 0 || sl >= P.d.NS) return;
-                slot_nx = sl;
-                cq = conv_load<4>(P, n2, sl, hk2 * KD + 4 * lane);
-                ck = conv_load<4>(P, n2, sl, (H + hk2) * KD + 4 * lane);
+                slot_nx = raw;
+                cq = conv_load<4>(P, n2, raw, hk2 * KD + 4 * lane);
+                ck = conv_load<4>(P, n2, raw, (H + hk2) * KD + 4 * lane);
             };
-            unit_fetch(warp - 2);
+            slot_fetch(warp - 2);
+            unit_fetch(warp - 2, raw_nx2);
+            slot_fetch(warp - 2 + NPW);
             for (int uu = warp - 2; uu < nun; uu += NPW) {
                 uint2 q_cur = make_uint2(0u, 0u), k_cur = make_uint2(0u, 0u);
                 if (slot_nx > 0) {
@@ -1061,12 +1061,27 @@ __global__ void __launch_bounds__(UT + NG * GT, 1) step_pipelined_kernel(StepPar
                     conv_eval<4>(ck, ko);
                     q_cur = make_uint2(uint32_t(qo[0]) | (uint32_t(qo[1]) << 16), uint32_t(qo[2]) | (uint32_t(qo[3]) << 16));
                     k_cur = make_uint2(uint32_t(ko[0]) | (uint32_t(ko[1]) << 16), uint32_t(ko[2]) | (uint32_t(ko[3]) << 16));
-                    conv_store_state<4>(P, slot_nx, hk1 * KD + 4 * lane, cq);
-                    conv_store_state<4>(P, slot_nx, (H + hk1) * KD + 4 * lane, ck);
                 }
-                unit_fetch(uu + NPW);
-                for (int g2 = 0; g2 < gqa; ++g2)
-                    if (!run_prologue(uu * gqa + g2, q_cur, k_cur)) return;
+                // the new conv state of q and k: three words per tap, kept until the unit's programs have been signalled
+                // (the signal is a release, and would wait for these stores to drain)
+                const int slot_cur = slot_nx;
+                uint32_t nq[3][2], nk[3][2];
+#pragma unroll
+                for (int e = 0; e < 2; ++e) {
+                    nq[0][e] = cq.st[1][e]; nq[1][e] = cq.st[2][e]; nq[2][e] = cq.x[e];
+                    nk[0][e] = ck.st[1][e]; nk[1][e] = ck.st[2][e]; nk[2][e] = ck.x[e];
+                }
+                const int raw = raw_nx2;
+                slot_fetch(uu + 2 * NPW);
+                unit_fetch(uu + NPW, raw);
+                bool ok = true;
+                for (int g2 = 0; g2 < gqa && ok; ++g2) ok = run_prologue(uu * gqa + g2, q_cur, k_cur);
+                if (slot_cur > 0) {
+                    const int u = bid + uu * grid, n1 = u / H, hk1 = u - n1 * H;
+                    conv_store_words<4>(P, slot_cur, hk1 * KD + 4 * lane, nq);
+                    conv_store_words<4>(P, slot_cur, (H + hk1) * KD + 4 * lane, nk);
+                }
+                if (!ok) return;
             }
         } else {
             const int MIXq = 2 * H * KD + HV * VD;

@@ -92,6 +92,13 @@ class LeapQuantState:
         self.kdecode_conv = KN.make_decode_conv(NS, HV, H, K, V, L, SS, R=R, ITERS=1, KDA=kda, GLB=float(gate_lower_bound),
                                                 scale=(128 ** -0.5 if kda else None))
         self.fused = True                                     # decode() = one fused launch; False = step then flush
+        # decode_conv(): False = the conv1d update kernel, then decode (two launches); True = the update inside the decode
+        # launch.  Replayed from a CUDA graph the two launches are the faster form at every batch size measured (the conv
+        # arithmetic of the single launch sits on the warps that feed its pipeline); the single launch saves a launch where
+        # launches are issued one by one from the host.
+        self.conv_one_launch = False
+        self._kconv = None
+        self._mixed = None
         # shared list of the heads whose window fills in a call (all zero between calls): lets a CTA without such a head take
         # over a head of a CTA that has several.  No counterpart in the reference.
         self.work = torch.zeros(KN.decode_work_ints(NS, HV), dtype=torch.int32, device=dev)
@@ -146,10 +153,22 @@ class LeapQuantState:
                     v["sq16"], v["uq"], self.Q0, idx)
 
     def decode_conv(self, ssm, x, conv_state, conv_weight, conv_bias, a, b, A_log, dt_bias, idx, out):
-        """decode() with the causal conv1d update of the step fused in: x bf16 [N, >= 2HK + HV*V] holds the RAW q | k | v
-        projections, conv_state is the engine's conv cache viewed (slot, channel, width - 1) (any strides; advanced in place),
-        conv_weight bf16 [channels, 4], conv_bias bf16 [channels] or None.  One launch; the activated q | k | v row is never
-        written to memory.  No counterpart in the reference, whose plugin calls vLLM's causal_conv1d_update first."""
+        """The causal conv1d update of the step and decode(): x bf16 [N, >= 2HK + HV*V] holds the RAW q | k | v projections,
+        conv_state is the engine's conv cache viewed (slot, channel, width - 1) (any strides; advanced in place), conv_weight
+        bf16 [channels, 4], conv_bias bf16 [channels] or None.  Two launches of this library (update kernel, decode), or, with
+        conv_one_launch, one, in which the activated q | k | v row is never written to memory; the results are the same bit for
+        bit.  No counterpart in the reference, whose plugin calls vLLM's causal_conv1d_update first."""
+        if not self.conv_one_launch:
+            C = 2 * self.H * self.K + self.HV * self.V
+            N = x.shape[0]
+            if self._kconv is None:
+                self._kconv = KN.make_conv1d_update(self.NS, C)
+            if self._mixed is None or self._mixed.shape[0] < N:
+                self._mixed = torch.empty(max(N, 64), C, dtype=torch.bfloat16, device=x.device)
+            mixed = self._mixed[:N]
+            i32 = idx if idx.dtype == torch.int32 else idx.to(torch.int32)
+            self._kconv(x, conv_state, conv_weight, conv_bias, i32, mixed)
+            return self.decode(ssm, mixed, a, b, A_log, dt_bias, i32, out)
         A_log = A_log if A_log.dtype == torch.float32 else self._p32(A_log)
         dt_bias = dt_bias if dt_bias.dtype == torch.float32 else self._p32(dt_bias)
         KA = self.K if self.kda else 1

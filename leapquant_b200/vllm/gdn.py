@@ -25,7 +25,7 @@ class GdnAdapter:
         self.engine_core = getattr(self.cls, self.core_name)
         self.engine_decode_kernel = getattr(module, "fused_sigmoid_gating_delta_rule_update", None)
         self.mixed_layer = None                               # the layer whose MIXED step is inside the engine's forward right now
-        self.fuse_conv = True                                 # pure decode: conv1d update fused into the decode launch
+        self.fuse_conv = True                                 # pure decode: conv1d update and decode through state.decode_conv()
 
     # ---- pieces ----
     def state_of(self, layer):

@@ -21,7 +21,7 @@ class KdaAdapter:
         self.conv_update = causal_conv1d_update
         self.eager_break = eager_break
         self.engine_forward = getattr(self.cls._forward, "__wrapped__", self.cls._forward)
-        self.fuse_conv = True                                 # pure decode: conv1d update fused into the decode launch
+        self.fuse_conv = True                                 # pure decode: conv1d update and decode through state.decode_conv()
 
     def state_of(self, layer):
         return get_state(layer, layer.kv_cache[1], H=layer.local_num_heads, kda=True,

@@ -56,15 +56,16 @@ def test_conv1d_update_against_oracle(dim_first):
                                             (True, 16, 4, 2, 2, 11), (True, 32, 8, 32, 32, 40)])
 @pytest.mark.parametrize("dim_first", [False, True], ids=["slot_tap_channel", "slot_channel_tap"])
 def test_fused_conv_decode_equals_conv_then_decode(kda, L, R, H, HV, N, dim_first):
-    """decode_conv (one launch) == conv1d update kernel, then decode: outputs, window buffers, packed state and conv state,
-    bit for bit, over more than a window, with null rows and rows that sit out some steps."""
+    """decode_conv as one launch == decode_conv as it runs by default (two launches) == the conv1d update kernel called by
+    hand, then decode: outputs, window buffers, packed state and conv state, bit for bit, over more than a window, with null
+    rows and rows that sit out some steps."""
     from leapquant_b200.kernels import make_conv1d_update
     NS, T = N + 2, L + 5
     C = 2 * H * K + HV * V
     cpu, gpu_f = make_pair(NS, HV, H, L, R, kda=kda, glb=(-5.0 if kda else 0.0), seed=8)
-    gpu_s = GpuSide(cpu)
+    gpu_s, gpu_d = GpuSide(cpu), GpuSide(cpu)
     store, w, b = conv_operands(NS, C, 5, dim_first)
-    st_f, st_s = store.cuda(), store.clone().cuda()
+    st_f, st_s, st_d = store.cuda(), store.clone().cuda(), store.clone().cuda()
     wg, bg = w.cuda(), b.cuda()
     g = torch.Generator().manual_seed(6)
     idx = torch.randperm(NS - 1, generator=g)[:N].int() + 1
@@ -73,8 +74,10 @@ def test_fused_conv_decode_equals_conv_then_decode(kda, L, R, H, HV, N, dim_firs
     idx = idx.cuda()
     _, a, b_, A_log, dtb = step_inputs(N, H, HV, T, 9, kda, gate_shift=2.0)
     conv = make_conv1d_update(NS, C)
+    gpu_f.st.conv_one_launch = True
+    assert not gpu_d.st.conv_one_launch
     o_f = torch.zeros(N, HV, V, dtype=torch.bfloat16, device="cuda")
-    o_s = torch.zeros_like(o_f)
+    o_s, o_d = torch.zeros_like(o_f), torch.zeros_like(o_f)
     mixed = torch.zeros(N, C, dtype=torch.bfloat16, device="cuda")
     bits = lambda t: t.view(torch.int32) if t.dtype == torch.float32 else t.view(torch.int16) if t.element_size() == 2 else t
     for t in range(T):
@@ -82,11 +85,13 @@ def test_fused_conv_decode_equals_conv_then_decode(kda, L, R, H, HV, N, dim_firs
         n = N if t % 3 else N // 2                                         # half of the rows skip every third step
         at, bt = a[t][:n].cuda(), b_[t][:n].cuda()
         gpu_f.st.decode_conv(gpu_f.ssm, x[:n], view_sct(st_f, dim_first), wg, bg, at, bt, A_log.cuda(), dtb.cuda(), idx[:n], o_f[:n])
+        gpu_d.st.decode_conv(gpu_d.ssm, x[:n], view_sct(st_d, dim_first), wg, bg, at, bt, A_log.cuda(), dtb.cuda(), idx[:n], o_d[:n])
         conv(x[:n], view_sct(st_s, dim_first), wg, bg, idx[:n], mixed[:n])
         gpu_s.st.decode(gpu_s.ssm, mixed[:n], at, bt, A_log.cuda(), dtb.cuda(), idx[:n], o_s[:n])
-        assert torch.equal(bits(o_f[:n]), bits(o_s[:n])), t
+        assert torch.equal(bits(o_f[:n]), bits(o_s[:n])) and torch.equal(bits(o_d[:n]), bits(o_s[:n])), t
         assert torch.equal(gpu_f.st.hcnt, gpu_s.st.hcnt), t
-    assert torch.equal(bits(st_f), bits(st_s)), "conv state"
+    assert torch.equal(bits(st_f), bits(st_s)) and torch.equal(bits(st_d), bits(st_s)), "conv state"
+    assert torch.equal(bits(gpu_d.ssm), bits(gpu_s.ssm))
     for name in ("Kbuf", "Ubuf", "Wbuf", "Pbuf") + (("Gbuf",) if kda else ()):
         assert torch.equal(bits(getattr(gpu_f.st, name)), bits(getattr(gpu_s.st, name))), name
     assert torch.equal(bits(gpu_f.ssm), bits(gpu_s.ssm))
