@@ -38,6 +38,7 @@ extern "C" {
 #define LQ_ERR_ALIGN (-3)        /* pointer or stride alignment */
 #define LQ_ERR_RANGE (-4)        /* a size is negative or inconsistent (e.g. HV % H != 0, N < 0) */
 #define LQ_ERR_LAUNCH (-5)       /* the CUDA runtime refused the launch; see lq_last_cuda_error() */
+#define LQ_ERR_LIMIT (-6)        /* more heads than the fixed scratch of lq_gdn_decode_noalloc holds */
 
 /* Shape of one layer's state, shared by all entry points. */
 typedef struct lq_dims {
@@ -124,6 +125,27 @@ int lq_kda_decode(const lq_dims* d, void* ssm, void* Kbuf, void* Ubuf, float* Wb
                   const float* Q0, int32_t iters, void* work, int64_t work_bytes, void* stream);
 /* Bytes of the `work` scratch for calls of up to `rows` live rows with HV value heads. */
 int64_t lq_decode_work_bytes(int32_t rows, int32_t HV);
+
+/* lq_gdn_decode for callers that cannot allocate device memory.  (No counterpart in the reference: its kernels get every
+ * buffer from torch.)  Some hosts of this library must not call cudaMalloc once they are running: a serving engine that
+ * has measured free memory and given all of it to its cache pool, so that a later allocation may fail or push it over;
+ * a plugin that lives under an allocator it does not own; a latency-bound thread for which the device-wide
+ * synchronisation inside cudaMalloc / cudaFree is a stall.  lq_gdn_decode leaves the shared list of due heads (`work`) to
+ * the caller, which is one more buffer to allocate; this entry point keeps that list inside the library instead, in a
+ * device array of fixed size that is part of the library image: every GPU that loads the library holds
+ * 4 * (16 + LQ_NOALLOC_MAX_HEADS) bytes (about 256 KiB) for it until the process exits, used or not.
+ *   - Arguments and results are those of lq_gdn_decode without `work` / `work_bytes`; inputs and outputs are still the
+ *     caller's.  It calls no cudaMalloc, cudaFree or other allocating routine.
+ *   - Limit: min(N, NS) * HV <= LQ_NOALLOC_MAX_HEADS, else LQ_ERR_LIMIT and nothing is launched.
+ *   - The first call on a device asks the runtime for the array's address on that device (cudaGetSymbolAddress, with the
+ *     caller's current device): make that first call outside any stream capture.
+ *   - Every call on a device shares the one array.  The call zeroes the part it uses (a memset on `stream` ahead of the
+ *     kernel), so a call that was cut short leaves nothing behind; two calls that overlap on the GPU (different streams,
+ *     or different threads without ordering) race on it and must not be made. */
+#define LQ_NOALLOC_MAX_HEADS 65536
+int lq_gdn_decode_noalloc(const lq_dims* d, void* ssm, void* Kbuf, void* Ubuf, float* Wbuf, float* Pbuf, int32_t* hcnt,
+                          const void* mixed, const void* a, const void* b, const float* A_log, const float* dt_bias,
+                          const int32_t* idx, void* o, int32_t N, float scale, const float* Q0, int32_t iters, void* stream);
 
 /* Operands of the causal conv1d update that precedes every decode step in the serving engine (the reference plugin calls
  * vLLM's causal_conv1d_update right before LeapQuantState.decode: reference leapquant/vllm/gdn.py:31-33, glm.py:72-73).

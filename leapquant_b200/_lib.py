@@ -14,7 +14,7 @@ LIB_PATH = os.environ.get("LEAPQUANT_B200_LIB") or os.path.join(_HERE, "libleapq
 
 EXPORTS = ("lq_version", "lq_strerror", "lq_last_cuda_error", "lq_device_status", "lq_set_option", "lq_gdn_step", "lq_kda_step",
            "lq_flush", "lq_gdn_decode", "lq_kda_decode", "lq_gdn_decode_conv", "lq_kda_decode_conv", "lq_causal_conv1d_update",
-           "lq_decode_work_bytes",
+           "lq_decode_work_bytes", "lq_gdn_decode_noalloc",
            "lq_quantize", "lq_dequant", "lq_lowrank")
 
 _P = ctypes.c_void_p
@@ -62,6 +62,7 @@ def lib():
         I64 = ctypes.c_int64
         L.lq_gdn_decode.argtypes = [D, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _I, _F, _P, _I, _P, I64, _P]
         L.lq_kda_decode.argtypes = [D, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _I, _F, _F, _P, _I, _P, I64, _P]
+        L.lq_gdn_decode_noalloc.argtypes = [D, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _I, _F, _P, _I, _P]
         L.lq_decode_work_bytes.argtypes = [_I, _I]
         L.lq_decode_work_bytes.restype = I64
         C = ctypes.POINTER(LqConv1d)
@@ -72,7 +73,8 @@ def lib():
         L.lq_dequant.argtypes = [D, _P, _P, _P, _P, _P, _P, _P, _P, _I, _I, _P]
         L.lq_lowrank.argtypes = [_P, _P, _P, _P, _I, _I, _I, _I, _I, _P]
         for name in ("lq_device_status", "lq_gdn_step", "lq_kda_step", "lq_flush", "lq_quantize", "lq_dequant", "lq_lowrank",
-                     "lq_gdn_decode", "lq_kda_decode", "lq_gdn_decode_conv", "lq_kda_decode_conv", "lq_causal_conv1d_update"):
+                     "lq_gdn_decode", "lq_kda_decode", "lq_gdn_decode_conv", "lq_kda_decode_conv", "lq_causal_conv1d_update",
+                     "lq_gdn_decode_noalloc"):
             getattr(L, name).restype = _I
         _lib = L
     return _lib

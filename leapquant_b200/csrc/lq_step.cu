@@ -1513,6 +1513,50 @@ extern "C" int lq_kda_decode_conv(const lq_dims* d, void* ssm, void* Kbuf, void*
                          iters, work, work_bytes, stream, conv);
 }
 
+// ------------------------------------------------------------------------------------------------------------------
+// GDN decode for callers that must not allocate.  The shared list of due heads that lq_gdn_decode takes as `work` lives
+// here in a file-scope device array of fixed size, which every GPU that loads the library holds until the process exits.
+// In host code the array's name only stands for the symbol: its device address comes from cudaGetSymbolAddress(), asked
+// once per device with that device current, and is what the kernel is given.
+// ------------------------------------------------------------------------------------------------------------------
+static __device__ __align__(256) int g_noalloc_work[lq::WL_ITEMS + LQ_NOALLOC_MAX_HEADS];
+static std::atomic<int*> g_noalloc_ptr[64];                     // per device: the array's address on that device (null = not asked yet)
+
+extern "C" int lq_gdn_decode_noalloc(const lq_dims* d, void* ssm, void* Kbuf, void* Ubuf, float* Wbuf, float* Pbuf, int32_t* hcnt,
+                                     const void* mixed, const void* a, const void* b, const float* A_log, const float* dt_bias,
+                                     const int32_t* idx, void* o, int32_t N, float scale, const float* Q0, int32_t iters,
+                                     void* stream) {
+    if (!d) return LQ_ERR_NULL;
+    if (N < 0) return LQ_ERR_RANGE;
+    const int64_t rows = N < d->NS ? N : d->NS;
+    if (d->HV <= 0 || rows * int64_t(d->HV) > LQ_NOALLOC_MAX_HEADS) return LQ_ERR_LIMIT;        // more heads than the array has entries
+    int dev = 0;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess || dev < 0 || dev >= 64) {
+        lq::set_last_cuda_error(e == cudaSuccess ? cudaErrorInvalidDevice : e);
+        return LQ_ERR_LAUNCH;
+    }
+    int* ptr = g_noalloc_ptr[dev].load(std::memory_order_acquire);
+    if (!ptr) {                                                  // first call on this device (two threads may both ask: same answer)
+        e = cudaGetSymbolAddress(reinterpret_cast<void**>(&ptr), g_noalloc_work);
+        if (e != cudaSuccess || !ptr) {
+            lq::set_last_cuda_error(e == cudaSuccess ? cudaErrorInvalidSymbol : e);
+            return LQ_ERR_LAUNCH;
+        }
+        g_noalloc_ptr[dev].store(ptr, std::memory_order_release);
+    }
+    if (N == 0) return LQ_OK;
+    // the array keeps what the last call left (all zero after a call that ran to its end): the part this call uses starts at zero
+    const size_t bytes = size_t(lq_decode_work_bytes(int32_t(rows), d->HV));
+    e = cudaMemsetAsync(ptr, 0, bytes, static_cast<cudaStream_t>(stream));
+    if (e != cudaSuccess) {
+        lq::set_last_cuda_error(e);
+        return LQ_ERR_LAUNCH;
+    }
+    return decode_common(d, ssm, Kbuf, Ubuf, Wbuf, Pbuf, nullptr, hcnt, mixed, a, b, A_log, dt_bias, idx, o, N, scale, 0.f, false, Q0,
+                         iters, ptr, int64_t(sizeof(int)) * (lq::WL_ITEMS + LQ_NOALLOC_MAX_HEADS), stream);
+}
+
 extern "C" int lq_causal_conv1d_update(const lq_conv1d* conv, const int32_t* idx, int32_t N, int32_t channels, int32_t NS, void* out,
                                        int64_t out_stride, void* stream) {
     if (!conv || !out || (N > 0 && !idx)) return LQ_ERR_NULL;
