@@ -826,7 +826,8 @@ def main():
     ap.add_argument("--step-impl", type=int, default=-1, help="debug: step kernel driver (see lq_set_option)")
     ap.add_argument("--profile-case", action="store_true",
                     help="for a profiler: quantize, stagger the fill levels (L - 1 decode launches), 4 more decode launches, "
-                         "the prefill round trip once, exit; prints nothing")
+                         "the prefill round trip once, L launches of the step kernel alone, one flush of every head, exit; "
+                         "prints nothing")
     args = ap.parse_args()
     if args.workload == "config4":
         return run_config4(args)
@@ -841,6 +842,9 @@ def main():
         for t in range(4):
             layer.decode_resident(t)
         layer.to_lockstep()
+        for t in range(layer.period):                  # one window of the step kernel alone, then the flush kernel with every head due
+            layer.step_only(t)
+        layer.flush_only()
         torch.cuda.synchronize()
     elif args.impl == "reference":
         run_reference(args, wl)

@@ -172,7 +172,10 @@ typedef struct lq_conv1d {
  * the pair causal_conv1d_update -> LeapQuantState.decode of the reference plugin (leapquant/vllm/gdn.py:25-36,
  * leapquant/vllm/glm.py:71-75) by ONE launch that never writes the intermediate q | k | v row to memory.  Results equal
  * lq_causal_conv1d_update followed by lq_*_decode bit for bit.  Only the fused single-launch form exists: a configuration
- * whose flush work area does not fit beside the step pipeline returns LQ_ERR_UNSUPPORTED. */
+ * whose flush work area does not fit beside the step pipeline returns LQ_ERR_UNSUPPORTED.  When to use it: the conv
+ * arithmetic of the single launch runs on the warps that feed the step pipeline, and replayed from a CUDA graph the two
+ * calls lq_causal_conv1d_update + lq_*_decode are the faster form (86 against 96 microseconds per step at 256 rows of 32
+ * heads on a B200); the single launch saves a launch where launches are issued one by one from the host. */
 int lq_gdn_decode_conv(const lq_dims* d, void* ssm, void* Kbuf, void* Ubuf, float* Wbuf, float* Pbuf, int32_t* hcnt,
                        const lq_conv1d* conv, const void* a, const void* b, const float* A_log, const float* dt_bias,
                        const int32_t* idx, void* o, int32_t N, float scale, const float* Q0, int32_t iters, void* work,

@@ -5,9 +5,13 @@ TileLang CUDA kernels.  The reference has no CPU or PyTorch implementation of th
 GDN quantize/dequant (all are CUDA kernels generated at run time), and it ships no tests, golden vectors or
 fixtures, so:
 
-  * parity of the decode-step and flush restatements is UNPINNED by reference outputs;
+  * parity of the decode-step and flush restatements is UNPINNED by reference outputs (their kernels were not run: the
+    generated code of the step kernel did not build here, and both spin on flags without a bound);
   * the packed layout (`state_views`) and the KDA torch round trip (`kda_rebuild`, `kda_checkpoint`) ARE pinned
-    against the reference's own Python code (fixtures under tests/golden/, produced by tests/golden/make_golden.py).
+    against the reference's own Python code (fixtures under tests/golden/, produced by tests/golden/make_golden.py);
+  * the GDN quantize, the dequantize and the low-rank factorisation ARE pinned against outputs of the reference's own
+    TileLang kernels, run once on a B200 (fixtures under tests/golden/ref_kernels/, produced by
+    tests/golden/make_ref_kernel_golden.py; tests/test_ref_kernel_golden.py).
 
 Only tests/, __graft_entry__.smoke() and bench.py's cpu_baseline / `--impl reference` leg may import this module.
 The product (leapquant_b200) never imports it and has no CPU fallback.
