@@ -42,10 +42,11 @@ WORKLOADS = {
     "gdn": dict(name="gdn_decode_H16_HV32_d128_L64_R4", H=16, HV=32, L=64, R=4, B=256, kda=False),
     "kda": dict(name="kda_decode_H32_HV32_d128_L32_R8", H=32, HV=32, L=32, R=8, B=128, kda=True),
 }
-# DRAM bytes (read + write) per algorithmic byte of the decode kernel, from the ncu captures summarised under profiles/
-# (decode_fused_gdn_B128_ncu.md: 150.1 MB + 4.7 MB for 4 096 programs at h = 32 against 153 MB algorithmic;
-# decode_fused_kda_B128_ncu.md).  `roofline.traffic` scales the live algorithmic bytes per launch by this ratio.
-NCU_TRAFFIC_RATIO = {"gdn": 1.01, "kda": None}
+# DRAM bytes (read + write) per algorithmic byte of the fused decode kernel on the staggered batch, from the ncu captures
+# summarised under profiles/ (decode_gdn_B256_ncu.md: 302.1 MB + 10.0 MB against 313.5 MB algorithmic;
+# decode_kda_B128_ncu.md: 145.5 MB + 6.5 MB against 159.6 MB).  `roofline.traffic` scales the live algorithmic bytes per
+# launch by this ratio.
+NCU_TRAFFIC_RATIO = {"gdn": 1.00, "kda": 0.95}
 MIN_TIMED_S = 0.5
 
 
