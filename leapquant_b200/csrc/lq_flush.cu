@@ -413,7 +413,6 @@ __device__ __forceinline__ void flush_init(const FlushSmem& s, const float* Q0, 
             s.QoT[c * 8 + r] = 0;
         }
     }
-    for (int i = tid; i < 128 * R; i += nthreads) s.Q0h[(i % R) * HS + i / R] = f_to_f16(Q0[i]);
     if (tid == 0) {
         mbar_init(s.mbar, 1);
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -458,6 +457,7 @@ __device__ __forceinline__ bool flush_head(const FlushSmem& s, const FlushArgs& 
         constexpr int NTC = 64 * 16 / NT;                   // window-row chunks (16 bytes) per thread (Lp <= 64)
         float wv = 0.f, pcv = 1.f, skv = 0.f, svv = 0.f, pcf[NF], wrow[NTC];
         uint16_t fu[NF], fq[NF];
+        float q0v[NF];                                      // the fixed start Q0 of the iteration: fetched with the head's other operands
         uint4 tk[NTC], tu[NTC], tg[KDA ? NTC : 1];
         const uint4* gbc = reinterpret_cast<const uint4*>(Gbuf + (KDA ? sh * L * KD : 0));
         if (tid < L) wv = __ldcg(Wbuf + sh * L + tid);
@@ -473,6 +473,7 @@ __device__ __forceinline__ bool flush_head(const FlushSmem& s, const FlushArgs& 
             fu[u] = in ? uq[r * (KD + VD) + c] : uint16_t(0);
             fq[u] = in ? uq[r * (KD + VD) + KD + c] : uint16_t(0);
             pcf[u] = (KDA && in) ? __ldcg(Pbuf + sh * KD + c) : 0.f;
+            q0v[u] = in ? __ldg(A.Q0 + i) : 0.f;
         }
 #pragma unroll
         for (int u = 0; u < NTC; ++u) {
@@ -501,6 +502,7 @@ __device__ __forceinline__ bool flush_head(const FlushSmem& s, const FlushArgs& 
                 s.Qoh[r * HS + c] = fq[u];
                 s.UoT[c * 8 + r] = uu;
                 s.QoT[c * 8 + r] = fq[u];
+                s.Q0h[(i % R) * HS + i / R] = f_to_f16(q0v[u]);      // Q0 is [128][R] row-major; kept transposed as f16
             }
         }
         // window rows -> operand tiles (rows L .. Lp-1 are zero).  GDN: tile 0 / 1 = head / remainder of w_j u_j, tile 2 = keys.
