@@ -1184,11 +1184,14 @@ __global__ void __launch_bounds__(UT + NG * GT, 1) step_pipelined_kernel(StepPar
         unsigned long long seen = 0;                             // (thread 0) the counter word as last read
         int ticket = -1, held = 1;                               // (thread 0) a ticket drawn but not resolved yet, and how many it stands for
         if (wl != nullptr) {
-            nh = ndl > 0 ? 1 : 0;
-            if (ndl > 1) __threadfence();                        // the step's stores of the appended heads come before their entries
+            // a CTA that filled four or more windows is in a call in which every CTA did (windows in phase): it keeps them all
+            // and flushes them in pairs, as without the list; two or three are the uneven case the list is for
+            const bool keep_all = ndl >= 4;
+            nh = keep_all ? ndl : (ndl > 0 ? 1 : 0);
+            if (ndl > 1 && !keep_all) __threadfence();           // the step's stores of the appended heads come before their entries
             __syncthreads();
             if (tid == 0) {
-                if (ndl == 1) {
+                if (ndl == 1 || keep_all) {
                     atomicAdd(wlw, WL_DONE1);                     // nothing to append, nothing to learn yet
                 } else if (ndl == 0) {
                     seen = atomicAdd(wlw, WL_DONE1 + WL_TAKEN1) + WL_DONE1;
