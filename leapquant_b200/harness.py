@@ -103,6 +103,23 @@ class HybridTP:
         if state == "fp32":
             self.fp32_kernels = self._find_fp32_kernels()
         self.lq = {}
+        self.kv_attention = self._find_kv_attention()
+
+    def _find_kv_attention(self):
+        """Decode attention over the KV cache from a library when one runs on this device (flash_attn's kv-cache kernel:
+        appends the new key / value and attends in one call); None = torch's scaled_dot_product_attention with a mask.
+        Attention is not part of the path this package accelerates: both arms of the comparison use the same one."""
+        try:
+            from flash_attn import flash_attn_with_kvcache
+            kc = torch.zeros(1, 16, self.KVH, self.AD, dtype=torch.bfloat16, device=self.dev)
+            q = torch.zeros(1, 1, self.QH, self.AD, dtype=torch.bfloat16, device=self.dev)
+            kn = torch.zeros(1, 1, self.KVH, self.AD, dtype=torch.bfloat16, device=self.dev)
+            flash_attn_with_kvcache(q, kc, kc.clone(), k=kn, v=kn, cache_seqlens=torch.zeros(1, dtype=torch.int32, device=self.dev),
+                                    causal=True)
+            torch.cuda.synchronize()
+            return flash_attn_with_kvcache
+        except Exception:
+            return None
 
     # ---- pieces ----
     def all_reduce(self, x):
@@ -251,11 +268,15 @@ class HybridTP:
                 kv = F.linear(h, p["kv"]).reshape(B, 2, self.KVH, self.AD)
                 q = self.rope(qg[:, 0], pos[:, None])                                     # [B, QH, AD]
                 k = self.rope(kv[:, 0], pos[:, None])
-                ar = torch.arange(B, device=self.dev)
-                p["kc"][ar, :, pos] = k
-                p["vc"][ar, :, pos] = kv[:, 1]
-                mask = (torch.arange(self.max_len, device=self.dev)[None] <= pos[:, None])[:, None, None, :]
-                o = F.scaled_dot_product_attention(q[:, :, None], p["kc"], p["vc"], attn_mask=mask, enable_gqa=True)[:, :, 0]
+                if self.kv_attention is not None:
+                    o = self.kv_attention(q[:, None], p["kc"].transpose(1, 2), p["vc"].transpose(1, 2), k=k[:, None], v=kv[:, 1][:, None],
+                                          cache_seqlens=pos.to(torch.int32), causal=True)[:, 0]
+                else:
+                    ar = torch.arange(B, device=self.dev)
+                    p["kc"][ar, :, pos] = k
+                    p["vc"][ar, :, pos] = kv[:, 1]
+                    mask = (torch.arange(self.max_len, device=self.dev)[None] <= pos[:, None])[:, None, None, :]
+                    o = F.scaled_dot_product_attention(q[:, :, None], p["kc"], p["vc"], attn_mask=mask, enable_gqa=True)[:, :, 0]
                 o = o * torch.sigmoid(qg[:, 1].float()).to(o.dtype)
                 y = F.linear(o.reshape(B, -1), p["out"])
             x = x + self.all_reduce(y)
@@ -328,6 +349,7 @@ def run_generation(cfg, state, batch, prompt_len, new_tokens, seed=0, use_graph=
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
     t_prefill, t_decode = float(t[0]), float(t[1])
     return {"state": state, "fp32_kernels": model.fp32_kernels[0] if model.fp32_kernels else None, "decode_mode": mode,
+            "attention": "flash_attn_with_kvcache" if model.kv_attention is not None else "torch sdpa, masked",
             "prefill_s": t_prefill, "decode_s": t_decode, "decode_steps_timed": steps, "ms_per_decode_step": 1e3 * t_decode / max(steps, 1),
             "decode_tokens_per_s": batch * steps / t_decode if steps else None, "first_tokens": first[:8].tolist(),
             "last_tokens": s_tok[:8].tolist(),
