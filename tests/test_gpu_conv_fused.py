@@ -6,7 +6,7 @@ import torch
 
 from lq_testlib import CpuSide, GpuSide, random_states
 from oracle import lq_oracle as O
-from test_gpu_parity import make_pair, step_inputs
+from test_gpu_parity import make_pair, step_inputs, work_list  # noqa: F401 (work_list is a fixture)
 
 pytestmark = pytest.mark.gpu
 K = V = 128
@@ -55,7 +55,7 @@ def test_conv1d_update_against_oracle(dim_first):
 @pytest.mark.parametrize("kda,L,R,H,HV,N", [(False, 16, 4, 2, 4, 11), (False, 64, 4, 16, 32, 40), (False, 16, 4, 1, 4, 9),
                                             (True, 16, 4, 2, 2, 11), (True, 32, 8, 32, 32, 40)])
 @pytest.mark.parametrize("dim_first", [False, True], ids=["slot_tap_channel", "slot_channel_tap"])
-def test_fused_conv_decode_equals_conv_then_decode(kda, L, R, H, HV, N, dim_first):
+def test_fused_conv_decode_equals_conv_then_decode(kda, L, R, H, HV, N, dim_first, work_list):
     """decode_conv as one launch == decode_conv as it runs by default (two launches) == the conv1d update kernel called by
     hand, then decode: outputs, window buffers, packed state and conv state, bit for bit, over more than a window, with null
     rows and rows that sit out some steps."""
