@@ -854,10 +854,6 @@ __global__ void __launch_bounds__(UT + NG * GT, 1) step_pipelined_kernel(StepPar
         }
     };
 
-    // The fused kernel takes its tensor memory (two teams x 128 columns) now, where the allocation overlaps the set-up, and not
-    // after the step, where the first flush would wait for it; every path to the end of the kernel gives it back.
-    __shared__ uint32_t tm_slot;
-    if (FUSE && warp == 0) tmem_alloc(&tm_slot, 2 * TMEM_COLS);
     if (tid == 0) {
         *dl_n = 0;
         *abortf = 0;
@@ -870,9 +866,7 @@ __global__ void __launch_bounds__(UT + NG * GT, 1) step_pipelined_kernel(StepPar
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
         fence_async_smem();
     }
-    if (FUSE) tc_fence_before_sync();
     __syncthreads();
-    if (FUSE) tc_fence_after_sync();
     pdl_trigger();
     pdl_wait();                                                  // everything below reads what earlier kernels of the stream wrote
 
@@ -1162,6 +1156,7 @@ __global__ void __launch_bounds__(UT + NG * GT, 1) step_pipelined_kernel(StepPar
     // parallel over the tile.  A serving batch whose sequences fill their windows at different steps gives most CTAs exactly
     // one head per step, and the latency of that flush is what the step pays.
     if constexpr (FUSE) {
+        __shared__ uint32_t tm_slot;
         __shared__ int s_pop[4];
         static_assert(UT + NG * GT == 512, "the fused flush is written for two teams of 256 threads");
         const int nteams = ft.teams;                             // work areas that fit in the ring: 1 or 2
@@ -1173,10 +1168,7 @@ __global__ void __launch_bounds__(UT + NG * GT, 1) step_pipelined_kernel(StepPar
         const int ndl = *abortf ? 0 : *dl_n;
         int* const wl = ft.work;
         unsigned long long* const wlw = reinterpret_cast<unsigned long long*>(wl);
-        if (wl == nullptr && ndl == 0) {
-            if (warp == 0) tmem_dealloc(tm_slot, 2 * TMEM_COLS);
-            return;
-        }
+        if (wl == nullptr && ndl == 0) return;                   // (before any tensor memory is held)
         // Rounds of heads: without the list one round of this CTA's own heads; with it, the CTA's first head and then one
         // round per ticket.  `heads` points into shared memory (the CTA's own list or the ticket's entries).
         const int* heads = dl;
@@ -1251,9 +1243,13 @@ __global__ void __launch_bounds__(UT + NG * GT, 1) step_pipelined_kernel(StepPar
             }
             more = nh > 0 && wl != nullptr;
             if (nh > 0) {
-            if (!inited) {                                       // first head of this CTA: the per-team constants (shared memory only:
-                const FlushSmem fi = flush_carve<R>(stage_smem + (team < nteams ? team : 0) * ft.team_bytes, L, KDA);      // the head's first
-                if (team < nteams) flush_init<R>(fi, ft.Q0, ttid, 256);                                                     // barrier publishes them)
+            if (!inited) {                                       // first head of this CTA: tensor memory and the per-team constants
+                if (warp == 0) tmem_alloc(&tm_slot, 2 * TMEM_COLS);
+                const FlushSmem fi = flush_carve<R>(stage_smem + (team < nteams ? team : 0) * ft.team_bytes, L, KDA);
+                if (team < nteams) flush_init<R>(fi, ft.Q0, ttid, 256);
+                tc_fence_before_sync();
+                __syncthreads();
+                tc_fence_after_sync();
                 inited = true;
             }
             const uint32_t tm = tm_slot;
@@ -1282,7 +1278,7 @@ __global__ void __launch_bounds__(UT + NG * GT, 1) step_pipelined_kernel(StepPar
         }
         tc_fence_before_sync();
         __syncthreads();
-        if (warp == 0) tmem_dealloc(tm_slot, 2 * TMEM_COLS);
+        if (inited && warp == 0) tmem_dealloc(tm_slot, 2 * TMEM_COLS);
         if (wl != nullptr) {
             // the last CTA to leave zeroes the list: every other CTA is past its last access
             if (tid == 0) s_pop[2] = (atomicAdd(wl + WL_EXITED, 1) == grid - 1) ? wl_count(ld_volatile_u64(wlw)) : -1;
