@@ -63,6 +63,13 @@ __device__ __forceinline__ uint16_t f_to_f16(float x) {
 __device__ __forceinline__ float round_f16(float x) { return __half2float(__float2half_rn(x)); }
 __device__ __forceinline__ float round_bf16(float x) { return __bfloat162float(__float2bfloat16_rn(x)); }
 
+// D += A B for one m16n8k16 tile, bf16 operands, f32 accumulator (warp-wide)
+__device__ __forceinline__ void mma_bf16_16816(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0,
+                                               uint32_t b1) {
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+                 : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+                 : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
 // Four int8 codes packed in `w` -> four floats, exactly.  The word is flipped to offset binary, each byte is dropped
 // into the low mantissa byte of 2^23 and 2^23 + 128 is subtracted.
 __device__ __forceinline__ void s8x4_to_f4(uint32_t w, float& f0, float& f1, float& f2, float& f3) {

@@ -171,22 +171,31 @@ quantize_kernel(lq_dims d, char* __restrict__ ssm, float* __restrict__ Wbuf, flo
 // dequantize in place
 // ------------------------------------------------------------------------------------------------------------------
 // S[v][c] = (q8 / 127 Sk[c] Sv[v] + sum_r Q_r[v] U_r[c]) p pc[c] + sum_{j<h} (w_j u_j[v]) (k_j[c] D_j[c])   (leapquant/kernels.py:2105-2117;
-// KDA: leapquant/state.py:118-128).  The per-element work is kept to one conversion, one multiply and 1 + R + h fused
-// multiply-adds by folding the constants into the vectors first: skq[c] = Sk[c] / 127 (* pc[c]), svp[v] = Sv[v] p,
-// Qp_r[v] = Q_r[v] p, Uc_r[c] = U_r[c] (* pc[c]).  The values differ from the reference's evaluation order in the last place of fp32.
+// KDA: leapquant/state.py:118-128).  The constants are folded into the vectors first: skq[c] = Sk[c] / 127 (* pc[c]),
+// svp[v] = Sv[v] p, Qp_r[v] = Q_r[v] p, Uc_r[c] = U_r[c] (* pc[c]).  The rank-R term runs on the tensor cores: Qp and Uc are
+// split into a bf16 head and a bf16 remainder and the three products head x head, remainder x head, head x remainder are laid
+// side by side along K of one `mma.sync.m16n8k16` (R = 4: K = 12 of 16; R = 8: two instructions), which keeps 16 bits of each
+// factor -- 1e-5 of the term -- and replaces 4 R multiply-adds per element by an eighth of an instruction.  What is left per
+// element is one conversion, one multiply, one fused multiply-add and h multiply-adds for the live window entries.  The
+// values differ from the reference's evaluation order by a few units in the last place of fp32.
+// Warp w owns rows 16 w .. 16 w + 15; lane (gid, tig) owns rows 16 w + gid, + 8 and, in each group of 16 columns, the four
+// columns 4 tig .. 4 tig + 3: the two n-tiles of a group are mapped onto the columns so that every lane ends up with four
+// contiguous ones (n index g of the first tile is column 4 (g / 2) + g % 2, of the second the same + 2).
 // The window rows stay bf16 in shared memory (KDA keys: decayed, fp32), so that three CTAs fit on an SM.
 template <int R>
 __global__ void __launch_bounds__(NT_LA, 3)
 dequant_kernel(lq_dims d, char* __restrict__ ssm, const uint16_t* __restrict__ Kbuf, const uint16_t* __restrict__ Ubuf,
                float* __restrict__ Wbuf, float* __restrict__ Pbuf, const uint16_t* __restrict__ Gbuf,
                int32_t* __restrict__ hcnt, const int32_t* __restrict__ idx, int kda) {
+    constexpr int KT = (3 * R + 15) / 16 * 16;            // K of the rank-R product: three pieces of R, padded to the instruction
+    constexpr int KS = KT + 8;                            // row stride of the operands in bf16 elements (16 bytes of padding)
     extern __shared__ __align__(16) float smem[];
     uint32_t* cw = reinterpret_cast<uint32_t*>(smem);     // [128][32] code words
     float* skq = smem + 4096;                             // [128] Sk / 127 (KDA: times pc)
     float* svp = skq + 128;                               // [128] Sv p
-    float* Uc = svp + 128;                                // [R][128] U_r (KDA: times pc)
-    float* Qp = Uc + R * 128;                             // [R][128] Q_r p
-    float* ws = Qp + R * 128;                             // [64] window weights
+    uint16_t* Aop = reinterpret_cast<uint16_t*>(svp + 128);   // [128 rows v][KS]: Qp head | Qp remainder | Qp head | 0
+    uint16_t* Bop = Aop + 128 * KS;                       // [128 cols c][KS]: Uc head | Uc head | Uc remainder | 0
+    float* ws = reinterpret_cast<float*>(Bop + 128 * KS); // [64] window weights
     float* Kf = ws + 64;                                  // KDA: [L][128] decayed keys (fp32); GDN: [L][64] bf16 pairs
     const int tid = threadIdx.x;
     const int n = blockIdx.x / d.HV, hv = blockIdx.x % d.HV;
@@ -208,9 +217,14 @@ dequant_kernel(lq_dims d, char* __restrict__ ssm, const uint16_t* __restrict__ K
         const uint16_t* uq = reinterpret_cast<const uint16_t*>(base + CK_UQ);
 #pragma unroll
         for (int r = 0; r < R; ++r) {
-            Uc[r * 128 + tid] = f16_to_f(uq[r * (KD + VD) + tid]) * pc;
-            Qp[r * 128 + tid] = f16_to_f(uq[r * (KD + VD) + KD + tid]) * p;
+            const float u = f16_to_f(uq[r * (KD + VD) + tid]) * pc, q = f16_to_f(uq[r * (KD + VD) + KD + tid]) * p;
+            const uint16_t uh = f_to_bf16(u), qh = f_to_bf16(q);
+            const uint16_t ul = f_to_bf16(u - bf16_to_f(uh)), ql = f_to_bf16(q - bf16_to_f(qh));
+            Aop[tid * KS + r] = qh; Aop[tid * KS + R + r] = ql; Aop[tid * KS + 2 * R + r] = qh;
+            Bop[tid * KS + r] = uh; Bop[tid * KS + R + r] = uh; Bop[tid * KS + 2 * R + r] = ul;
         }
+#pragma unroll
+        for (int r = 3 * R; r < KT; ++r) { Aop[tid * KS + r] = 0; Bop[tid * KS + r] = 0; }
     }
     if (tid < d.L) ws[tid] = tid < h ? Wbuf[sh * d.L + tid] : 0.f;
     {
@@ -239,65 +253,69 @@ dequant_kernel(lq_dims d, char* __restrict__ ssm, const uint16_t* __restrict__ K
     }
     if (kda) __syncthreads();
 
-    // thread (ty, tx) owns rows v0 .. v0 + 7 and the eight columns 4 tx .. + 3, 64 + 4 tx .. + 3
-    const int ty = tid >> 4, tx = tid & 15, v0 = ty * 8;
-    float acc[8][8];
-    {
-        float uu[R][8], skl[8];
+    const int warp = tid >> 5, lane = tid & 31, gid = lane >> 2, tig = lane & 3;
+    const int r0 = 16 * warp + gid, r1 = r0 + 8;
+    // rank-R term: A fragments of this warp's 16 rows once per K step, B fragments per n-tile
+    uint32_t af[KT / 16][4];
 #pragma unroll
-        for (int k = 0; k < 4; ++k) {
-            skl[k] = skq[4 * tx + k];
-            skl[4 + k] = skq[64 + 4 * tx + k];
+    for (int ks = 0; ks < KT / 16; ++ks) {
+        af[ks][0] = *reinterpret_cast<const uint32_t*>(Aop + r0 * KS + 16 * ks + 2 * tig);
+        af[ks][1] = *reinterpret_cast<const uint32_t*>(Aop + r1 * KS + 16 * ks + 2 * tig);
+        af[ks][2] = *reinterpret_cast<const uint32_t*>(Aop + r0 * KS + 16 * ks + 8 + 2 * tig);
+        af[ks][3] = *reinterpret_cast<const uint32_t*>(Aop + r1 * KS + 16 * ks + 8 + 2 * tig);
+    }
+    const int cn = 4 * (gid >> 1) + (gid & 1);              // column (within a group of 16) that n index gid of the first n-tile stands for
+    const float sv0 = svp[r0], sv1 = svp[r1];
+    float* out = reinterpret_cast<float*>(base);            // (everything of the slot that is read was copied to shared memory above)
+    // one group of 16 columns at a time, start to finish: eight accumulators per thread instead of sixty-four
+#pragma unroll 2
+    for (int q = 0; q < 8; ++q) {
+        float c0[4] = {0.f, 0.f, 0.f, 0.f}, c1[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
-            for (int r = 0; r < R; ++r) {
-                uu[r][k] = Uc[r * 128 + 4 * tx + k];
-                uu[r][4 + k] = Uc[r * 128 + 64 + 4 * tx + k];
+        for (int ks = 0; ks < KT / 16; ++ks) {
+            const uint16_t* b0p = Bop + (16 * q + cn) * KS + 16 * ks + 2 * tig;
+            const uint16_t* b1p = b0p + 2 * KS;
+            mma_bf16_16816(c0, af[ks][0], af[ks][1], af[ks][2], af[ks][3], *reinterpret_cast<const uint32_t*>(b0p),
+                           *reinterpret_cast<const uint32_t*>(b0p + 8));
+            mma_bf16_16816(c1, af[ks][0], af[ks][1], af[ks][2], af[ks][3], *reinterpret_cast<const uint32_t*>(b1p),
+                           *reinterpret_cast<const uint32_t*>(b1p + 8));
+        }
+        float a0[4] = {c0[0], c0[1], c1[0], c1[1]}, a1[4] = {c0[2], c0[3], c1[2], c1[3]};      // rows r0, r1; columns 16 q + 4 tig + k
+        // codes: one word = this lane's four columns of a row
+        {
+            const float4 sk4 = *reinterpret_cast<const float4*>(skq + 16 * q + 4 * tig);
+            float f[4], g[4];
+            s8x4_to_f4(cw[r0 * 32 + 4 * q + tig], f[0], f[1], f[2], f[3]);
+            s8x4_to_f4(cw[r1 * 32 + 4 * q + tig], g[0], g[1], g[2], g[3]);
+            const float skl[4] = {sk4.x, sk4.y, sk4.z, sk4.w};
+#pragma unroll
+            for (int k = 0; k < 4; ++k) {
+                a0[k] = fmaf(f[k] * skl[k], sv0, a0[k]);
+                a1[k] = fmaf(g[k] * skl[k], sv1, a1[k]);
             }
         }
+        // live window entries
+        for (int j = 0; j < h; ++j) {
+            const float wj = ws[j];
+            const uint16_t* urow = reinterpret_cast<const uint16_t*>(Ub2 + j * 64);
+            const float u0 = bf16_to_f(urow[r0]) * wj, u1 = bf16_to_f(urow[r1]) * wj;
+            float kk[4];
+            if (kda) {
+                const float4 ka = *reinterpret_cast<const float4*>(Kf + j * 128 + 16 * q + 4 * tig);
+                kk[0] = ka.x; kk[1] = ka.y; kk[2] = ka.z; kk[3] = ka.w;
+            } else {
+                const uint2 ka = *reinterpret_cast<const uint2*>(Kb2 + j * 64 + 8 * q + 2 * tig);
+                const float2 k01 = bf16x2_to_f2(ka.x), k23 = bf16x2_to_f2(ka.y);
+                kk[0] = k01.x; kk[1] = k01.y; kk[2] = k23.x; kk[3] = k23.y;
+            }
 #pragma unroll
-        for (int i = 0; i < 8; ++i) {
-            float f[8];
-            s8x4_to_f4(cw[(v0 + i) * 32 + tx], f[0], f[1], f[2], f[3]);
-            s8x4_to_f4(cw[(v0 + i) * 32 + 16 + tx], f[4], f[5], f[6], f[7]);
-            const float svv = svp[v0 + i];
-            float qv[R];
-#pragma unroll
-            for (int r = 0; r < R; ++r) qv[r] = Qp[r * 128 + v0 + i];
-#pragma unroll
-            for (int k = 0; k < 8; ++k) {
-                float a2 = (f[k] * skl[k]) * svv;
-#pragma unroll
-                for (int r = 0; r < R; ++r) a2 = fmaf(qv[r], uu[r][k], a2);
-                acc[i][k] = a2;
+            for (int k = 0; k < 4; ++k) {
+                a0[k] = fmaf(u0, kk[k], a0[k]);
+                a1[k] = fmaf(u1, kk[k], a1[k]);
             }
         }
-    }
-    // live window entries
-    for (int j = 0; j < h; ++j) {
-        const float wj = ws[j];
-        const uint4 uw = *reinterpret_cast<const uint4*>(Ub2 + j * 64 + ty * 4);       // values v0 .. v0 + 7
-        const float2 u01 = bf16x2_to_f2(uw.x), u23 = bf16x2_to_f2(uw.y), u45 = bf16x2_to_f2(uw.z), u67 = bf16x2_to_f2(uw.w);
-        const float uu[8] = {u01.x * wj, u01.y * wj, u23.x * wj, u23.y * wj, u45.x * wj, u45.y * wj, u67.x * wj, u67.y * wj};
-        float kk[8];
-        if (kda) {
-            const float4 ka = *reinterpret_cast<const float4*>(Kf + j * 128 + 4 * tx);
-            const float4 kb4 = *reinterpret_cast<const float4*>(Kf + j * 128 + 64 + 4 * tx);
-            kk[0] = ka.x; kk[1] = ka.y; kk[2] = ka.z; kk[3] = ka.w; kk[4] = kb4.x; kk[5] = kb4.y; kk[6] = kb4.z; kk[7] = kb4.w;
-        } else {
-            const uint2 ka = *reinterpret_cast<const uint2*>(Kb2 + j * 64 + 2 * tx), kb2 = *reinterpret_cast<const uint2*>(Kb2 + j * 64 + 32 + 2 * tx);
-            const float2 k01 = bf16x2_to_f2(ka.x), k23 = bf16x2_to_f2(ka.y), k45 = bf16x2_to_f2(kb2.x), k67 = bf16x2_to_f2(kb2.y);
-            kk[0] = k01.x; kk[1] = k01.y; kk[2] = k23.x; kk[3] = k23.y; kk[4] = k45.x; kk[5] = k45.y; kk[6] = k67.x; kk[7] = k67.y;
-        }
-#pragma unroll
-        for (int i = 0; i < 8; ++i)
-#pragma unroll
-            for (int k = 0; k < 8; ++k) acc[i][k] = fmaf(uu[i], kk[k], acc[i][k]);
-    }
-    float* out = reinterpret_cast<float*>(base);
-#pragma unroll
-    for (int i = 0; i < 8; ++i) {
-        *reinterpret_cast<float4*>(out + (v0 + i) * KD + 4 * tx) = make_float4(acc[i][0], acc[i][1], acc[i][2], acc[i][3]);
-        *reinterpret_cast<float4*>(out + (v0 + i) * KD + 64 + 4 * tx) = make_float4(acc[i][4], acc[i][5], acc[i][6], acc[i][7]);
+        *reinterpret_cast<float4*>(out + r0 * KD + 16 * q + 4 * tig) = make_float4(a0[0], a0[1], a0[2], a0[3]);
+        *reinterpret_cast<float4*>(out + r1 * KD + 16 * q + 4 * tig) = make_float4(a1[0], a1[1], a1[2], a1[3]);
     }
     if (!kda) {
         for (int j = tid; j < d.L; j += NT_LA) Wbuf[sh * d.L + j] = 0.f;
@@ -377,7 +395,8 @@ extern "C" int lq_dequant(const lq_dims* d, void* ssm, const void* Kbuf, const v
     if (misaligned16({ssm, Kbuf, Ubuf})) return LQ_ERR_ALIGN;
     if (N == 0) return LQ_OK;
     // codes, folded scales, factors, weights, window rows (bf16; KDA keys fp32 because they carry the decay)
-    const size_t smem = sizeof(float) * (4096 + 2 * 128 + 2 * d->R * 128 + 64 + (kda ? d->L * 128 : d->L * 64) + d->L * 64);
+    const int kt = (3 * d->R + 15) / 16 * 16 + 8;               // operand row of the rank-R product, bf16 elements
+    const size_t smem = sizeof(float) * (4096 + 2 * 128 + 64 + (kda ? d->L * 128 : d->L * 64) + d->L * 64) + size_t(2) * 128 * kt * 2;
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     dim3 grid(unsigned(N) * d->HV), block(NT_LA);
     if (d->R == 4) {

@@ -308,13 +308,6 @@ __device__ __forceinline__ void s8x4_to_h2x2(uint32_t w, uint32_t& lo, uint32_t&
     lo = *reinterpret_cast<const uint32_t*>(&r0);
     hi = *reinterpret_cast<const uint32_t*>(&r1);
 }
-// D += A B for one m16n8k16 tile, bf16 operands, f32 accumulator (warp-wide)
-__device__ __forceinline__ void mma_bf16_16816(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0,
-                                               uint32_t b1) {
-    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
-                 : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
-                 : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
-}
 // D += A B for one m16n8k16 tile, f16 operands, f32 accumulator (warp-wide)
 __device__ __forceinline__ void mma_f16_16816(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0,
                                               uint32_t b1) {
