@@ -38,7 +38,7 @@ extern "C" {
 #define LQ_ERR_ALIGN (-3)        /* pointer or stride alignment */
 #define LQ_ERR_RANGE (-4)        /* a size is negative or inconsistent (e.g. HV % H != 0, N < 0) */
 #define LQ_ERR_LAUNCH (-5)       /* the CUDA runtime refused the launch; see lq_last_cuda_error() */
-#define LQ_ERR_LIMIT (-6)        /* more heads than the fixed scratch of lq_gdn_decode_noalloc holds */
+#define LQ_ERR_LIMIT (-6)        /* a call larger than lq_gdn_decode_noalloc takes */
 
 /* Shape of one layer's state, shared by all entry points. */
 typedef struct lq_dims {
@@ -68,8 +68,8 @@ int lq_device_status(int* status);
  * "pdl": 1 (default) launches the step and flush kernels with programmatic stream serialisation, so that the launch and
  * set-up of one overlap the tail of its predecessor on the stream; 0 = plain launches.
  * "work_list_min_programs": the fewest (row, head) programs of a fused decode call for which the `work` list passed to it
- * is used (-1 = default, sixteen per SM; 0 = whenever `work` is given).  The list costs a few global atomics per launch,
- * about three microseconds, and saves the flush of one head when the due heads sit unevenly on the CTAs. */
+ * is used (-1 = default, sixteen per SM; 0 = whenever `work` is given).  The mailboxes cost an atomic round trip or two
+ * per launch and save the flush of one head when the due heads sit unevenly on the CTAs. */
 int lq_set_option(const char* name, int32_t value);
 
 /* GDN decode step.  Replaces the kernel built by make_gdn_step (reference leapquant/kernels.py:27-692, launch
@@ -106,15 +106,13 @@ int lq_flush(const lq_dims* d, void* ssm, void* Kbuf, void* Ubuf, float* Wbuf, f
  * Where the fused form is not available (a debug step driver is selected, or the working set of one flush team does not
  * fit in the shared memory the step pipeline leaves behind) the two kernels are launched one after the other.
  *
- * `work` (optional, may be NULL): device scratch of at least lq_decode_work_bytes(min(N, NS), HV) bytes, 8-byte aligned, ALL
- * ZERO before the first call that uses it; the kernel leaves it all zero again.  With it the CTAs share one list of the
- * heads whose window filled in this call: a CTA flushes the first such head of its own and appends the others, and a CTA
- * that has none left takes them over (a serving batch fills the windows of a few rows per step, and the program-to-CTA
- * map puts their heads on the same CTAs now and then).  Results do not depend on it.  Calls that use the same `work` must
- * not overlap on the GPU.  The list makes CTAs wait for one another, so every CTA of the launch must be resident at once:
- * the launch uses one CTA per SM, which a process that owns the whole GPU gives; under a limit on the SMs a context may
- * use (MPS active-thread percentage, green contexts) pass NULL.  Small calls ignore it (see "work_list_min_programs").
- * NS * HV must stay below 2^23. */
+ * `work` (optional, may be NULL): device scratch of at least lq_decode_work_bytes(N, HV) bytes (16 KiB), 8-byte aligned, ALL
+ * ZERO before the first call that uses it; every call leaves it ready for the next (all zero but for a generation counter).  It holds a small mailbox per CTA: a CTA
+ * that filled the windows of two or three heads in this call flushes the first and posts the others; a CTA that filled none
+ * takes posted heads over (a serving batch fills the windows of a few rows per step, and the program-to-CTA map puts their
+ * heads on the same CTAs now and then); what nobody took, the poster flushes itself, so no CTA ever waits for another.
+ * Results do not depend on it.  Calls that use the same `work` must not overlap on the GPU.  Small calls ignore it (see
+ * "work_list_min_programs"). */
 int lq_gdn_decode(const lq_dims* d, void* ssm, void* Kbuf, void* Ubuf, float* Wbuf, float* Pbuf, int32_t* hcnt,
                   const void* mixed, const void* a, const void* b, const float* A_log, const float* dt_bias,
                   const int32_t* idx, void* o, int32_t N, float scale, const float* Q0, int32_t iters, void* work,
@@ -130,13 +128,14 @@ int64_t lq_decode_work_bytes(int32_t rows, int32_t HV);
  * buffer from torch.)  Some hosts of this library must not call cudaMalloc once they are running: a serving engine that
  * has measured free memory and given all of it to its cache pool, so that a later allocation may fail or push it over;
  * a plugin that lives under an allocator it does not own; a latency-bound thread for which the device-wide
- * synchronisation inside cudaMalloc / cudaFree is a stall.  lq_gdn_decode leaves the shared list of due heads (`work`) to
- * the caller, which is one more buffer to allocate; this entry point keeps that list inside the library instead, in a
- * device array of fixed size that is part of the library image: every GPU that loads the library holds
- * 4 * (16 + LQ_NOALLOC_MAX_HEADS) bytes (about 256 KiB) for it until the process exits, used or not.
+ * synchronisation inside cudaMalloc / cudaFree is a stall.  lq_gdn_decode leaves the mailboxes of due heads (`work`) to
+ * the caller, which is one more buffer to allocate; this entry point keeps them inside the library instead, in a device
+ * array of fixed size that is part of the library image: every GPU that loads the library holds lq_decode_work_bytes()
+ * = 16 KiB for it until the process exits, used or not.
  *   - Arguments and results are those of lq_gdn_decode without `work` / `work_bytes`; inputs and outputs are still the
  *     caller's.  It calls no cudaMalloc, cudaFree or other allocating routine.
- *   - Limit: min(N, NS) * HV <= LQ_NOALLOC_MAX_HEADS, else LQ_ERR_LIMIT and nothing is launched.
+ *   - Limit: calls of at most LQ_NOALLOC_MAX_HEADS (row, head) pairs, min(N, NS) * HV, and GPUs of at most 1 024 SMs (one
+ *     mailbox per CTA); a larger call returns LQ_ERR_LIMIT and nothing is launched.
  *   - The first call on a device asks the runtime for the array's address on that device (cudaGetSymbolAddress, with the
  *     caller's current device): make that first call outside any stream capture.
  *   - Every call on a device shares the one array.  The call zeroes the part it uses (a memset on `stream` ahead of the

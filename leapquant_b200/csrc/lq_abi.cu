@@ -66,7 +66,7 @@ extern "C" const char* lq_strerror(int code) {
         case LQ_ERR_ALIGN: return "state tensor must be 16-byte aligned with a slot stride that is a multiple of 4 floats";
         case LQ_ERR_RANGE: return "a size argument is negative or inconsistent";
         case LQ_ERR_LAUNCH: return "CUDA launch failed (see lq_last_cuda_error)";
-        case LQ_ERR_LIMIT: return "more (row, head) pairs than the fixed scratch of lq_gdn_decode_noalloc holds (LQ_NOALLOC_MAX_HEADS)";
+        case LQ_ERR_LIMIT: return "more (row, head) pairs than one call of lq_gdn_decode_noalloc takes (LQ_NOALLOC_MAX_HEADS)";
         default: return "unknown leapquant_b200 error code";
     }
 }

@@ -782,26 +782,24 @@ struct FuseTail {
     int team_bytes;                                 // shared memory of one team
     int* work;                                      // shared list of due heads (global scratch, see WL_*) or null: every CTA flushes its own
 };
-// Shared work list of the fused flush (global scratch of the caller, all zero between launches).  A CTA keeps the first head
-// whose window it filled and appends the others; when it has flushed its own it draws tickets (fetch-and-add) and flushes
-// the entries its tickets name, whoever appended them, so a CTA without due heads takes over the second or third head of a
-// CTA that has several.  One 64-bit word holds the three counters -- tickets drawn, entries appended, CTAs that have
-// reported -- so one atomic both draws a ticket and tells whether the list is final.  A ticket past the end of the list is
-// resolved when every CTA has reported: its holder waits for the slowest CTA's step, as the launch does anyway.  That wait
-// needs every CTA of the launch to be resident at once, which one CTA per SM on a whole GPU gives; a context limited to
-// part of the SMs must run without the list (the wait is bounded and ends with ST_FLUSH_TIMEOUT in the status word).  The
-// last CTA to leave zeroes the list for the next launch.
-constexpr int WL_EXITED = 2, WL_ITEMS = 16;                      // int offsets (the counter word is ints 0 and 1); item = head + 1, 0 = not written yet
-constexpr int WL_FIELD = 24;                                     // bits of the ticket and entry counters
-constexpr unsigned long long WL_TAKEN1 = 1ull, WL_COUNT1 = 1ull << WL_FIELD, WL_DONE1 = 1ull << (2 * WL_FIELD);
-__device__ __forceinline__ int wl_taken(unsigned long long w) { return int(w & (WL_COUNT1 - 1)); }
-__device__ __forceinline__ int wl_count(unsigned long long w) { return int((w >> WL_FIELD) & (WL_COUNT1 - 1)); }
-__device__ __forceinline__ int wl_done(unsigned long long w) { return int(w >> (2 * WL_FIELD)); }
+// Shared mailboxes of the fused flush (global scratch of the caller, all zero between launches).  A serving batch fills the
+// windows of a few rows per step, and the program -> CTA map puts two or three of their heads on some CTAs and none on
+// others.  A CTA that filled two or three windows keeps the first head and leaves the others in its own mailbox (a few
+// slots per CTA: plain stores, no atomics); a CTA that filled none scans the mailboxes and claims an entry with an atomic
+// exchange, which also empties the slot.  The owner, when it has flushed its own head, claims back whatever is still in its
+// mailbox and flushes that too: every entry is flushed exactly once whether or not anybody helps, so nobody waits for
+// anybody for correctness, helpers may give up at any time, and the slots are all zero again when the kernel ends.
+// Helpers stop when the launch's reports are complete and a scan finds nothing: every CTA adds one to a counter after its
+// mailbox is written; the CTA that makes it `grid` sets the counter back to zero and bumps a generation word, which every
+// CTA read when it started (its own report, and therefore the last one, comes after that read).
+// A CTA that filled four or more windows is in a call in which every CTA did (windows in phase) and keeps them all.
+constexpr int WL_DONE = 0, WL_GEN = 1, WL_BOX = 16;              // int offsets: reports of this launch, generation, mailboxes
+constexpr int WL_SLOTS = 4;                                      // slots per CTA (at most two are used); entry = head + 1
+constexpr int WL_MAX_CTAS = 1024;                                // the scratch is sized for launches of up to this many CTAs
+constexpr int WL_ITEMS = WL_BOX;                                 // (first int after the header)
+constexpr uint32_t WL_HELP_POLLS = 4096;                         // a helper gives up after this many empty scans (about a millisecond)
 __device__ __forceinline__ void st_volatile_i32(int* p, int v) { *reinterpret_cast<volatile int*>(p) = v; }
 __device__ __forceinline__ int ld_volatile_i32(const int* p) { return *reinterpret_cast<const volatile int*>(p); }
-__device__ __forceinline__ unsigned long long ld_volatile_u64(const unsigned long long* p) {
-    return *reinterpret_cast<const volatile unsigned long long*>(p);
-}
 
 #ifndef LQ_NPW
 #define LQ_NPW 2
@@ -862,6 +860,8 @@ __global__ void __launch_bounds__(UT + NG * GT, 1) step_pipelined_kernel(StepPar
     __syncthreads();
     pdl_trigger();
     pdl_wait();                                                  // everything below reads what earlier kernels of the stream wrote
+    int gen0 = 0;                                                // (thread 0) generation of the mailboxes when this CTA started
+    if (FUSE && tid == 0 && ft.work != nullptr) gen0 = ld_volatile_i32(ft.work + WL_GEN);
 
     auto run_roles = [&]() {
     if (warp == 0) {
@@ -1151,6 +1151,7 @@ __global__ void __launch_bounds__(UT + NG * GT, 1) step_pipelined_kernel(StepPar
     if constexpr (FUSE) {
         __shared__ uint32_t tm_slot;
         __shared__ int s_pop[4];
+        __shared__ int s_list[24];                               // mailbox slots a scan found occupied
         static_assert(UT + NG * GT == 512, "the fused flush is written for two teams of 256 threads");
         const int nteams = ft.teams;                             // work areas that fit in the ring: 1 or 2
         const int team = tid >> 8, ttid = tid & 255;
@@ -1160,128 +1161,129 @@ __global__ void __launch_bounds__(UT + NG * GT, 1) step_pipelined_kernel(StepPar
         __syncthreads();                                         // every role is done; the ring is dead, this CTA's global writes are issued
         const int ndl = *abortf ? 0 : *dl_n;
         int* const wl = ft.work;
-        unsigned long long* const wlw = reinterpret_cast<unsigned long long*>(wl);
         if (wl == nullptr && ndl == 0) return;                   // (before any tensor memory is held)
-        // Rounds of heads: without the list one round of this CTA's own heads; with it, the CTA's first head and then one
-        // round per ticket.  `heads` points into shared memory (the CTA's own list or the ticket's entries).
-        const int* heads = dl;
-        int nh = ndl;
-        unsigned long long seen = 0;                             // (thread 0) the counter word as last read
-        int ticket = -1, held = 1;                               // (thread 0) a ticket drawn but not resolved yet, and how many it stands for
+        const bool keep_all = wl == nullptr || ndl >= 4 || ndl - 1 > WL_SLOTS;
+        const int npub = keep_all ? 0 : (ndl > 1 ? ndl - 1 : 0); // heads left in this CTA's mailbox
+        int* const box = wl + WL_BOX;
         if (wl != nullptr) {
-            // a CTA that filled four or more windows is in a call in which every CTA did (windows in phase): it keeps them all
-            // and flushes them in pairs, as without the list; two or three are the uneven case the list is for
-            const bool keep_all = ndl >= 4;
-            nh = keep_all ? ndl : (ndl > 0 ? 1 : 0);
-            if (ndl > 1 && !keep_all) __threadfence();           // the step's stores of the appended heads come before their entries
+            if (npub > 0) __threadfence();                       // the step's stores of the posted heads come before their entries
             __syncthreads();
             if (tid == 0) {
-                if (ndl == 1 || keep_all) {
-                    atomicAdd(wlw, WL_DONE1);                     // nothing to append, nothing to learn yet
-                } else if (ndl == 0) {
-                    seen = atomicAdd(wlw, WL_DONE1 + WL_TAKEN1) + WL_DONE1;
-                    ticket = wl_taken(seen);
-                } else {
-                    seen = atomicAdd(wlw, WL_DONE1 + (ndl - 1) * WL_COUNT1);
-                    const int base = wl_count(seen);
-                    for (int i = 1; i < ndl; ++i) st_volatile_i32(wl + WL_ITEMS + base + i - 1, dl[i] + 1);
-                    seen += WL_DONE1 + (ndl - 1) * WL_COUNT1;
+                for (int i = 0; i < npub; ++i) st_volatile_i32(box + bid * WL_SLOTS + i, dl[1 + i] + 1);
+                __threadfence();
+                const int reported = atomicAdd(wl + WL_DONE, 1);
+                if (reported == grid - 1) {                      // the last CTA to report closes the launch's count at once: the others
+                    st_volatile_i32(wl + WL_DONE, 0);            // learn from the generation that no more heads will be posted.  (This
+                    __threadfence();                             // thread reaches the first barrier of its flush a round trip late;
+                    atomicAdd(wl + WL_GEN, 1);                   // the flush starts with global loads that take as long.)
                 }
             }
         }
+        // Rounds of heads: first what this CTA keeps of its own list; with the mailboxes, then one head per round -- its own
+        // posted heads that nobody took, or, for a CTA that filled nothing, heads from other CTAs' mailboxes.
+        const int* heads = dl;
+        int nh = keep_all ? ndl : (ndl > 0 ? 1 : 0);
+        int reclaim = 0;                                         // (thread 0) next slot of the own mailbox to look at
+        const int total = grid * WL_SLOTS;
         bool inited = false;
         bool more = true;
         while (more) {
-            if (nh == 0) {                                       // (shared list only) the next ticket
+            if (nh == 0) {                                       // (mailboxes only) find the next head
                 if (tid == 0) {
-                    int q0 = -1, q1 = -1;
+                    int q = -1;
                     if (!*abortf) {
-                        if (ticket < 0) {
-                            // more entries waiting than CTAs: two side by side (throughput); else one by the whole CTA (latency)
-                            held = (nteams == 2 && wl_count(seen) - wl_taken(seen) > grid) ? 2 : 1;
-                            seen = atomicAdd(wlw, held * WL_TAKEN1);
-                            ticket = wl_taken(seen);
-                        }
-                        const int want = held;
-                        bool gave_up = true;
-                        for (uint32_t it = 0; it < WAIT_LIMIT; ++it) {
-                            if (ticket < wl_count(seen) || wl_done(seen) >= grid) { gave_up = false; break; }
-                            if (it > 8) __nanosleep(64);
-                            seen = ld_volatile_u64(wlw);
-                        }
-                        const int valid = gave_up ? 0 : min(want, wl_count(seen) - ticket);
-                        for (int j = 0; j < valid; ++j) {        // between the count and the entry: a moment
-                            int q = -1;
-                            for (uint32_t it = 0; it < WAIT_LIMIT && q < 0; ++it) q = ld_volatile_i32(wl + WL_ITEMS + ticket + j) - 1;
-                            if (q < 0) { gave_up = true; q0 = q1 = -1; break; }
-                            if (j == 0) q0 = q; else q1 = q;
-                        }
-                        if (gave_up) atomicOr(&g_status, ST_FLUSH_TIMEOUT);
-                        __threadfence();                         // the head's data is read after its entry
-                        ticket = -1;
-                        // a long list keeps every CTA busy anyway: draw the next tickets now, so that the atomic's round trip
-                        // runs under this flush (a short list is left to whoever is idle)
-                        if (q0 >= 0 && wl_count(seen) - wl_taken(seen) > 3 * grid) {
-                            held = nteams == 2 ? 2 : 1;
-                            seen = atomicAdd(wlw, held * WL_TAKEN1);
-                            ticket = wl_taken(seen);
+                        for (; reclaim < npub && q < 0; ++reclaim) {
+                            const int x = atomicExch(box + bid * WL_SLOTS + reclaim, 0);
+                            if (x > 0) q = x - 1;
                         }
                     }
-                    s_pop[0] = q0;
-                    s_pop[1] = q1;
+                    s_pop[0] = q;
                 }
                 __syncthreads();
-                heads = s_pop;
-                nh = s_pop[0] < 0 ? 0 : (s_pop[1] < 0 ? 1 : 2);
-            }
-            more = nh > 0 && wl != nullptr;
-            if (nh > 0) {
-            if (!inited) {                                       // first head of this CTA: tensor memory and the per-team constants
-                if (warp == 0) tmem_alloc(&tm_slot, 2 * TMEM_COLS);
-                const FlushSmem fi = flush_carve<R>(stage_smem + (team < nteams ? team : 0) * ft.team_bytes, L, KDA);
-                if (team < nteams) flush_init<R>(fi, ft.Q0, ttid, 256);
-                tc_fence_before_sync();
-                __syncthreads();
-                tc_fence_after_sync();
-                inited = true;
-            }
-            const uint32_t tm = tm_slot;
-            int k = 0;
-            if (nteams == 2 && nh >= 2) {                        // pairs: each team of 8 warps goes through its own heads
-                const FlushSmem fs = flush_carve<R>(stage_smem + team * ft.team_bytes, L, KDA);
-                auto tsync = [&] { named_bar(8 + team, 256); };
-                const int npair = nh >> 1;
-                bool ok = true;
-                for (int i = 0; i < npair && ok; ++i) ok = flush_head<R, KDA, 8>(fs, A, heads[2 * i + team], ttid, tm + team * TMEM_COLS, tsync);
-                if (!ok && ttid == 0) *abortf = 1;
-                k = 2 * npair;
-                __syncthreads();
-            }
-            if (k < nh && *abortf == 0) {                        // a last single head: all 16 warps
-                const FlushSmem f0 = flush_carve<R>(stage_smem, L, KDA);
-                for (; k < nh; ++k)
-                    if (!flush_head<R, KDA, 16>(f0, A, heads[k], tid, tm, [] { __syncthreads(); })) {
-                        if (tid == 0) *abortf = 1;
-                        k = nh;
+                int q = s_pop[0];
+                if (q < 0 && *abortf == 0) {                     // nothing (left) of its own: help the others
+                    // One trip = the generation and every mailbox slot, read side by side.  A scan that races with the last
+                    // postings may miss one: its owner flushes it.  Occupied slots go to a short list and the CTA tries the one
+                    // its number picks, so that helpers spread over the entries.
+                    for (uint32_t it = 0; it < WL_HELP_POLLS; ++it) {
+                        __syncthreads();                         // (s_pop of the previous trip has been read)
+                        if (tid == 0) {
+                            s_pop[2] = 0;
+                            s_pop[1] = ld_volatile_i32(wl + WL_GEN);
+                        }
+                        __syncthreads();
+                        for (int i = tid; i < total; i += UT + NG * GT)
+                            if (ld_volatile_i32(box + i) != 0) {
+                                const int pos = atomicAdd(&s_pop[2], 1);
+                                if (pos < 24) s_list[pos] = i;
+                            }
+                        __syncthreads();
+                        if (tid == 0) {
+                            int got = -1;                        // -1: nothing yet, -2: lost the race for an entry, -3: launch over
+                            const int nfound = min(s_pop[2], 24);
+                            if (nfound > 0) {
+                                const int x = atomicExch(box + s_list[(bid * 7 + int(it)) % nfound], 0);
+                                got = x > 0 ? x - 1 : -2;
+                                if (x > 0) __threadfence();      // the head's data is read after its entry
+                            } else if (s_pop[1] != gen0) {
+                                got = -3;
+                            }
+                            s_pop[0] = got;
+                        }
+                        __syncthreads();
+                        const int got = s_pop[0];
+                        if (got >= 0) q = got;
+                        // leave the loop with a head, when the launch is over, or -- a CTA that had heads of its own comes late, when
+                        // the postings are in -- as soon as a scan finds nothing; only a CTA that filled no window waits for more
+                        if (got >= 0 || got == -3 || (got == -1 && ndl > 0)) it = WL_HELP_POLLS;
+                        else if (got == -1) __nanosleep(100);
                     }
+                    __syncthreads();
+                    if (tid == 0) s_pop[0] = q;
+                    __syncthreads();
+                }
+                heads = s_pop;
+                nh = q >= 0 ? 1 : 0;
+                if (nh == 0) more = false;
             }
-            __syncthreads();                                     // (s_pop is rewritten by the next round; abort flag settled)
+            if (nh > 0) {
+                if (!inited) {                                   // first head of this CTA: tensor memory and the per-team constants
+                    if (warp == 0) tmem_alloc(&tm_slot, 2 * TMEM_COLS);
+                    const FlushSmem fi = flush_carve<R>(stage_smem + (team < nteams ? team : 0) * ft.team_bytes, L, KDA);
+                    if (team < nteams) flush_init<R>(fi, ft.Q0, ttid, 256);
+                    tc_fence_before_sync();
+                    __syncthreads();
+                    tc_fence_after_sync();
+                    inited = true;
+                }
+                const uint32_t tm = tm_slot;
+                int k = 0;
+                if (nteams == 2 && nh >= 2) {                    // pairs: each team of 8 warps goes through its own heads
+                    const FlushSmem fs = flush_carve<R>(stage_smem + team * ft.team_bytes, L, KDA);
+                    auto tsync = [&] { named_bar(8 + team, 256); };
+                    const int npair = nh >> 1;
+                    bool ok = true;
+                    for (int i = 0; i < npair && ok; ++i) ok = flush_head<R, KDA, 8>(fs, A, heads[2 * i + team], ttid, tm + team * TMEM_COLS, tsync);
+                    if (!ok && ttid == 0) *abortf = 1;
+                    k = 2 * npair;
+                    __syncthreads();
+                }
+                if (k < nh && *abortf == 0) {                    // a last single head: all 16 warps
+                    const FlushSmem f0 = flush_carve<R>(stage_smem, L, KDA);
+                    for (; k < nh; ++k)
+                        if (!flush_head<R, KDA, 16>(f0, A, heads[k], tid, tm, [] { __syncthreads(); })) {
+                            if (tid == 0) *abortf = 1;
+                            k = nh;
+                        }
+                }
+                __syncthreads();                                 // (s_pop is rewritten by the next round; abort flag settled)
             }
+            if (wl == nullptr) more = false;
             nh = 0;
         }
         tc_fence_before_sync();
         __syncthreads();
         if (inited && warp == 0) tmem_dealloc(tm_slot, 2 * TMEM_COLS);
-        if (wl != nullptr) {
-            // the last CTA to leave zeroes the list: every other CTA is past its last access
-            if (tid == 0) s_pop[2] = (atomicAdd(wl + WL_EXITED, 1) == grid - 1) ? wl_count(ld_volatile_u64(wlw)) : -1;
-            __syncthreads();
-            const int nclean = s_pop[2];
-            if (nclean >= 0) {
-                for (int i = tid; i < nclean; i += UT + NG * GT) wl[WL_ITEMS + i] = 0;
-                if (tid == 0) { *wlw = 0ull; wl[WL_EXITED] = 0; }
-            }
-        }
     }
 }
 
@@ -1334,9 +1336,10 @@ static int launch_step(const StepParams& P, cudaStream_t st, const FuseTail* fus
         ft.team_bytes = int((flush_smem_bytes<R>(P.d.L, 0, KDA) + 127) & ~size_t(127));
         ft.teams = (2 * ft.team_bytes <= ring_bytes) ? 2 : (ft.team_bytes <= ring_bytes ? 1 : 0);
         if (ft.teams == 0) return LQ_ERR_UNSUPPORTED;
-        // the list costs two or three microseconds of atomics per launch: it pays once a CTA has many programs
+        // the mailboxes cost an atomic round trip or two per launch: they pay once a CTA has many programs
         const int wl_min = g_work_list_min.load(std::memory_order_relaxed);
         if (int64_t(P.N) * P.d.HV < (wl_min >= 0 ? int64_t(wl_min) : int64_t(16) * device_sm_count())) ft.work = nullptr;
+        if (device_sm_count() > WL_MAX_CTAS) ft.work = nullptr;
         if (conv) {
             int rc = ensure_smem((const void*)step_pipelined_kernel<R, KDA, NG, true, true>, smem);
             if (rc) return rc;
@@ -1457,9 +1460,8 @@ static int decode_common(const lq_dims* d, void* ssm, void* Kbuf, void* Ubuf, fl
                          void* work, int64_t work_bytes, void* stream, const lq_conv1d* conv = nullptr) {
     if (!Q0) return LQ_ERR_NULL;
     if (iters < 0) return LQ_ERR_RANGE;
-    if (work) {                                                  // shared list of due heads: one entry per head the call can fill
+    if (work) {                                                  // shared mailboxes of due heads
         if (reinterpret_cast<uintptr_t>(work) & 7) return LQ_ERR_ALIGN;
-        if (d && int64_t(d->NS) * d->HV >= (int64_t(1) << (lq::WL_FIELD - 1))) return LQ_ERR_RANGE;    // the counters are 24-bit fields
         if (d && N > 0 && work_bytes < lq_decode_work_bytes(N < d->NS ? N : d->NS, d->HV)) return LQ_ERR_RANGE;
     }
     lq::FuseTail ft = {Q0, iters, 0, 0, static_cast<int*>(work)};
@@ -1472,7 +1474,9 @@ static int decode_common(const lq_dims* d, void* ssm, void* Kbuf, void* Ubuf, fl
 }
 
 extern "C" int64_t lq_decode_work_bytes(int32_t rows, int32_t HV) {
-    return 4 * (int64_t(lq::WL_ITEMS) + int64_t(rows > 0 ? rows : 0) * int64_t(HV > 0 ? HV : 0));
+    (void)rows;                                                  // (the scratch does not grow with the call: a few slots per CTA)
+    (void)HV;
+    return 4 * (int64_t(lq::WL_BOX) + int64_t(lq::WL_SLOTS) * lq::WL_MAX_CTAS);
 }
 
 extern "C" int lq_gdn_decode(const lq_dims* d, void* ssm, void* Kbuf, void* Ubuf, float* Wbuf, float* Pbuf, int32_t* hcnt,
@@ -1510,12 +1514,12 @@ extern "C" int lq_kda_decode_conv(const lq_dims* d, void* ssm, void* Kbuf, void*
 }
 
 // ------------------------------------------------------------------------------------------------------------------
-// GDN decode for callers that must not allocate.  The shared list of due heads that lq_gdn_decode takes as `work` lives
+// GDN decode for callers that must not allocate.  The mailboxes of due heads that lq_gdn_decode takes as `work` live
 // here in a file-scope device array of fixed size, which every GPU that loads the library holds until the process exits.
 // In host code the array's name only stands for the symbol: its device address comes from cudaGetSymbolAddress(), asked
 // once per device with that device current, and is what the kernel is given.
 // ------------------------------------------------------------------------------------------------------------------
-static __device__ __align__(256) int g_noalloc_work[lq::WL_ITEMS + LQ_NOALLOC_MAX_HEADS];
+static __device__ __align__(256) int g_noalloc_work[lq::WL_BOX + lq::WL_SLOTS * lq::WL_MAX_CTAS];
 static std::atomic<int*> g_noalloc_ptr[64];                     // per device: the array's address on that device (null = not asked yet)
 
 extern "C" int lq_gdn_decode_noalloc(const lq_dims* d, void* ssm, void* Kbuf, void* Ubuf, float* Wbuf, float* Pbuf, int32_t* hcnt,
@@ -1525,7 +1529,7 @@ extern "C" int lq_gdn_decode_noalloc(const lq_dims* d, void* ssm, void* Kbuf, vo
     if (!d) return LQ_ERR_NULL;
     if (N < 0) return LQ_ERR_RANGE;
     const int64_t rows = N < d->NS ? N : d->NS;
-    if (d->HV <= 0 || rows * int64_t(d->HV) > LQ_NOALLOC_MAX_HEADS) return LQ_ERR_LIMIT;        // more heads than the array has entries
+    if (d->HV <= 0 || rows * int64_t(d->HV) > LQ_NOALLOC_MAX_HEADS) return LQ_ERR_LIMIT;        // larger than the largest call this entry takes
     int dev = 0;
     cudaError_t e = cudaGetDevice(&dev);
     if (e != cudaSuccess || dev < 0 || dev >= 64) {
@@ -1550,7 +1554,7 @@ extern "C" int lq_gdn_decode_noalloc(const lq_dims* d, void* ssm, void* Kbuf, vo
         return LQ_ERR_LAUNCH;
     }
     return decode_common(d, ssm, Kbuf, Ubuf, Wbuf, Pbuf, nullptr, hcnt, mixed, a, b, A_log, dt_bias, idx, o, N, scale, 0.f, false, Q0,
-                         iters, ptr, int64_t(sizeof(int)) * (lq::WL_ITEMS + LQ_NOALLOC_MAX_HEADS), stream);
+                         iters, ptr, int64_t(sizeof(int)) * (lq::WL_BOX + lq::WL_SLOTS * lq::WL_MAX_CTAS), stream);
 }
 
 extern "C" int lq_causal_conv1d_update(const lq_conv1d* conv, const int32_t* idx, int32_t N, int32_t channels, int32_t NS, void* out,

@@ -99,8 +99,8 @@ class LeapQuantState:
         self.conv_one_launch = False
         self._kconv = None
         self._mixed = None
-        # shared list of the heads whose window fills in a call (all zero between calls): lets a CTA without such a head take
-        # over a head of a CTA that has several.  No counterpart in the reference.
+        # mailboxes for the heads whose window fills in a call (zeroed once, here): let a CTA without such a head take over a
+        # head of a CTA that has several.  No counterpart in the reference.
         self.work = torch.zeros(KN.decode_work_ints(NS, HV), dtype=torch.int32, device=dev)
         self.kdeq = KN.make_dequant(NS, HV, K, V, L, SS, buf_dtype=KN.BF16, R=R, kda=kda)
         self.kquant = KN.make_quantize(NS, HV, K, V, L, SS, R=R, ITERS=3 if kda else 1, kda=kda)

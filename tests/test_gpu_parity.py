@@ -556,7 +556,8 @@ def test_fused_decode_equals_step_then_flush(kda, L, R, H, HV, work_list):
     for name in ("Kbuf", "Ubuf", "Wbuf", "Pbuf") + (("Gbuf",) if kda else ()):
         assert torch.equal(bits(getattr(gpu_f.st, name)), bits(getattr(gpu_s.st, name))), name
     assert torch.equal(bits(gpu_f.ssm), bits(gpu_s.ssm))
-    assert int(gpu_f.st.work.abs().max()) == 0, "the shared list is left all zero"
+    w = gpu_f.st.work
+    assert int(w[0]) == 0 and int(w[2:].abs().max()) == 0, "the mailboxes are left empty (word 1 is a generation counter)"
     from leapquant_b200 import _lib
     torch.cuda.synchronize()
     assert _lib.device_status() == 0

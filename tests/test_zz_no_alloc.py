@@ -1,7 +1,7 @@
-"""GPU test of lq_gdn_decode_noalloc, the decode entry point for callers that cannot allocate device memory: the shared list
-of due heads lives in a fixed device array inside the library instead of a buffer of the caller's.  Called through the C
+"""GPU test of lq_gdn_decode_noalloc, the decode entry point for callers that cannot allocate device memory: the mailboxes
+of due heads live in a fixed device array inside the library instead of a buffer of the caller's.  Called through the C
 ABI, twice in a row, against lq_gdn_decode with a caller-owned list on the same inputs: outputs, window buffers and packed
-state must agree bit for bit (the list never changes a result, only which CTA flushes a head).
+state must agree bit for bit (the mailboxes never change a result, only which CTA flushes a head).
 
 The file sorts after the other test files on purpose: it has to pass both in a fresh process and after everything else has
 used the device.
@@ -42,7 +42,7 @@ class Side:
 def test_noalloc_decode_matches_decode_twice_in_a_row():
     from leapquant_b200 import _lib
     from oracle import lq_oracle as O
-    NS, N, HV, H, L, R = 81, 80, 32, 16, 8, 4                  # 2 560 programs: the shared list is in use by default
+    NS, N, HV, H, L, R = 81, 80, 32, 16, 8, 4                  # 2 560 programs: the mailboxes are in use by default
     g = torch.Generator(device="cuda").manual_seed(41)
     base = torch.randn(NS, HV, V, K, device="cuda", generator=g) * 0.5
     ours, ref = Side(base, NS, HV, H, L, R), Side(base, NS, HV, H, L, R)
