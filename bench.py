@@ -433,7 +433,9 @@ def secondary_layer_numbers(layer, peak, reps_step=3):
     L, HV, R, kda = wl["L"], wl["HV"], wl["R"], wl["kda"]
     gqa = HV // wl["H"]
     st = layer.st
-    layer.to_lockstep()                                          # warm-up of the two kernels; windows empty
+    st.dequantize(layer.ssm, torch.zeros(1, dtype=torch.int32, device=layer.device))      # loads the kernel (null slot: no work)
+    torch.cuda.synchronize()
+    live_deq_s, _ = layer.to_lockstep()                          # windows as the main measurement left them (every fill level): live
     for t in range(3):
         layer.decode_resident(t)                                 # a few live entries for the dequantize to fold in
     deq_s, qnt_s = layer.to_lockstep()
@@ -442,7 +444,10 @@ def secondary_layer_numbers(layer, peak, reps_step=3):
                                   "dequantize_gbs": rt / deq_s / 1e9, "quantize_gbs": rt / qnt_s / 1e9,
                                   "dequantize_frac_of_measured_hbm": rt / deq_s / 1e9 / peak,
                                   "quantize_frac_of_measured_hbm": rt / qnt_s / 1e9 / peak,
-                                  "bytes_per_head": roundtrip_bytes(R)}}
+                                  "bytes_per_head": roundtrip_bytes(R),
+                                  "dequantize_live_windows_ms": 1e3 * live_deq_s,
+                                  "note": "dequantize_ms: windows with 3 entries (right after a prefill); dequantize_live_windows_ms: "
+                                          "the staggered windows of the decode batch (a mixed prefill + decode step), first call"}}
     # lock-step: every head flushes on the same step (the graph is the one captured for the staggered run)
     dt_l, reps_l = replay_timed(layer.graph, 1, 0.1)
     amort = window_bytes_per_head_step(L, R, gqa, kda)

@@ -78,12 +78,7 @@ __device__ __forceinline__ void mma_h_16816(float (&c)[4], uint32_t a0, uint32_t
                  : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
                  : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
 }
-__device__ __forceinline__ void ldmatrix_x4_trans(uint32_t (&r)[4], const void* smem_row) {
-    const uint32_t addr = uint32_t(__cvta_generic_to_shared(smem_row));
-    asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];"
-                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3])
-                 : "r"(addr));
-}
+// (ldmatrix_x4_trans: lq_quant.cu, compiled ahead of this file in the same translation unit)
 __device__ __forceinline__ void ldmatrix_x4(uint32_t (&r)[4], const void* smem_row) {
     const uint32_t addr = uint32_t(__cvta_generic_to_shared(smem_row));
     asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"

@@ -167,6 +167,13 @@ quantize_kernel(lq_dims d, char* __restrict__ ssm, float* __restrict__ Wbuf, flo
     if (tid == 0) hcnt[sh] = 0;
 }
 
+// four 8 x 8 b16 tiles, transposed: lane l supplies the address of row l % 8 of tile l / 8 and receives, of each tile, the
+// elements (2 (l % 4), l / 4) and (2 (l % 4) + 1, l / 4)
+__device__ __forceinline__ void ldmatrix_x4_trans(uint32_t (&r)[4], const void* p) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0, %1, %2, %3}, [%4];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(smem_u32(p)));
+}
+
 // ------------------------------------------------------------------------------------------------------------------
 // dequantize in place
 // ------------------------------------------------------------------------------------------------------------------
@@ -196,7 +203,8 @@ dequant_kernel(lq_dims d, char* __restrict__ ssm, const uint16_t* __restrict__ K
     uint16_t* Aop = reinterpret_cast<uint16_t*>(svp + 128);   // [128 rows v][KS]: Qp head | Qp remainder | Qp head | 0
     uint16_t* Bop = Aop + 128 * KS;                       // [128 cols c][KS]: Uc head | Uc head | Uc remainder | 0
     float* ws = reinterpret_cast<float*>(Bop + 128 * KS); // [64] window weights
-    float* Kf = ws + 64;                                  // KDA: [L][128] decayed keys (fp32); GDN: [L][64] bf16 pairs
+    float* Kf = ws + 64;                                  // KDA: [L][128] decayed keys (fp32), then the values [L][64] bf16 pairs
+                                                          // GDN: keys [Lp][WST] bf16 (columns permuted), then values [Lp][WST] bf16
     const int tid = threadIdx.x;
     const int n = blockIdx.x / d.HV, hv = blockIdx.x % d.HV;
     const int slot = idx[n];
@@ -205,8 +213,12 @@ dequant_kernel(lq_dims d, char* __restrict__ ssm, const uint16_t* __restrict__ K
     const int64_t sh = int64_t(slot) * d.HV + hv;
     const int h = min(max(hcnt[sh], 0), d.L);
     const float p = kda ? 1.f : Pbuf[sh];
-    uint32_t* Kb2 = reinterpret_cast<uint32_t*>(Kf);                              // GDN keys as stored
-    uint32_t* Ub2 = reinterpret_cast<uint32_t*>(Kf + (kda ? d.L * 128 : d.L * 64));  // values as stored (bf16 pairs) [L][64]
+    constexpr int WST = 136;                              // GDN window rows in shared memory: 128 bf16 + 16 bytes, so that the
+                                                          // eight rows of an ldmatrix tile fall into different bank groups
+    const int Lp = (d.L + 15) & ~15;
+    uint16_t* Ks = reinterpret_cast<uint16_t*>(Kf);       // GDN keys: within every 16 columns c -> 8 (c % 4 / 2) + 2 (c / 4) + c % 2
+    uint16_t* Us = Ks + Lp * WST;                         // GDN values as stored
+    uint32_t* Ub2 = reinterpret_cast<uint32_t*>(Kf + d.L * 128);                  // KDA values as stored (bf16 pairs) [L][64]
 
     for (int i = tid; i < 4096 / 4; i += NT_LA)
         reinterpret_cast<uint4*>(cw)[i] = reinterpret_cast<const uint4*>(base + CK_CODES)[i];
@@ -226,20 +238,28 @@ dequant_kernel(lq_dims d, char* __restrict__ ssm, const uint16_t* __restrict__ K
 #pragma unroll
         for (int r = 3 * R; r < KT; ++r) { Aop[tid * KS + r] = 0; Bop[tid * KS + r] = 0; }
     }
-    if (tid < d.L) ws[tid] = tid < h ? Wbuf[sh * d.L + tid] : 0.f;
+    if (tid < 64) ws[tid] = tid < h ? Wbuf[sh * d.L + tid] : 0.f;         // (all 64: the tensor-core window term reads whole steps of 16)
     {
         const uint4* kb = reinterpret_cast<const uint4*>(Kbuf + sh * d.L * KD);
         const uint4* ub = reinterpret_cast<const uint4*>(Ubuf + sh * d.L * VD);
-        for (int i = tid; i < h * 16; i += NT_LA) {
-            reinterpret_cast<uint4*>(Ub2)[i] = ub[i];
-            const uint4 kv = kb[i];
+        const int hp = kda ? h : ((h + 15) & ~15);           // GDN: whole k-steps of 16 rows, the rows past h zero
+        for (int i = tid; i < hp * 16; i += NT_LA) {
+            const int j = i >> 4, c8 = i & 15;                // row, 16-byte chunk (8 columns) of the row
+            const uint4 z = make_uint4(0u, 0u, 0u, 0u);
+            const uint4 uv = j < h ? ub[i] : z, kv = j < h ? kb[i] : z;
             if (kda) {
+                reinterpret_cast<uint4*>(Ub2)[i] = uv;
                 float4* kp = reinterpret_cast<float4*>(Kf + i * 8);
                 const float2 a0 = bf16x2_to_f2(kv.x), a1 = bf16x2_to_f2(kv.y), a2 = bf16x2_to_f2(kv.z), a3 = bf16x2_to_f2(kv.w);
                 kp[0] = make_float4(a0.x, a0.y, a1.x, a1.y);
                 kp[1] = make_float4(a2.x, a2.y, a3.x, a3.y);
             } else {
-                reinterpret_cast<uint4*>(Kb2)[i] = kv;
+                *reinterpret_cast<uint4*>(Us + j * WST + 8 * c8) = uv;
+                // the chunk holds columns 4 t .. 4 t + 7 of a group of 16 (t = 0 or 2): pairs (4t, 4t+1), (4t+4, 4t+5) go to the
+                // first n-tile of the group at 2 t, 2 t + 2, pairs (4t+2, 4t+3), (4t+6, 4t+7) to the second at 8 + 2 t, 8 + 2 t + 2
+                uint16_t* kd = Ks + j * WST + 16 * (c8 >> 1) + 4 * (c8 & 1);
+                *reinterpret_cast<uint2*>(kd) = make_uint2(kv.x, kv.z);
+                *reinterpret_cast<uint2*>(kd + 8) = make_uint2(kv.y, kv.w);
             }
         }
     }
@@ -267,55 +287,92 @@ dequant_kernel(lq_dims d, char* __restrict__ ssm, const uint16_t* __restrict__ K
     const int cn = 4 * (gid >> 1) + (gid & 1);              // column (within a group of 16) that n index gid of the first n-tile stands for
     const float sv0 = svp[r0], sv1 = svp[r1];
     float* out = reinterpret_cast<float*>(base);            // (everything of the slot that is read was copied to shared memory above)
-    // one group of 16 columns at a time, start to finish: eight accumulators per thread instead of sixty-four
-#pragma unroll 2
-    for (int q = 0; q < 8; ++q) {
-        float c0[4] = {0.f, 0.f, 0.f, 0.f}, c1[4] = {0.f, 0.f, 0.f, 0.f};
+    // two groups of 16 columns at a time, start to finish: sixteen accumulators per thread instead of sixty-four, and the
+    // values of a window entry are fetched four times per entry, not eight
+#pragma unroll 1
+    for (int qp = 0; qp < 4; ++qp) {
+        float a0[2][4], a1[2][4];                           // [group][column]: rows r0 and r1, columns 16 q + 4 tig + k
 #pragma unroll
-        for (int ks = 0; ks < KT / 16; ++ks) {
-            const uint16_t* b0p = Bop + (16 * q + cn) * KS + 16 * ks + 2 * tig;
-            const uint16_t* b1p = b0p + 2 * KS;
-            mma_bf16_16816(c0, af[ks][0], af[ks][1], af[ks][2], af[ks][3], *reinterpret_cast<const uint32_t*>(b0p),
-                           *reinterpret_cast<const uint32_t*>(b0p + 8));
-            mma_bf16_16816(c1, af[ks][0], af[ks][1], af[ks][2], af[ks][3], *reinterpret_cast<const uint32_t*>(b1p),
-                           *reinterpret_cast<const uint32_t*>(b1p + 8));
-        }
-        float a0[4] = {c0[0], c0[1], c1[0], c1[1]}, a1[4] = {c0[2], c0[3], c1[2], c1[3]};      // rows r0, r1; columns 16 q + 4 tig + k
-        // codes: one word = this lane's four columns of a row
-        {
+        for (int g2 = 0; g2 < 2; ++g2) {
+            const int q = 2 * qp + g2;
+            float c0[4] = {0.f, 0.f, 0.f, 0.f}, c1[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+            for (int ks = 0; ks < KT / 16; ++ks) {
+                const uint16_t* b0p = Bop + (16 * q + cn) * KS + 16 * ks + 2 * tig;
+                const uint16_t* b1p = b0p + 2 * KS;
+                mma_bf16_16816(c0, af[ks][0], af[ks][1], af[ks][2], af[ks][3], *reinterpret_cast<const uint32_t*>(b0p),
+                               *reinterpret_cast<const uint32_t*>(b0p + 8));
+                mma_bf16_16816(c1, af[ks][0], af[ks][1], af[ks][2], af[ks][3], *reinterpret_cast<const uint32_t*>(b1p),
+                               *reinterpret_cast<const uint32_t*>(b1p + 8));
+            }
+            // codes: one word = this lane's four columns of a row
             const float4 sk4 = *reinterpret_cast<const float4*>(skq + 16 * q + 4 * tig);
             float f[4], g[4];
             s8x4_to_f4(cw[r0 * 32 + 4 * q + tig], f[0], f[1], f[2], f[3]);
             s8x4_to_f4(cw[r1 * 32 + 4 * q + tig], g[0], g[1], g[2], g[3]);
             const float skl[4] = {sk4.x, sk4.y, sk4.z, sk4.w};
+            const float cc0[4] = {c0[0], c0[1], c1[0], c1[1]}, cc1[4] = {c0[2], c0[3], c1[2], c1[3]};
 #pragma unroll
             for (int k = 0; k < 4; ++k) {
-                a0[k] = fmaf(f[k] * skl[k], sv0, a0[k]);
-                a1[k] = fmaf(g[k] * skl[k], sv1, a1[k]);
+                a0[g2][k] = fmaf(f[k] * skl[k], sv0, cc0[k]);
+                a1[g2][k] = fmaf(g[k] * skl[k], sv1, cc1[k]);
             }
         }
         // live window entries
-        for (int j = 0; j < h; ++j) {
-            const float wj = ws[j];
-            const uint16_t* urow = reinterpret_cast<const uint16_t*>(Ub2 + j * 64);
-            const float u0 = bf16_to_f(urow[r0]) * wj, u1 = bf16_to_f(urow[r1]) * wj;
-            float kk[4];
-            if (kda) {
-                const float4 ka = *reinterpret_cast<const float4*>(Kf + j * 128 + 16 * q + 4 * tig);
-                kk[0] = ka.x; kk[1] = ka.y; kk[2] = ka.z; kk[3] = ka.w;
-            } else {
-                const uint2 ka = *reinterpret_cast<const uint2*>(Kb2 + j * 64 + 8 * q + 2 * tig);
-                const float2 k01 = bf16x2_to_f2(ka.x), k23 = bf16x2_to_f2(ka.y);
-                kk[0] = k01.x; kk[1] = k01.y; kk[2] = k23.x; kk[3] = k23.y;
-            }
+        if (kda) {
+            for (int j = 0; j < h; ++j) {
+                const float wj = ws[j];
+                const uint16_t* urow = reinterpret_cast<const uint16_t*>(Ub2 + j * 64);
+                const float u0 = bf16_to_f(urow[r0]) * wj, u1 = bf16_to_f(urow[r1]) * wj;
 #pragma unroll
-            for (int k = 0; k < 4; ++k) {
-                a0[k] = fmaf(u0, kk[k], a0[k]);
-                a1[k] = fmaf(u1, kk[k], a1[k]);
+                for (int g2 = 0; g2 < 2; ++g2) {
+                    const float4 ka = *reinterpret_cast<const float4*>(Kf + j * 128 + 16 * (2 * qp + g2) + 4 * tig);
+                    const float kk[4] = {ka.x, ka.y, ka.z, ka.w};
+#pragma unroll
+                    for (int k = 0; k < 4; ++k) {
+                        a0[g2][k] = fmaf(u0, kk[k], a0[g2][k]);
+                        a1[g2][k] = fmaf(u1, kk[k], a1[g2][k]);
+                    }
+                }
+            }
+        } else {
+            // GDN: sum_j (w_j u_j[v]) k_j[c] on the tensor cores, 16 entries per step.  A = the values, read transposed from their
+            // rows ([j][v] -> rows v, K index j), scaled by w_j in registers and split into a bf16 head and remainder (the keys
+            // are exact in bf16); B = the keys, read transposed from their column-permuted rows.
+            for (int j0 = 0; j0 < h; j0 += 16) {
+                uint32_t au[4];
+                ldmatrix_x4_trans(au, Us + (j0 + (lane & 7) + ((lane >> 4) << 3)) * WST + 16 * warp + (((lane >> 3) & 1) << 3));
+                const float2 w01 = *reinterpret_cast<const float2*>(ws + j0 + 2 * tig), w89 = *reinterpret_cast<const float2*>(ws + j0 + 8 + 2 * tig);
+                uint32_t ah[4], al[4];
+#pragma unroll
+                for (int i = 0; i < 4; ++i) {                // au[0], au[1]: entries j0 + 2 tig, + 1; au[2], au[3]: j0 + 8 + 2 tig, + 1
+                    const float2 wv = i < 2 ? w01 : w89;
+                    const float2 uv = bf16x2_to_f2(au[i]);
+                    const float x0 = uv.x * wv.x, x1 = uv.y * wv.y;
+                    ah[i] = f2_to_bf16x2(x0, x1);
+                    const float2 hv2 = bf16x2_to_f2(ah[i]);
+                    al[i] = f2_to_bf16x2(x0 - hv2.x, x1 - hv2.y);
+                }
+#pragma unroll
+                for (int g2 = 0; g2 < 2; ++g2) {
+                    uint32_t bk[4];                          // keys of the group's two n-tiles: (tile 0: rows j0.., j0 + 8..), (tile 1: ..)
+                    ldmatrix_x4_trans(bk, Ks + (j0 + (lane & 7) + (((lane >> 3) & 1) << 3)) * WST + 16 * (2 * qp + g2) + ((lane >> 4) << 3));
+                    float c0[4] = {a0[g2][0], a0[g2][1], a1[g2][0], a1[g2][1]}, c1[4] = {a0[g2][2], a0[g2][3], a1[g2][2], a1[g2][3]};
+                    mma_bf16_16816(c0, ah[0], ah[1], ah[2], ah[3], bk[0], bk[1]);
+                    mma_bf16_16816(c0, al[0], al[1], al[2], al[3], bk[0], bk[1]);
+                    mma_bf16_16816(c1, ah[0], ah[1], ah[2], ah[3], bk[2], bk[3]);
+                    mma_bf16_16816(c1, al[0], al[1], al[2], al[3], bk[2], bk[3]);
+                    a0[g2][0] = c0[0]; a0[g2][1] = c0[1]; a1[g2][0] = c0[2]; a1[g2][1] = c0[3];
+                    a0[g2][2] = c1[0]; a0[g2][3] = c1[1]; a1[g2][2] = c1[2]; a1[g2][3] = c1[3];
+                }
             }
         }
-        *reinterpret_cast<float4*>(out + r0 * KD + 16 * q + 4 * tig) = make_float4(a0[0], a0[1], a0[2], a0[3]);
-        *reinterpret_cast<float4*>(out + r1 * KD + 16 * q + 4 * tig) = make_float4(a1[0], a1[1], a1[2], a1[3]);
+#pragma unroll
+        for (int g2 = 0; g2 < 2; ++g2) {
+            const int q = 2 * qp + g2;
+            *reinterpret_cast<float4*>(out + r0 * KD + 16 * q + 4 * tig) = make_float4(a0[g2][0], a0[g2][1], a0[g2][2], a0[g2][3]);
+            *reinterpret_cast<float4*>(out + r1 * KD + 16 * q + 4 * tig) = make_float4(a1[g2][0], a1[g2][1], a1[g2][2], a1[g2][3]);
+        }
     }
     if (!kda) {
         for (int j = tid; j < d.L; j += NT_LA) Wbuf[sh * d.L + j] = 0.f;
@@ -396,7 +453,8 @@ extern "C" int lq_dequant(const lq_dims* d, void* ssm, const void* Kbuf, const v
     if (N == 0) return LQ_OK;
     // codes, folded scales, factors, weights, window rows (bf16; KDA keys fp32 because they carry the decay)
     const int kt = (3 * d->R + 15) / 16 * 16 + 8;               // operand row of the rank-R product, bf16 elements
-    const size_t smem = sizeof(float) * (4096 + 2 * 128 + 64 + (kda ? d->L * 128 : d->L * 64) + d->L * 64) + size_t(2) * 128 * kt * 2;
+    const size_t win = kda ? sizeof(float) * (d->L * 128 + d->L * 64) : size_t(2) * ((d->L + 15) & ~15) * 136 * 2;
+    const size_t smem = sizeof(float) * (4096 + 2 * 128 + 64) + win + size_t(2) * 128 * kt * 2;
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     dim3 grid(unsigned(N) * d->HV), block(NT_LA);
     if (d->R == 4) {
