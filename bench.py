@@ -718,6 +718,18 @@ def run_b200(args, wl):
                            "isolated_quantize_outlier_states": outlier_quantize(ly2, peak)}
             del ly2
             torch.cuda.empty_cache()
+            # the same layer at twice the batch: the launch is twice as long, filling and draining its pipeline weigh half as much
+            B3 = 2 * other["B"]
+            ly3 = Layer(other, B3, device, seed=310, host_io=False)
+            for t in range(3):
+                ly3.decode_resident(t)
+            ly3.to_lockstep()
+            dt3, done3, _ = measure_staggered(ly3, other["L"], 0.15)
+            v3 = B3 * other["HV"] * done3 / dt3
+            extras[key]["at_twice_the_batch"] = {"batch": B3, "ms_per_step": 1e3 * dt3 / done3, "value": v3,
+                                                 "frac_of_measured_hbm": v3 * am2 / 1e9 / peak}
+            del ly3
+            torch.cuda.empty_cache()
             sweep = []
             for Bs in (1, 8, 32, 128, 256):
                 lys = Layer(wl, Bs, device, seed=400 + Bs, host_io=False)
