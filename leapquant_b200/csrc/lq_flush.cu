@@ -345,7 +345,7 @@ __device__ __forceinline__ void cholqr_pass_team(float (&x)[R], float* __restric
 }
 
 // Arguments of the flush of one head (plain pointers: the fused decode kernel flushes heads whose window rows it -- or, with
-// the shared work list, ANOTHER CTA of the same launch -- wrote a moment before: none of them may be read through the
+// the mailboxes, ANOTHER CTA of the same launch -- wrote a moment before: none of them may be read through the
 // non-coherent path, and what the step writes (window rows, weights, decay) is read with ld.global.cg, past the L1 of an SM
 // that may hold an older copy of a line it shares with a neighbouring head).
 struct FlushArgs {

@@ -780,7 +780,7 @@ struct FuseTail {
     int iters;
     int teams;                                      // teams of 256 threads that fit in the ring side by side (1 or 2)
     int team_bytes;                                 // shared memory of one team
-    int* work;                                      // shared list of due heads (global scratch, see WL_*) or null: every CTA flushes its own
+    int* work;                                      // mailboxes of due heads (global scratch, see WL_*) or null: every CTA flushes its own
 };
 // Shared mailboxes of the fused flush (global scratch of the caller, all zero between launches).  A serving batch fills the
 // windows of a few rows per step, and the program -> CTA map puts two or three of their heads on some CTAs and none on
@@ -1289,7 +1289,7 @@ __global__ void __launch_bounds__(UT + NG * GT, 1) step_pipelined_kernel(StepPar
 
 // 0 = pipelined, 1 = direct, 2 = one warp per program (GDN; KDA falls back to the pipelined driver)
 static std::atomic<int> g_step_impl{0};
-// fewest (row, head) programs of a decode call for which the shared work list is used; -1 = sixteen per SM
+// fewest (row, head) programs of a decode call for which the mailboxes are used; -1 = sixteen per SM
 static std::atomic<int> g_work_list_min{-1};
 
 // fuse != nullptr: the pipelined driver also flushes, in the same launch, the heads whose window it fills (Q0, iters from

@@ -38,7 +38,7 @@ def _launch(fn, what, dev_tensor, *args):
 
 
 def _work(work):
-    """(pointer, bytes) of the optional shared work list of the fused decode (an int32 tensor, all zero), or (None, 0)."""
+    """(pointer, bytes) of the optional mailbox scratch of the fused decode (an int32 tensor, zeroed once), or (None, 0)."""
     if work is None:
         return None, 0
     return _lib.ptr(work), work.numel() * work.element_size()

@@ -60,7 +60,7 @@ def test_argument_errors_are_codes_not_crashes():
     assert L.lq_gdn_decode(*dec, one, -1, None, 0, None) == -4                                       # negative iters
     assert L.lq_gdn_decode(good, mis, *dec[2:], one, 1, None, 0, None) == -3                         # misaligned state
     assert L.lq_gdn_decode(*dec[:14], 0, 0.0, one, 1, None, 0, None) == 0                            # N == 0
-    assert L.lq_gdn_decode(*dec, one, 1, one, 16, None) == -4                                        # work list too small for the call
+    assert L.lq_gdn_decode(*dec, one, 1, one, 16, None) == -4                                        # mailbox scratch too small
     assert L.lq_decode_work_bytes(8, 4) == 4 * (16 + 4 * 1024)
     assert L.lq_kda_decode(good, one, one, one, one, one, None, one, one, one, one, one, one, one, one, 1, 0.0, 0.0, one, 1,
                            None, 0, None) == -1                                                      # KDA needs Gbuf

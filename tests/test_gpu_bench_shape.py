@@ -119,8 +119,8 @@ def all_windows_one_short(kda, L, R, H, HV, seed):
 @pytest.mark.parametrize("kda,L,R,H,HV", CONFIGS)
 def test_decode_every_window_fills(kda, L, R, H, HV, work_list):
     """(ii) One decode call in which all 1 280 windows fill: every CTA of the fused kernel flushes eight or nine heads, each
-    team four or five, one after the other in the same shared memory (or, sharing one list, its first head and then pairs
-    and single heads by ticket).  Bit-identical to the step kernel followed by the flush kernel."""
+    team four or five, one after the other in the same shared memory (with the mailboxes too: a CTA that filled four or more
+    windows keeps them all).  Bit-identical to the step kernel followed by the flush kernel."""
     cpu, idx, (mixed, a, b_, A_log, dtb) = all_windows_one_short(kda, L, R, H, HV, 21)
     gpu_f, gpu_s = GpuSide(cpu), GpuSide(cpu)
     gpu_s.st.fused = False
