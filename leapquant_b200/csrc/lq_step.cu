@@ -974,6 +974,7 @@ __global__ void __launch_bounds__(UT + NG * GT, 1) step_pipelined_kernel(StepPar
                 if (which == k) { o_fix = uint32_t(m0[k]); o_h = uint32_t(m1[k] - m0[k]); }
             __syncwarp();
         }
+        const uint64_t keep_policy = l2_policy_evict_last();
         for (int i = 0; i < nit; ++i) {
             const int dsc = i % ND;
             if (!warp_wait_bounded(ready + dsc, uint32_t(i / ND) & 1u, lane)) {
@@ -992,7 +993,12 @@ __global__ void __launch_bounds__(UT + NG * GT, 1) step_pipelined_kernel(StepPar
                 const char* src = c_base + uint64_t(uint32_t(sc.slot)) * c_slot + uint64_t(uint32_t(sc.hv)) * c_hv +
                                   uint64_t(uint32_t(sc.n)) * c_n + uint64_t(hk) * c_hk;
                 const uint32_t bytes = b_fix + uint32_t(sc.h) * b_h;
-                if (bytes) bulk_g2s(st + o_fix + uint32_t(sc.h) * o_h, src, bytes, full + dsc);
+                // a program that fills its window is followed, at the end of this launch, by the flush of the same head, which
+                // reads the same checkpoint and window rows again: its copies ask L2 to keep those lines
+                if (bytes) {
+                    if (FUSE && sc.h + 1 == L) bulk_g2s_hint(st + o_fix + uint32_t(sc.h) * o_h, src, bytes, full + dsc, keep_policy);
+                    else bulk_g2s(st + o_fix + uint32_t(sc.h) * o_h, src, bytes, full + dsc);
+                }
             } else if (lane == 0) {
                 // nothing to copy (padding row, null slot or full window): this warp completes the phase itself.  Doing it here
                 // and not in the producer keeps this warp inside the full -> normed -> empty chain for every program, so the
