@@ -201,3 +201,46 @@ def test_shared_work_list_staggered_fill(kda, L, R, H, HV):
         assert torch.equal(bits(arms[0][0]), bits(ssm))
     torch.cuda.synchronize()
     assert _lib.device_status() == 0
+
+
+@pytest.mark.parametrize("kda,L,R,H,HV,N", [pytest.param(False, 16, 4, 16, 32, 200, id="gdn_L16"), pytest.param(True, 8, 8, 32, 32, 300, id="kda_L8")])
+def test_mailboxes_with_random_batches(kda, L, R, H, HV, N):
+    """(v) Short windows and a random 90 % of the rows in every call: the number of heads that fill per step, and the CTAs they
+    land on, change from call to call.  Over twenty windows the decode with mailboxes and the decode in which every CTA
+    flushes its own heads stay bit-identical, the mailboxes are empty after every call and no wait runs out."""
+    from leapquant_b200 import _lib
+    from leapquant_b200.state import LeapQuantState
+    NS = N + 1
+    g = torch.Generator(device="cuda").manual_seed(51)
+    base = torch.randn(NS, HV, V, K, device="cuda", generator=g) * 0.5
+    idx = torch.arange(1, N + 1, dtype=torch.int32, device="cuda")
+    arms = []
+    for name in ("mailboxes", "own"):
+        ssm = base.clone()
+        st = LeapQuantState(ssm, H, kda=kda, gate_lower_bound=-5.0 if kda else 0.0, L=L, R=R)
+        st.quantize(ssm, idx)
+        if name == "own":
+            st.work = None
+        arms.append((ssm, st, torch.zeros(N, HV, V, dtype=torch.bfloat16, device="cuda")))
+    T = 4 * L
+    mixed, a, b_, A_log, dtb = step_inputs(N, H, HV, T, 52, kda, gate_shift=3.0)
+    mixed, a, b_, A_log, dtb = mixed.cuda(), a.cuda(), b_.cuda(), A_log.cuda(), dtb.cuda()
+    bits = lambda x: x.view(torch.int32) if x.dtype == torch.float32 else x.view(torch.int16) if x.element_size() == 2 else x
+    gen = torch.Generator().manual_seed(53)
+    for s in range(20 * L):
+        t = s % T
+        rows = torch.nonzero(torch.rand(N, generator=gen) < 0.9).flatten().cuda()
+        n = rows.numel()
+        for ssm, st, o in arms:
+            st.decode(ssm, mixed[t][rows].contiguous(), a[t][rows].contiguous(), b_[t][rows].contiguous(), A_log, dtb,
+                      idx[rows].contiguous(), o[:n])
+        if s % 8 == 0:
+            assert torch.equal(bits(arms[0][2][:n]), bits(arms[1][2][:n])), s
+            assert torch.equal(arms[0][1].hcnt, arms[1][1].hcnt), s
+            w = arms[0][1].work
+            assert int(w[0]) == 0 and int(w[2:].abs().max()) == 0, s
+    for name in ("Kbuf", "Ubuf", "Wbuf", "Pbuf") + (("Gbuf",) if kda else ()):
+        assert torch.equal(bits(getattr(arms[0][1], name)), bits(getattr(arms[1][1], name))), name
+    assert torch.equal(bits(arms[0][0]), bits(arms[1][0]))
+    torch.cuda.synchronize()
+    assert _lib.device_status() == 0
