@@ -1202,6 +1202,8 @@ __global__ void __launch_bounds__(UT + NG * GT, 1) step_pipelined_kernel(StepPar
                             const int x = atomicExch(box + bid * WL_SLOTS + reclaim, 0);
                             if (x > 0) q = x - 1;
                         }
+                    } else {                                     // a wait ran out somewhere in this CTA (the status word says so): what it
+                        for (; reclaim < npub; ++reclaim) atomicExch(box + bid * WL_SLOTS + reclaim, 0);       // posted must not outlive the launch
                     }
                     s_pop[0] = q;
                 }
