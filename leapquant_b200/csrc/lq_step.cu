@@ -1171,17 +1171,20 @@ __global__ void __launch_bounds__(UT + NG * GT, 1) step_pipelined_kernel(StepPar
         const bool keep_all = wl == nullptr || ndl >= 4 || ndl - 1 > WL_SLOTS;
         const int npub = keep_all ? 0 : (ndl > 1 ? ndl - 1 : 0); // heads left in this CTA's mailbox
         int* const box = wl + WL_BOX;
+        if (tid == 0) { s_pop[2] = 0; s_pop[3] = 0; }            // [2]: occupied slots found by a scan, [3]: 1 = nothing was posted in this launch
         if (wl != nullptr) {
             if (npub > 0) __threadfence();                       // the step's stores of the posted heads come before their entries
             __syncthreads();
             if (tid == 0) {
                 for (int i = 0; i < npub; ++i) st_volatile_i32(box + bid * WL_SLOTS + i, dl[1 + i] + 1);
-                __threadfence();
-                const int reported = atomicAdd(wl + WL_DONE, 1);
-                if (reported == grid - 1) {                      // the last CTA to report closes the launch's count at once: the others
-                    st_volatile_i32(wl + WL_DONE, 0);            // learn from the generation that no more heads will be posted.  (This
-                    __threadfence();                             // thread reaches the first barrier of its flush a round trip late;
-                    atomicAdd(wl + WL_GEN, 1);                   // the flush starts with global loads that take as long.)
+                if (npub > 0) __threadfence();
+                // one word counts the reports (low 16 bits) and the heads posted (above them)
+                const int old = atomicAdd(wl + WL_DONE, 1 + (npub << 16));
+                if ((old & 0xffff) == grid - 1) {                // the last CTA to report closes the launch's count at once: the others
+                    const int any = ((old >> 16) + npub) > 0;    // learn from the generation that no more heads will be posted, and from
+                    st_volatile_i32(wl + WL_DONE, 0);            // its low bit whether any was.  (This thread reaches the first barrier
+                    st_volatile_i32(wl + WL_GEN, (gen0 & ~1) + 2 + any);      // of its flush a round trip late; the flush starts with
+                    if (!any) s_pop[3] = 1;                      // global loads that take as long.)
                 }
             }
         }
@@ -1209,17 +1212,13 @@ __global__ void __launch_bounds__(UT + NG * GT, 1) step_pipelined_kernel(StepPar
                 }
                 __syncthreads();
                 int q = s_pop[0];
-                if (q < 0 && *abortf == 0) {                     // nothing (left) of its own: help the others
+                if (q < 0 && *abortf == 0 && s_pop[3] == 0) {    // nothing (left) of its own: help the others
                     // One trip = the generation and every mailbox slot, read side by side.  A scan that races with the last
                     // postings may miss one: its owner flushes it.  Occupied slots go to a short list and the CTA tries the one
                     // its number picks, so that helpers spread over the entries.
                     for (uint32_t it = 0; it < WL_HELP_POLLS; ++it) {
-                        __syncthreads();                         // (s_pop of the previous trip has been read)
-                        if (tid == 0) {
-                            s_pop[2] = 0;
-                            s_pop[1] = ld_volatile_i32(wl + WL_GEN);
-                        }
-                        __syncthreads();
+                        int g = 0;
+                        if (tid == 0) g = ld_volatile_i32(wl + WL_GEN);
                         for (int i = tid; i < total; i += UT + NG * GT)
                             if (ld_volatile_i32(box + i) != 0) {
                                 const int pos = atomicAdd(&s_pop[2], 1);
@@ -1227,16 +1226,18 @@ __global__ void __launch_bounds__(UT + NG * GT, 1) step_pipelined_kernel(StepPar
                             }
                         __syncthreads();
                         if (tid == 0) {
-                            int got = -1;                        // -1: nothing yet, -2: lost the race for an entry, -3: launch over
+                            int got = -1;                        // -1: nothing yet, -2: lost the race for an entry, -3: nothing more to come
                             const int nfound = min(s_pop[2], 24);
                             if (nfound > 0) {
                                 const int x = atomicExch(box + s_list[(bid * 7 + int(it)) % nfound], 0);
                                 got = x > 0 ? x - 1 : -2;
                                 if (x > 0) __threadfence();      // the head's data is read after its entry
-                            } else if (s_pop[1] != gen0) {
+                            } else if (g != gen0) {
                                 got = -3;
                             }
+                            if (got < 0 && g != gen0 && (g & 1) == 0) got = -3;         // the launch closed with nothing posted
                             s_pop[0] = got;
+                            s_pop[2] = 0;                        // (for the next scan)
                         }
                         __syncthreads();
                         const int got = s_pop[0];
