@@ -53,17 +53,19 @@ __device__ __forceinline__ void quant_rows_div(const float* __restrict__ E, cons
         const float rv127 = QMAX / svv;
 #pragma unroll
         for (int i = 0; i < 4; ++i) {
+            // rint() by adding 1.5 * 2^23: the sum's low mantissa byte is the code in two's complement.  |y| <= 127 (1 + 3e-7) by
+            // construction of Sv, so the reference's clamp to [-127, 127] never acts and is not evaluated.
             uint32_t b[4];
 #pragma unroll
             for (int k = 0; k < 4; ++k) {
                 const float y = a[4 * i + k] * rv127;
-                float c = rintf(y);
+                float t = y + 12582912.0f;
+                const float c = t - 12582912.0f;
                 if (fabsf(fabsf(y - c) - 0.5f) < 1e-3f)                        // on a rounding boundary: the exact expression decides
-                    c = rintf(e[4 * i + k] / (sk[i * 32 + l8 * 4 + k] * svv) * QMAX);
-                c = fminf(fmaxf(c, -QMAX), QMAX);
-                b[k] = uint32_t(int(c)) & 0xffu;
+                    t = e[4 * i + k] / (sk[i * 32 + l8 * 4 + k] * svv) * QMAX + 12582912.0f;
+                b[k] = __float_as_uint(t);
             }
-            codes[row * 32 + i * 8 + l8] = b[0] | (b[1] << 8) | (b[2] << 16) | (b[3] << 24);
+            codes[row * 32 + i * 8 + l8] = __byte_perm(__byte_perm(b[0], b[1], 0x0040), __byte_perm(b[2], b[3], 0x0040), 0x5410);
         }
     }
 }
