@@ -205,8 +205,8 @@ dequant_kernel(lq_dims d, char* __restrict__ ssm, const uint16_t* __restrict__ K
     uint16_t* Aop = reinterpret_cast<uint16_t*>(svp + 128);   // [128 rows v][KS]: Qp head | Qp remainder | Qp head | 0
     uint16_t* Bop = Aop + 128 * KS;                       // [128 cols c][KS]: Uc head | Uc head | Uc remainder | 0
     float* ws = reinterpret_cast<float*>(Bop + 128 * KS); // [64] window weights
-    float* Kf = ws + 64;                                  // KDA: [L][128] decayed keys (fp32), then the values [L][64] bf16 pairs
-                                                          // GDN: keys [Lp][WST] bf16 (columns permuted), then values [Lp][WST] bf16
+    float* Kf = ws + 64;                                  // keys [Lp][WST] bf16 (columns permuted), values [Lp][WST] bf16; KDA: the keys are
+                                                          // the head of k_j D_j, followed by its remainder [Lp][WST] and the raw keys [Lp][128]
     const int tid = threadIdx.x;
     const int n = blockIdx.x / d.HV, hv = blockIdx.x % d.HV;
     const int slot = idx[n];
@@ -218,9 +218,10 @@ dequant_kernel(lq_dims d, char* __restrict__ ssm, const uint16_t* __restrict__ K
     constexpr int WST = 136;                              // GDN window rows in shared memory: 128 bf16 + 16 bytes, so that the
                                                           // eight rows of an ldmatrix tile fall into different bank groups
     const int Lp = (d.L + 15) & ~15;
-    uint16_t* Ks = reinterpret_cast<uint16_t*>(Kf);       // GDN keys: within every 16 columns c -> 8 (c % 4 / 2) + 2 (c / 4) + c % 2
-    uint16_t* Us = Ks + Lp * WST;                         // GDN values as stored
-    uint32_t* Ub2 = reinterpret_cast<uint32_t*>(Kf + d.L * 128);                  // KDA values as stored (bf16 pairs) [L][64]
+    uint16_t* Ks = reinterpret_cast<uint16_t*>(Kf);       // keys: within every 16 columns c -> 8 (c % 4 / 2) + 2 (c / 4) + c % 2
+    uint16_t* Us = Ks + Lp * WST;                         // values as stored
+    uint16_t* Kl = Us + Lp * WST;                         // KDA: remainder of k_j D_j, same layout as Ks
+    uint16_t* Kraw = Kl + Lp * WST;                       // KDA: keys as stored [Lp][128], read by the scan below
 
     for (int i = tid; i < 4096 / 4; i += NT_LA)
         reinterpret_cast<uint4*>(cw)[i] = reinterpret_cast<const uint4*>(base + CK_CODES)[i];
@@ -244,19 +245,15 @@ dequant_kernel(lq_dims d, char* __restrict__ ssm, const uint16_t* __restrict__ K
     {
         const uint4* kb = reinterpret_cast<const uint4*>(Kbuf + sh * d.L * KD);
         const uint4* ub = reinterpret_cast<const uint4*>(Ubuf + sh * d.L * VD);
-        const int hp = kda ? h : ((h + 15) & ~15);           // GDN: whole k-steps of 16 rows, the rows past h zero
+        const int hp = (h + 15) & ~15;                       // whole k-steps of 16 rows, the rows past h zero
         for (int i = tid; i < hp * 16; i += NT_LA) {
             const int j = i >> 4, c8 = i & 15;                // row, 16-byte chunk (8 columns) of the row
             const uint4 z = make_uint4(0u, 0u, 0u, 0u);
             const uint4 uv = j < h ? ub[i] : z, kv = j < h ? kb[i] : z;
+            *reinterpret_cast<uint4*>(Us + j * WST + 8 * c8) = uv;
             if (kda) {
-                reinterpret_cast<uint4*>(Ub2)[i] = uv;
-                float4* kp = reinterpret_cast<float4*>(Kf + i * 8);
-                const float2 a0 = bf16x2_to_f2(kv.x), a1 = bf16x2_to_f2(kv.y), a2 = bf16x2_to_f2(kv.z), a3 = bf16x2_to_f2(kv.w);
-                kp[0] = make_float4(a0.x, a0.y, a1.x, a1.y);
-                kp[1] = make_float4(a2.x, a2.y, a3.x, a3.y);
+                reinterpret_cast<uint4*>(Kraw)[i] = kv;
             } else {
-                *reinterpret_cast<uint4*>(Us + j * WST + 8 * c8) = uv;
                 // the chunk holds columns 4 t .. 4 t + 7 of a group of 16 (t = 0 or 2): pairs (4t, 4t+1), (4t+4, 4t+5) go to the
                 // first n-tile of the group at 2 t, 2 t + 2, pairs (4t+2, 4t+3), (4t+6, 4t+7) to the second at 8 + 2 t, 8 + 2 t + 2
                 uint16_t* kd = Ks + j * WST + 16 * (c8 >> 1) + 4 * (c8 & 1);
@@ -266,10 +263,16 @@ dequant_kernel(lq_dims d, char* __restrict__ ssm, const uint16_t* __restrict__ K
         }
     }
     __syncthreads();
-    if (kda && tid < 128) {                    // D_j = prod_{j < i < h} e_i, backward running product per column
-        float dcur = 1.f;
+    if (kda && tid < 128) {                    // D_j = prod_{j < i < h} e_i, backward running product per column; k_j D_j as a
+        float dcur = 1.f;                      // bf16 head and remainder at the column's place in the permuted rows
+        const int hp = (h + 15) & ~15;
+        const int cp = (tid & ~15) + 8 * ((tid & 3) >> 1) + 2 * ((tid & 15) >> 2) + (tid & 1);
+        for (int j = hp - 1; j >= h; --j) { Ks[j * WST + cp] = 0; Kl[j * WST + cp] = 0; }
         for (int j = h - 1; j >= 0; --j) {
-            Kf[j * 128 + tid] *= dcur;
+            const float kd = bf16_to_f(Kraw[j * 128 + tid]) * dcur;
+            const uint16_t kh = f_to_bf16(kd);
+            Ks[j * WST + cp] = kh;
+            Kl[j * WST + cp] = f_to_bf16(kd - bf16_to_f(kh));
             dcur *= f16_to_f(Gbuf[(sh * d.L + j) * KD + tid]);
         }
     }
@@ -320,53 +323,42 @@ dequant_kernel(lq_dims d, char* __restrict__ ssm, const uint16_t* __restrict__ K
                 a1[g2][k] = fmaf(g[k] * skl[k], sv1, cc1[k]);
             }
         }
-        // live window entries
-        if (kda) {
-            for (int j = 0; j < h; ++j) {
-                const float wj = ws[j];
-                const uint16_t* urow = reinterpret_cast<const uint16_t*>(Ub2 + j * 64);
-                const float u0 = bf16_to_f(urow[r0]) * wj, u1 = bf16_to_f(urow[r1]) * wj;
+        // live window entries: sum_j (w_j u_j[v]) (k_j[c] D_j[c]) on the tensor cores, 16 entries per step.  A = the values, read
+        // transposed from their rows ([j][v] -> rows v, K index j), scaled by w_j in registers and split into a bf16 head and
+        // remainder; B = the keys, read transposed from their column-permuted rows (GDN: exact in bf16; KDA: head and remainder
+        // of the decayed keys, three products).
+        for (int j0 = 0; j0 < h; j0 += 16) {
+            uint32_t au[4];
+            ldmatrix_x4_trans(au, Us + (j0 + (lane & 7) + ((lane >> 4) << 3)) * WST + 16 * warp + (((lane >> 3) & 1) << 3));
+            const float2 w01 = *reinterpret_cast<const float2*>(ws + j0 + 2 * tig), w89 = *reinterpret_cast<const float2*>(ws + j0 + 8 + 2 * tig);
+            uint32_t ah[4], al[4];
 #pragma unroll
-                for (int g2 = 0; g2 < 2; ++g2) {
-                    const float4 ka = *reinterpret_cast<const float4*>(Kf + j * 128 + 16 * (2 * qp + g2) + 4 * tig);
-                    const float kk[4] = {ka.x, ka.y, ka.z, ka.w};
-#pragma unroll
-                    for (int k = 0; k < 4; ++k) {
-                        a0[g2][k] = fmaf(u0, kk[k], a0[g2][k]);
-                        a1[g2][k] = fmaf(u1, kk[k], a1[g2][k]);
-                    }
-                }
+            for (int i = 0; i < 4; ++i) {                    // au[0], au[1]: entries j0 + 2 tig, + 1; au[2], au[3]: j0 + 8 + 2 tig, + 1
+                const float2 wv = i < 2 ? w01 : w89;
+                const float2 uv = bf16x2_to_f2(au[i]);
+                const float x0 = uv.x * wv.x, x1 = uv.y * wv.y;
+                ah[i] = f2_to_bf16x2(x0, x1);
+                const float2 hv2 = bf16x2_to_f2(ah[i]);
+                al[i] = f2_to_bf16x2(x0 - hv2.x, x1 - hv2.y);
             }
-        } else {
-            // GDN: sum_j (w_j u_j[v]) k_j[c] on the tensor cores, 16 entries per step.  A = the values, read transposed from their
-            // rows ([j][v] -> rows v, K index j), scaled by w_j in registers and split into a bf16 head and remainder (the keys
-            // are exact in bf16); B = the keys, read transposed from their column-permuted rows.
-            for (int j0 = 0; j0 < h; j0 += 16) {
-                uint32_t au[4];
-                ldmatrix_x4_trans(au, Us + (j0 + (lane & 7) + ((lane >> 4) << 3)) * WST + 16 * warp + (((lane >> 3) & 1) << 3));
-                const float2 w01 = *reinterpret_cast<const float2*>(ws + j0 + 2 * tig), w89 = *reinterpret_cast<const float2*>(ws + j0 + 8 + 2 * tig);
-                uint32_t ah[4], al[4];
 #pragma unroll
-                for (int i = 0; i < 4; ++i) {                // au[0], au[1]: entries j0 + 2 tig, + 1; au[2], au[3]: j0 + 8 + 2 tig, + 1
-                    const float2 wv = i < 2 ? w01 : w89;
-                    const float2 uv = bf16x2_to_f2(au[i]);
-                    const float x0 = uv.x * wv.x, x1 = uv.y * wv.y;
-                    ah[i] = f2_to_bf16x2(x0, x1);
-                    const float2 hv2 = bf16x2_to_f2(ah[i]);
-                    al[i] = f2_to_bf16x2(x0 - hv2.x, x1 - hv2.y);
+            for (int g2 = 0; g2 < 2; ++g2) {
+                const int koff = (j0 + (lane & 7) + (((lane >> 3) & 1) << 3)) * WST + 16 * (2 * qp + g2) + ((lane >> 4) << 3);
+                uint32_t bk[4];                              // keys of the group's two n-tiles: (tile 0: rows j0.., j0 + 8..), (tile 1: ..)
+                ldmatrix_x4_trans(bk, Ks + koff);
+                float c0[4] = {a0[g2][0], a0[g2][1], a1[g2][0], a1[g2][1]}, c1[4] = {a0[g2][2], a0[g2][3], a1[g2][2], a1[g2][3]};
+                mma_bf16_16816(c0, ah[0], ah[1], ah[2], ah[3], bk[0], bk[1]);
+                mma_bf16_16816(c0, al[0], al[1], al[2], al[3], bk[0], bk[1]);
+                mma_bf16_16816(c1, ah[0], ah[1], ah[2], ah[3], bk[2], bk[3]);
+                mma_bf16_16816(c1, al[0], al[1], al[2], al[3], bk[2], bk[3]);
+                if (kda) {
+                    uint32_t bl[4];
+                    ldmatrix_x4_trans(bl, Kl + koff);
+                    mma_bf16_16816(c0, ah[0], ah[1], ah[2], ah[3], bl[0], bl[1]);
+                    mma_bf16_16816(c1, ah[0], ah[1], ah[2], ah[3], bl[2], bl[3]);
                 }
-#pragma unroll
-                for (int g2 = 0; g2 < 2; ++g2) {
-                    uint32_t bk[4];                          // keys of the group's two n-tiles: (tile 0: rows j0.., j0 + 8..), (tile 1: ..)
-                    ldmatrix_x4_trans(bk, Ks + (j0 + (lane & 7) + (((lane >> 3) & 1) << 3)) * WST + 16 * (2 * qp + g2) + ((lane >> 4) << 3));
-                    float c0[4] = {a0[g2][0], a0[g2][1], a1[g2][0], a1[g2][1]}, c1[4] = {a0[g2][2], a0[g2][3], a1[g2][2], a1[g2][3]};
-                    mma_bf16_16816(c0, ah[0], ah[1], ah[2], ah[3], bk[0], bk[1]);
-                    mma_bf16_16816(c0, al[0], al[1], al[2], al[3], bk[0], bk[1]);
-                    mma_bf16_16816(c1, ah[0], ah[1], ah[2], ah[3], bk[2], bk[3]);
-                    mma_bf16_16816(c1, al[0], al[1], al[2], al[3], bk[2], bk[3]);
-                    a0[g2][0] = c0[0]; a0[g2][1] = c0[1]; a1[g2][0] = c0[2]; a1[g2][1] = c0[3];
-                    a0[g2][2] = c1[0]; a0[g2][3] = c1[1]; a1[g2][2] = c1[2]; a1[g2][3] = c1[3];
-                }
+                a0[g2][0] = c0[0]; a0[g2][1] = c0[1]; a1[g2][0] = c0[2]; a1[g2][1] = c0[3];
+                a0[g2][2] = c1[0]; a0[g2][3] = c1[1]; a1[g2][2] = c1[2]; a1[g2][3] = c1[3];
             }
         }
 #pragma unroll
@@ -455,7 +447,7 @@ extern "C" int lq_dequant(const lq_dims* d, void* ssm, const void* Kbuf, const v
     if (N == 0) return LQ_OK;
     // codes, folded scales, factors, weights, window rows (bf16; KDA keys fp32 because they carry the decay)
     const int kt = (3 * d->R + 15) / 16 * 16 + 8;               // operand row of the rank-R product, bf16 elements
-    const size_t win = kda ? sizeof(float) * (d->L * 128 + d->L * 64) : size_t(2) * ((d->L + 15) & ~15) * 136 * 2;
+    const size_t win = size_t((d->L + 15) & ~15) * (kda ? 3 * 136 * 2 + 128 * 2 : 2 * 136 * 2);
     const size_t smem = sizeof(float) * (4096 + 2 * 128 + 64) + win + size_t(2) * 128 * kt * 2;
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     dim3 grid(unsigned(N) * d->HV), block(NT_LA);
