@@ -121,7 +121,7 @@ int lq_kda_decode(const lq_dims* d, void* ssm, void* Kbuf, void* Ubuf, float* Wb
                   int32_t* hcnt, const void* mixed, const void* a, const void* b, const float* A_log,
                   const float* dt_bias, const int32_t* idx, void* o, int32_t N, float scale, float gate_lower_bound,
                   const float* Q0, int32_t iters, void* work, int64_t work_bytes, void* stream);
-/* Bytes of the `work` scratch for calls of up to `rows` live rows with HV value heads. */
+/* Bytes of the `work` scratch: 16 KiB (a mailbox per CTA for launches of up to 1 024 CTAs), whatever `rows` and `HV`. */
 int64_t lq_decode_work_bytes(int32_t rows, int32_t HV);
 
 /* lq_gdn_decode for callers that cannot allocate device memory.  (No counterpart in the reference: its kernels get every

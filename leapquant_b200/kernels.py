@@ -45,7 +45,7 @@ def _work(work):
 
 
 def decode_work_ints(rows, HV):
-    """int32 elements of the `work` tensor the fused decode needs for calls of up to `rows` live rows."""
+    """int32 elements of the `work` tensor of the fused decode (mailboxes of due heads: a fixed 16 KiB, whatever the call)."""
     return int(_lib.lib().lq_decode_work_bytes(int(rows), int(HV))) // 4
 
 
