@@ -439,6 +439,7 @@ def secondary_layer_numbers(layer, peak, reps_step=3):
     for t in range(3):
         layer.decode_resident(t)                                 # a few live entries for the dequantize to fold in
     deq_s, qnt_s = layer.to_lockstep()
+    deq0_s, _ = layer.to_lockstep()                              # windows empty: a slot between two chunks of its prefill
     rt = B * HV * roundtrip_bytes(R)
     out = {"prefill_round_trip": {"dequantize_ms": 1e3 * deq_s, "quantize_ms": 1e3 * qnt_s,
                                   "dequantize_gbs": rt / deq_s / 1e9, "quantize_gbs": rt / qnt_s / 1e9,
@@ -446,8 +447,11 @@ def secondary_layer_numbers(layer, peak, reps_step=3):
                                   "quantize_frac_of_measured_hbm": rt / qnt_s / 1e9 / peak,
                                   "bytes_per_head": roundtrip_bytes(R),
                                   "dequantize_live_windows_ms": 1e3 * live_deq_s,
-                                  "note": "dequantize_ms: windows with 3 entries (right after a prefill); dequantize_live_windows_ms: "
-                                          "the staggered windows of the decode batch (a mixed prefill + decode step), first call"}}
+                                  "dequantize_empty_windows_ms": 1e3 * deq0_s,
+                                  "dequantize_empty_windows_frac_of_measured_hbm": rt / deq0_s / 1e9 / peak,
+                                  "note": "dequantize_ms: windows with 3 entries; dequantize_empty_windows_ms: no live entry (a slot "
+                                          "between two chunks of its prefill); dequantize_live_windows_ms: the staggered windows of "
+                                          "the decode batch (a mixed prefill + decode step), first call"}}
     # lock-step: every head flushes on the same step (the graph is the one captured for the staggered run)
     dt_l, reps_l = replay_timed(layer.graph, 1, 0.1)
     amort = window_bytes_per_head_step(L, R, gqa, kda)
