@@ -509,13 +509,8 @@ dequant_kernel(lq_dims d, char* __restrict__ ssm, const uint16_t* __restrict__ K
 #pragma unroll
         for (int g2 = 0; g2 < 2; ++g2) {
             const int q = 2 * qp + g2;
-#ifdef LQ_DQ_NOSTORE
-            if (a0[g2][0] == 1.2345e38f || a1[g2][3] == 1.2345e38f || a0[g2][1] + a0[g2][2] + a0[g2][3] + a1[g2][0] + a1[g2][1] + a1[g2][2] == 1.2345e38f)
-#endif
-            {
             *reinterpret_cast<float4*>(out + r0 * KD + 16 * q + 4 * tig) = make_float4(a0[g2][0], a0[g2][1], a0[g2][2], a0[g2][3]);
             *reinterpret_cast<float4*>(out + r1 * KD + 16 * q + 4 * tig) = make_float4(a1[g2][0], a1[g2][1], a1[g2][2], a1[g2][3]);
-            }
         }
     }
     __syncwarp();
