@@ -21,7 +21,8 @@ import types
 import pytest
 import torch
 
-REF = os.environ.get("LEAPQUANT_REFERENCE", "/root/reference")
+# a checkout of the reference: LEAPQUANT_REFERENCE, or a directory `reference` beside this repository
+REF = os.environ.get("LEAPQUANT_REFERENCE") or os.path.join(os.path.dirname(os.path.dirname(os.path.dirname(os.path.abspath(__file__)))), "reference")
 HAVE_REF = os.path.exists(os.path.join(REF, "leapquant", "vllm", "gdn.py"))
 NS = types.SimpleNamespace
 
