@@ -51,7 +51,8 @@ def packed(ssm, views, slots):
 def main():
     out = sys.argv[1] if len(sys.argv) > 1 else os.path.join(HERE, "ref_kernels")
     os.makedirs(out, exist_ok=True)
-    ref = os.environ.get("LEAPQUANT_REFERENCE", "/root/reference")
+    # a checkout of the reference: LEAPQUANT_REFERENCE, or a directory `reference` beside this repository
+    ref = os.environ.get("LEAPQUANT_REFERENCE") or os.path.join(os.path.dirname(os.path.dirname(os.path.dirname(HERE))), "reference")
     sys.path.insert(0, ref)
     log = {"reference": ref, "torch": torch.__version__, "device": torch.cuda.get_device_name(0), "kernels": {}}
     try:
