@@ -244,3 +244,55 @@ def test_mailboxes_with_random_batches(kda, L, R, H, HV, N):
     assert torch.equal(bits(arms[0][0]), bits(arms[1][0]))
     torch.cuda.synchronize()
     assert _lib.device_status() == 0
+
+
+@pytest.mark.parametrize("kda,L,R,H,HV", CONFIGS)
+def test_dequantize_many_heads_per_cta(kda, L, R, H, HV):
+    """(vi) The dequantize kernel is persistent: with 10 560 heads every CTA walks 35 or 36 of them, so its two stages are
+    reused many times and the warp that looks ahead fetches a second batch of 32 heads.  Windows of every length (empty,
+    short enough to travel with the stage, longer), padding rows in the batch.  One call over the whole batch gives the bits
+    of calls of eight rows each -- one head per CTA, the shape the oracle tests cover -- and no wait runs out."""
+    from leapquant_b200 import _lib
+    from leapquant_b200.state import LeapQuantState
+    N, NS = 330, 331
+    g = torch.Generator(device="cuda").manual_seed(61)
+    base = torch.randn(NS, HV, V, K, device="cuda", generator=g) * 0.5
+    idx_all = torch.arange(1, N + 1, dtype=torch.int32, device="cuda")
+    st0 = LeapQuantState(base, H, kda=kda, gate_lower_bound=-5.0 if kda else 0.0, L=L, R=R)
+    st0.quantize(base, idx_all)
+    # windows: a third empty, a third with at most 8 entries, the rest anything up to L
+    kind = torch.randint(0, 3, (NS, HV), device="cuda", generator=g)
+    short = torch.randint(1, 9, (NS, HV), device="cuda", generator=g)
+    long_ = torch.randint(1, L + 1, (NS, HV), device="cuda", generator=g)
+    st0.hcnt.copy_(torch.where(kind == 0, torch.zeros_like(short), torch.where(kind == 1, short, long_)).to(torch.int32))
+    st0.Kbuf.copy_((torch.randn(st0.Kbuf.shape, device="cuda", generator=g) * 0.1).to(torch.bfloat16))
+    st0.Ubuf.copy_((torch.randn(st0.Ubuf.shape, device="cuda", generator=g) * 0.5).to(torch.bfloat16))
+    st0.Wbuf.copy_(torch.rand(st0.Wbuf.shape, device="cuda", generator=g))
+    if kda:
+        st0.Pbuf.copy_(-torch.rand(st0.Pbuf.shape, device="cuda", generator=g))
+        st0.Gbuf.copy_((0.9 + 0.1 * torch.rand(st0.Gbuf.shape, device="cuda", generator=g)).to(torch.float16))
+    else:
+        st0.Pbuf.copy_(0.5 + 0.5 * torch.rand(st0.Pbuf.shape, device="cuda", generator=g))
+    names = ("Kbuf", "Ubuf", "Wbuf", "Pbuf", "hcnt") + (("Gbuf",) if kda else ())
+    snap = {n: getattr(st0, n).clone() for n in names}
+    # the batch: every slot once, in a shuffled order, with padding rows (slot 0) in between
+    perm = (torch.randperm(N, generator=torch.Generator().manual_seed(62)) + 1).to(torch.int32)
+    rows = torch.cat([perm[:100], torch.zeros(3, dtype=torch.int32), perm[100:], torch.zeros(1, dtype=torch.int32)]).cuda()
+    results = []
+    for chunk in (rows.numel(), 8):
+        ssm = base.clone()
+        for n in names:
+            getattr(st0, n).copy_(snap[n])
+        for i in range(0, rows.numel(), chunk):
+            st0.dequantize(ssm, rows[i:i + chunk].contiguous())
+        results.append((ssm, {n: getattr(st0, n).clone() for n in names}))
+    torch.cuda.synchronize()
+    assert _lib.device_status() == 0
+    (s_all, b_all), (s_8, b_8) = results
+    assert torch.equal(s_all.view(torch.int32), s_8.view(torch.int32))
+    for n in names:
+        a, b = b_all[n], b_8[n]
+        assert torch.equal(a.view(torch.int16) if a.element_size() == 2 else a.view(torch.int32), b.view(torch.int16) if b.element_size() == 2 else b.view(torch.int32)), n
+    assert not torch.equal(s_all[1:], base[1:])                  # (something was dequantized)
+    if not kda:
+        assert int(b_all["hcnt"][1:].abs().max()) == 0           # the GDN dequantize folds the window in and empties it
