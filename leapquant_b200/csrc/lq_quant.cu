@@ -1,8 +1,9 @@
 // Standalone quantize, in-place dequantize and low-rank factorisation kernels (sm_100a).
 //
-// One CTA of 256 threads per (row, value head); the head's 128 x 128 fp32 tile lives in shared memory for the whole
-// kernel, so the in-place rewrite of the slot (fp32 state <-> packed 8-bit checkpoint) never reads what it has
-// already overwritten.
+// Quantize and low-rank: one CTA of 256 threads per (row, value head), the head's 128 x 128 fp32 tile in shared memory for
+// the whole kernel.  Dequantize: persistent CTAs that walk the heads, each head's checkpoint staged in shared memory.
+// Either way the in-place rewrite of a slot (fp32 state <-> packed 8-bit checkpoint) never reads what it has already
+// overwritten.
 #include "lq_linalg.cuh"
 
 namespace lq {
