@@ -795,6 +795,7 @@ struct FuseTail {
 // A CTA that filled four or more windows is in a call in which every CTA did (windows in phase) and keeps them all.
 constexpr int WL_DONE = 0, WL_GEN = 1, WL_BOX = 16;              // int offsets: reports of this launch, generation, mailboxes
 constexpr int WL_SLOTS = 4;                                      // slots per CTA (at most two are used); entry = head + 1
+constexpr int WL_EARLY = 2;                                      // heads after a CTA's first that are posted (the rest stay with it)
 constexpr int WL_MAX_CTAS = 1024;                                // the scratch is sized for launches of up to this many CTAs
 constexpr int WL_ITEMS = WL_BOX;                                 // (first int after the header)
 constexpr uint32_t WL_HELP_POLLS = 4096;                         // a helper gives up after this many empty scans (about a millisecond)
@@ -1110,6 +1111,24 @@ __global__ void __launch_bounds__(UT + NG * GT, 1) step_pipelined_kernel(StepPar
     const int bar = 1 + g;
     const GroupScratch gs = carve_scratch(scratch0 + g * SCRATCH_BYTES);
     volatile int* gflag = gflag0 + g;
+    // A head whose window is full goes on this CTA's list.  With the mailboxes the second and the third head of the list are
+    // posted at once, while the CTA still has programs to run: a CTA that ends its programs with nothing to flush then finds
+    // them in its first look.  (Called by the whole group; `wrote`: the group has just written the head's new window entry.)
+    auto note_due = [&](int head, bool wrote) {
+        if (ft.work == nullptr) {
+            if (t == 0) dl[atomicAdd(dl_n, 1)] = head;
+            return;
+        }
+        if (wrote) named_bar(bar, GT);                          // every thread's stores to the head are issued
+        if (t == 0) {
+            const int k = atomicAdd(dl_n, 1);
+            dl[k] = head;
+            if (k >= 1 && k <= WL_EARLY) {
+                __threadfence();                                 // the head's data comes before its entry
+                st_volatile_i32(ft.work + WL_BOX + bid * WL_SLOTS + (k - 1), head + 1);
+            }
+        }
+    };
     for (int i = g; i < nit; i += NG) {
         const int dsc = i % ND;
         // one warp polls and publishes the outcome; the other warps sleep at the group barrier
@@ -1129,9 +1148,9 @@ __global__ void __launch_bounds__(UT + NG * GT, 1) step_pipelined_kernel(StepPar
         auto release = [&] { mbar_arrive(empty + dsc); };
         if (prog_live(sc, L)) {
             step_body<R, KDA, CONV>(P, sc, st, lay, gs, t, bar, release);
-            if (FUSE && t == 0 && sc.h + 1 == L) dl[atomicAdd(dl_n, 1)] = sc.slot * HV + sc.hv;      // window just filled
+            if (FUSE && sc.h + 1 == L) note_due(sc.slot * HV + sc.hv, true);                        // window just filled
         } else {
-            if (FUSE && t == 0 && sc.slot > 0 && sc.h == L) dl[atomicAdd(dl_n, 1)] = sc.slot * HV + sc.hv;   // was full already
+            if (FUSE && sc.slot > 0 && sc.h == L) note_due(sc.slot * HV + sc.hv, false);             // was full already
             release();
             int n0, hv0;
             row_head(i, n0, hv0);
@@ -1168,16 +1187,17 @@ __global__ void __launch_bounds__(UT + NG * GT, 1) step_pipelined_kernel(StepPar
         const int ndl = *abortf ? 0 : *dl_n;
         int* const wl = ft.work;
         if (wl == nullptr && ndl == 0) return;                   // (before any tensor memory is held)
-        const bool keep_all = wl == nullptr || ndl >= 4 || ndl - 1 > WL_SLOTS;
-        const int npub = keep_all ? 0 : (ndl > 1 ? ndl - 1 : 0); // heads left in this CTA's mailbox
+        // dl[1 .. npub] were posted by the consumers when they found them; the CTA keeps dl[0] and dl[npub + 1 ..]
+        const int nfound = *dl_n;                               // (also after an abort: what was posted has to be taken back)
+        const int npub = wl == nullptr ? 0 : (nfound - 1 < WL_EARLY ? (nfound > 1 ? nfound - 1 : 0) : WL_EARLY);
         int* const box = wl + WL_BOX;
-        if (tid == 0) { s_pop[2] = 0; s_pop[3] = 0; }            // [2]: occupied slots found by a scan, [3]: 1 = nothing was posted in this launch
+        if (tid == 0) {
+            s_pop[2] = 0; s_pop[3] = 0;                          // [2]: occupied slots found by a scan, [3]: 1 = nothing was posted in this launch
+            if (npub > 0) dl[npub] = dl[0];                      // the kept heads, contiguous: dl[npub .. nfound - 1]
+        }
         if (wl != nullptr) {
-            if (npub > 0) __threadfence();                       // the step's stores of the posted heads come before their entries
             __syncthreads();
             if (tid == 0) {
-                for (int i = 0; i < npub; ++i) st_volatile_i32(box + bid * WL_SLOTS + i, dl[1 + i] + 1);
-                if (npub > 0) __threadfence();
                 // one word counts the reports (low 16 bits) and the heads posted (above them)
                 const int old = atomicAdd(wl + WL_DONE, 1 + (npub << 16));
                 if ((old & 0xffff) == grid - 1) {                // the last CTA to report closes the launch's count at once: the others
@@ -1190,8 +1210,9 @@ __global__ void __launch_bounds__(UT + NG * GT, 1) step_pipelined_kernel(StepPar
         }
         // Rounds of heads: first what this CTA keeps of its own list; with the mailboxes, then one head per round -- its own
         // posted heads that nobody took, or, for a CTA that filled nothing, heads from other CTAs' mailboxes.
-        const int* heads = dl;
-        int nh = keep_all ? ndl : (ndl > 0 ? 1 : 0);
+        __syncthreads();                                         // (dl[npub] is in place)
+        const int* heads = dl + npub;
+        int nh = ndl > 0 ? ndl - npub : 0;
         int reclaim = 0;                                         // (thread 0) next slot of the own mailbox to look at
         const int total = grid * WL_SLOTS;
         bool inited = false;
