@@ -784,15 +784,17 @@ struct FuseTail {
 };
 // Shared mailboxes of the fused flush (global scratch of the caller, all zero between launches).  A serving batch fills the
 // windows of a few rows per step, and the program -> CTA map puts two or three of their heads on some CTAs and none on
-// others.  A CTA that filled two or three windows keeps the first head and leaves the others in its own mailbox (a few
-// slots per CTA: plain stores, no atomics); a CTA that filled none scans the mailboxes and claims an entry with an atomic
-// exchange, which also empties the slot.  The owner, when it has flushed its own head, claims back whatever is still in its
-// mailbox and flushes that too: every entry is flushed exactly once whether or not anybody helps, so nobody waits for
-// anybody for correctness, helpers may give up at any time, and the slots are all zero again when the kernel ends.
-// Helpers stop when the launch's reports are complete and a scan finds nothing: every CTA adds one to a counter after its
-// mailbox is written; the CTA that makes it `grid` sets the counter back to zero and bumps a generation word, which every
+// others.  A CTA keeps the first head whose window it fills; the second and the third go into its own mailbox (a few slots
+// per CTA: plain stores, no atomics) as soon as their program has run, while the CTA still has programs ahead of it, and any
+// more stay with it.  A CTA that filled none scans the mailboxes when its programs are done and claims an entry with an
+// atomic exchange, which also empties the slot.  The owner, when it has flushed what it kept, claims back whatever is still
+// in its mailbox and flushes that too: every entry is flushed exactly once whether or not anybody helps, so nobody waits
+// for anybody for correctness, helpers may give up at any time, and the slots are all zero again when the kernel ends.
+// Helpers stop when the launch's reports are complete and a scan finds nothing: every CTA adds one to a counter when its
+// programs are done; the CTA that makes it `grid` sets the counter back to zero and bumps a generation word, which every
 // CTA read when it started (its own report, and therefore the last one, comes after that read).
-// A CTA that filled four or more windows is in a call in which every CTA did (windows in phase) and keeps them all.
+// (When every window fills in the same step each CTA has dozens of heads: it posts two, nobody has time for them, and it
+// takes them back at the end.)
 constexpr int WL_DONE = 0, WL_GEN = 1, WL_BOX = 16;              // int offsets: reports of this launch, generation, mailboxes
 constexpr int WL_SLOTS = 4;                                      // slots per CTA (at most two are used); entry = head + 1
 constexpr int WL_EARLY = 2;                                      // heads after a CTA's first that are posted (the rest stay with it)
